@@ -1,0 +1,70 @@
+// Library-wide state of the C ABI: error text, device status word, launch counter.
+#include <stdarg.h>
+#include <atomic>
+#include <string.h>
+
+#include "common.cuh"
+
+static thread_local char g_err[512] = "";
+static std::atomic<uint64_t> g_launches{0};
+
+__device__ unsigned int g_fg_status = 0;
+
+void fg_set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+void fg_count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+unsigned int* fg_status_word_device_ptr() {
+    // One symbol address per device; looked up lazily for the current device.
+    static unsigned int* ptrs[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!ptrs[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_fg_status) != cudaSuccess) return nullptr;
+        ptrs[dev] = (unsigned int*)p;
+    }
+    return ptrs[dev];
+}
+
+int fg_num_sms() {
+    static int sms[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!sms[dev]) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        sms[dev] = v;
+    }
+    return sms[dev];
+}
+
+extern "C" {
+
+int fg_version(void) { return 100; }
+
+const char* fg_last_error(void) { return g_err; }
+
+uint64_t fg_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int fg_device_status(unsigned int* status) {
+    FG_REQUIRE(status != nullptr, FG_ERR_INVALID_ARGUMENT, "status must not be NULL");
+    unsigned int v = 0, zero = 0;
+    FG_CUDA(cudaDeviceSynchronize());
+    FG_CUDA(cudaMemcpyFromSymbol(&v, g_fg_status, sizeof(v)));
+    if (v != 0) FG_CUDA(cudaMemcpyToSymbol(g_fg_status, &zero, sizeof(zero)));
+    *status = v;
+    if (v != 0) {
+        fg_set_error("device status 0x%08x: a bounded wait inside a kernel ran out (code %u, site %u)", v,
+                     v >> 16, v & 0xffffu);
+        return FG_ERR_DEVICE_STATUS;
+    }
+    return FG_OK;
+}
+
+}  // extern "C"

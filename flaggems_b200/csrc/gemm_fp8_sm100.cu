@@ -1,0 +1,641 @@
+// FP8 (e4m3) scaled matrix products on tcgen05 tensor cores for sm_100a.
+//
+// One persistent, warp-specialised kernel template serves the dense scaled GEMM
+// (scalar / per-row / per-column scales), the 128x128 block-scaled GEMM and the grouped
+// expert GEMMs of the fused MoE layer:
+//
+//   warp 0      TMA producer: A tile [128 x 128 B] and B tile [BN x 128 B] per K block into a
+//               multi-stage shared-memory ring (128-byte swizzle), mbarrier complete_tx.
+//   warp 1      MMA issuer: tcgen05.mma kind::f8f6f4, M=128, N=BN, K=32 per instruction, fp32
+//               accumulators in TMEM (two buffers of BN columns), tcgen05.commit to release
+//               ring stages and to publish accumulators.
+//   warps 2..   epilogue: tcgen05.ld TMEM -> registers, scales / SiLU / router weight / bias,
+//               conversion and global stores.  BN/32 warps; each thread owns one tile row and
+//               128 accumulator columns.
+//
+// Block-scaled mode: the accumulator of every 128-wide K block is published separately and
+// the epilogue warps fold it into fp32 registers as acc += partial * (As[m,kb] * Bs[nb,kb])
+// while the MMA warp fills the other TMEM buffer.
+//
+// Every mbarrier wait is bounded; a wait that runs out sets the device status word and the
+// CTA drains and frees its TMEM instead of hanging.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+using namespace fgptx;
+
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 128;  // e4m3: bytes == elements; one 128-byte swizzle row
+constexpr int UMMA_K = 32;
+constexpr int GROUP_M = 16;  // m-blocks per rasterisation band
+
+struct GemmParams {
+    int64_t M;  // dense: rows of A and C.  grouped: rows available in A (upper bound)
+    int N;      // rows of B per expert (fused SiLU: 2*I)
+    int K;
+    int n_out;  // columns written (N, or I with fused SiLU)
+    void* c;
+    int64_t ld_c;
+    int out_dtype;
+    int c_vec_ok;  // rows of C are 16-byte aligned
+    const float* sa;
+    const float* sb;
+    const void* bias;
+    int sa_mode, sb_mode;  // FG_SCALE_SCALAR / FG_SCALE_VECTOR (ignored in block mode)
+    int bias_after_round;
+    int64_t ld_as;                                  // block mode: row stride of As
+    int64_t bs_stride_n, bs_stride_k, bs_stride_e;  // block mode: strides of Bs
+    int64_t sb_stride_e;                            // vector mode: per-expert stride of sb
+    int grouped;
+    const int32_t* sorted_ids;
+    const int32_t* expert_ids;
+    const int32_t* num_post_pad;
+    int block_rows;  // rows per m-tile (TMA box rows of A), <= 128
+    int64_t numel;
+    int scatter, mul_weight;
+    const void* topk_w;
+    int topk_w_dtype;
+    unsigned int* status;
+};
+
+template <int BN>
+struct Cfg {
+    static constexpr int EPI_WARPS = BN / 32;
+    static constexpr int THREADS = 64 + 32 * EPI_WARPS;
+    static constexpr int A_BYTES = BLOCK_M * BLOCK_K;
+    static constexpr int B_BYTES = BN * BLOCK_K;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = BN == 256 ? 4 : 6;
+    static constexpr int TMEM_COLS = 2 * BN;
+    static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
+};
+
+__device__ __forceinline__ float load_as_float(const void* p, int dtype, int64_t i) {
+    if (dtype == FG_DTYPE_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+    if (dtype == FG_DTYPE_F16) return __half2float(reinterpret_cast<const __half*>(p)[i]);
+    return reinterpret_cast<const float*>(p)[i];
+}
+
+__device__ __forceinline__ float round_through(float v, int dtype) {
+    if (dtype == FG_DTYPE_BF16) return __bfloat162float(__float2bfloat16_rn(v));
+    if (dtype == FG_DTYPE_F16) return __half2float(__float2half_rn(v));
+    return v;
+}
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+
+// Stores 32 consecutive output values of one row; ncols (<= 32) of them are in range.
+__device__ __forceinline__ void store_chunk(void* row_ptr, int col0, const float (&v)[32], int ncols, int dtype,
+                                            bool vec_ok) {
+    if (dtype == FG_DTYPE_F32) {
+        float* o = reinterpret_cast<float*>(row_ptr) + col0;
+        if (vec_ok && ncols == 32) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                reinterpret_cast<float4*>(o)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (i < ncols) o[i] = v[i];
+        }
+        return;
+    }
+    uint32_t w[16];
+    if (dtype == FG_DTYPE_BF16) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+    }
+    uint16_t* o = reinterpret_cast<uint16_t*>(row_ptr) + col0;
+    if (vec_ok && ncols == 32) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            reinterpret_cast<uint4*>(o)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (i < ncols) o[i] = (uint16_t)((i & 1) ? (w[i >> 1] >> 16) : (w[i >> 1] & 0xffffu));
+    }
+}
+
+struct TileCoord {
+    int m_blk, n_blk;
+};
+
+__device__ __forceinline__ TileCoord tile_coord(int t, int num_m, int num_n) {
+    const int band = t / (GROUP_M * num_n);
+    const int first_m = band * GROUP_M;
+    const int gm = min(GROUP_M, num_m - first_m);
+    const int rem = t - band * GROUP_M * num_n;
+    TileCoord tc;
+    tc.m_blk = first_m + rem % gm;
+    tc.n_blk = rem / gm;
+    return tc;
+}
+
+template <int BN, bool BLOCK_SCALED, bool FUSE_SILU>
+__global__ void __launch_bounds__(Cfg<BN>::THREADS, 1)
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                const GemmParams p) {
+    using C = Cfg<BN>;
+    constexpr int STAGES = C::STAGES;
+    constexpr int OUT_TILE_N = FUSE_SILU ? BN / 2 : BN;  // output columns per tile
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * C::STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* tmem_full = empty_bar + STAGES;
+    uint64_t* tmem_empty = tmem_full + 2;
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    volatile uint32_t* abort_flag = tmem_base_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tmem_full[b], 1);
+            mbar_init(&tmem_empty[b], C::EPI_WARPS);
+        }
+        *abort_flag = 0u;
+        fence_mbar_init();
+        tma_prefetch_desc(&tm_a);
+        tma_prefetch_desc(&tm_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_base_slot, C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    const int num_k_blocks = (p.K + BLOCK_K - 1) / BLOCK_K;
+    int num_m;
+    if (p.grouped) {
+        int64_t rows = *p.num_post_pad;
+        if (rows > p.M) rows = p.M;
+        num_m = (int)(rows / p.block_rows);
+    } else {
+        num_m = (int)((p.M + BLOCK_M - 1) / BLOCK_M);
+    }
+    const int num_n = (p.n_out + OUT_TILE_N - 1) / OUT_TILE_N;
+    const int num_tiles = num_m * num_n;
+    const int a_rows_step = p.grouped ? p.block_rows : BLOCK_M;
+    const uint32_t stage_tx = (uint32_t)(a_rows_step * BLOCK_K + C::B_BYTES);
+
+    if (warp == 0) {
+        // ------------------------------- TMA producer -------------------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const TileCoord tc = tile_coord(t, num_m, num_n);
+                const int expert = p.grouped ? p.expert_ids[tc.m_blk] : 0;
+                if (expert < 0) continue;
+                const int m0 = tc.m_blk * a_rows_step;
+                const int n0 = tc.n_blk * OUT_TILE_N;
+                for (int kb = 0; kb < num_k_blocks; ++kb) {
+                    ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 1);
+                    if (!ok) break;
+                    uint8_t* sa = smem + stage * C::STAGE_BYTES;
+                    uint8_t* sb = sa + C::A_BYTES;
+                    mbar_arrive_expect_tx(&full_bar[stage], stage_tx);
+                    tma_load_2d(sa, &tm_a, &full_bar[stage], kb * BLOCK_K, m0);
+                    if constexpr (FUSE_SILU) {
+                        tma_load_3d(sb, &tm_b, &full_bar[stage], kb * BLOCK_K, n0, expert);
+                        tma_load_3d(sb + (BN / 2) * BLOCK_K, &tm_b, &full_bar[stage], kb * BLOCK_K, p.N / 2 + n0,
+                                    expert);
+                    } else {
+                        tma_load_3d(sb, &tm_b, &full_bar[stage], kb * BLOCK_K, n0, expert);
+                    }
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------- MMA issuer ---------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_e4m3_f32(BLOCK_M, BN);
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t acc_iter = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const TileCoord tc = tile_coord(t, num_m, num_n);
+                const int expert = p.grouped ? p.expert_ids[tc.m_blk] : 0;
+                if (expert < 0) continue;
+                for (int kb = 0; kb < num_k_blocks; ++kb) {
+                    const uint32_t buf = acc_iter & 1u;
+                    if (BLOCK_SCALED || kb == 0) {
+                        ok = mbar_wait(&tmem_empty[buf], ((acc_iter >> 1) & 1u) ^ 1u, abort_flag, p.status, 2);
+                        if (!ok) break;
+                    }
+                    ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(smem + stage * C::STAGE_BYTES);
+                    const uint64_t a_desc = umma_desc_k_sw128(a_addr);
+                    const uint64_t b_desc = umma_desc_k_sw128(a_addr + C::A_BYTES);
+                    const uint32_t d_tmem = tmem_base + buf * BN;
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                        const uint32_t accumulate = BLOCK_SCALED ? (k != 0) : ((kb | k) != 0);
+                        // advancing K by 32 bytes inside the swizzle row: +2 in 16-byte units
+                        umma_f8f6f4(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, accumulate);
+                    }
+                    umma_commit(&empty_bar[stage]);
+                    if (BLOCK_SCALED || kb == num_k_blocks - 1) {
+                        umma_commit(&tmem_full[buf]);
+                        ++acc_iter;
+                    }
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else {
+        // ------------------------------- epilogue -----------------------------------------
+        const int ew = warp - 2;
+        const int quad = warp & 3;                  // TMEM lanes this warp may touch: [32*quad, +32)
+        const int half = C::EPI_WARPS == 8 ? ew / 4 : 0;
+        const int r_in_tile = quad * 32 + lane;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+        uint32_t acc_iter = 0;
+        bool ok = true;
+
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            const TileCoord tc = tile_coord(t, num_m, num_n);
+            const int expert = p.grouped ? p.expert_ids[tc.m_blk] : 0;
+            const int m0 = tc.m_blk * a_rows_step;
+            const int n0 = tc.n_blk * OUT_TILE_N;
+            const int64_t row = (int64_t)m0 + r_in_tile;  // row of A (sorted row when grouped)
+
+            // Where this thread's row goes, and whether it is written at all.
+            bool row_ok;
+            int64_t out_row = row;
+            float weight = 1.0f;
+            if (p.grouped) {
+                row_ok = r_in_tile < p.block_rows;
+                if (row_ok && (p.scatter || p.mul_weight)) {
+                    const int32_t sid = p.sorted_ids[row];
+                    const bool real = sid >= 0 && sid < p.numel;
+                    if (p.scatter) {
+                        row_ok = real;
+                        out_row = sid;
+                    }
+                    if (p.mul_weight && real) weight = load_as_float(p.topk_w, p.topk_w_dtype, sid);
+                }
+            } else {
+                row_ok = row < p.M;
+            }
+            const int esz = p.out_dtype == FG_DTYPE_F32 ? 4 : 2;
+            uint8_t* out_ptr = reinterpret_cast<uint8_t*>(p.c) + out_row * p.ld_c * esz;
+            // column of output chunk c (32 wide) handled by this thread
+            const int out_col_base = n0 + (FUSE_SILU ? 64 * half : 128 * half);
+            constexpr int OUT_CHUNKS = FUSE_SILU ? 2 : 4;
+
+            if (expert < 0) {
+                // Block of an expert that is not on this rank: the rows are defined to be zero.
+                if (row_ok) {
+                    float z[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) z[i] = 0.0f;
+#pragma unroll
+                    for (int c = 0; c < OUT_CHUNKS; ++c) {
+                        const int col = out_col_base + 32 * c;
+                        const int nc = min(32, p.n_out - col);
+                        if (nc > 0) store_chunk(out_ptr, col, z, nc, p.out_dtype, p.c_vec_ok);
+                    }
+                }
+                continue;
+            }
+            const int64_t srow = p.grouped ? row : (row < p.M ? row : p.M - 1);  // row used for scale loads
+
+            if constexpr (!BLOCK_SCALED) {
+                const uint32_t buf = acc_iter & 1u;
+                ok = mbar_wait(&tmem_full[buf], (acc_iter >> 1) & 1u, abort_flag, p.status, 4);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const float sa = p.sa_mode == FG_SCALE_VECTOR ? p.sa[srow] : p.sa[0];
+                const float* sbp = p.sb + (p.sb_mode == FG_SCALE_VECTOR ? (int64_t)expert * p.sb_stride_e : (int64_t)expert * (p.grouped ? 1 : 0));
+                const uint32_t tbuf = lane_addr + buf * BN;
+#pragma unroll
+                for (int c = 0; c < OUT_CHUNKS; ++c) {
+                    const int col = out_col_base + 32 * c;
+                    uint32_t raw[32];
+                    float v[32];
+                    if constexpr (FUSE_SILU) {
+                        uint32_t raw_up[32];
+                        tmem_ld_32x32b_x32(tbuf + 64 * half + 32 * c, raw);
+                        tmem_ld_32x32b_x32(tbuf + BN / 2 + 64 * half + 32 * c, raw_up);
+                        tmem_ld_wait();
+                        const int up_off = p.N / 2;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int n = min(col + i, p.n_out - 1);
+                            const float sg = p.sb_mode == FG_SCALE_VECTOR ? __ldg(sbp + n) : sbp[0];
+                            const float su = p.sb_mode == FG_SCALE_VECTOR ? __ldg(sbp + up_off + n) : sbp[0];
+                            const float g = __uint_as_float(raw[i]) * sa * sg;
+                            const float u = __uint_as_float(raw_up[i]) * sa * su;
+                            v[i] = silu_mul(g, u);
+                        }
+                    } else {
+                        tmem_ld_32x32b_x32(tbuf + 128 * half + 32 * c, raw);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int n = min(col + i, p.n_out - 1);
+                            const float sb = p.sb_mode == FG_SCALE_VECTOR ? __ldg(sbp + n) : sbp[0];
+                            float x = sb * (sa * __uint_as_float(raw[i]));
+                            x *= weight;
+                            if (p.bias) {
+                                const float b = load_as_float(p.bias, p.out_dtype, n);
+                                x = p.bias_after_round ? round_through(x, p.out_dtype) + b : x + b;
+                            }
+                            v[i] = x;
+                        }
+                    }
+                    const int nc = min(32, p.n_out - col);
+                    if (row_ok && nc > 0) store_chunk(out_ptr, col, v, nc, p.out_dtype, p.c_vec_ok);
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+                ++acc_iter;
+            } else {
+                float acc[128];
+#pragma unroll
+                for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
+                // Block row of Bs for this thread's columns (two of them with fused SiLU).
+                const float* bs_e = p.sb + (int64_t)expert * p.bs_stride_e;
+                int nb0, nb1;
+                if constexpr (FUSE_SILU) {
+                    nb0 = (n0 + 64 * half) / 128;
+                    nb1 = (p.N / 2 + n0 + 64 * half) / 128;
+                } else {
+                    nb0 = nb1 = (n0 + 128 * half) / 128;
+                }
+                const int max_nb = (p.N + 127) / 128 - 1;
+                nb0 = min(nb0, max_nb);
+                nb1 = min(nb1, max_nb);
+                const float* as_row = p.sa + srow * p.ld_as;
+                float as_next = as_row[0];
+                for (int kb = 0; kb < num_k_blocks; ++kb) {
+                    const float a_s = as_next;
+                    if (kb + 1 < num_k_blocks) as_next = as_row[kb + 1];
+                    const float sc0 = a_s * __ldg(bs_e + nb0 * p.bs_stride_n + kb * p.bs_stride_k);
+                    const float sc1 = FUSE_SILU ? a_s * __ldg(bs_e + nb1 * p.bs_stride_n + kb * p.bs_stride_k) : sc0;
+                    const uint32_t buf = acc_iter & 1u;
+                    ok = mbar_wait(&tmem_full[buf], (acc_iter >> 1) & 1u, abort_flag, p.status, 5);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t tbuf = lane_addr + buf * BN;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t raw[32];
+                        uint32_t tcol;
+                        if constexpr (FUSE_SILU) tcol = (c < 2 ? 0 : BN / 2) + 64 * half + 32 * (c & 1);
+                        else tcol = 128 * half + 32 * c;
+                        tmem_ld_32x32b_x32(tbuf + tcol, raw);
+                        tmem_ld_wait();
+                        const float sc = (FUSE_SILU && c >= 2) ? sc1 : sc0;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) acc[32 * c + i] = fmaf(__uint_as_float(raw[i]), sc, acc[32 * c + i]);
+                    }
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+                    ++acc_iter;
+                }
+                if (!ok) break;
+#pragma unroll
+                for (int c = 0; c < OUT_CHUNKS; ++c) {
+                    const int col = out_col_base + 32 * c;
+                    float v[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if constexpr (FUSE_SILU) v[i] = silu_mul(acc[32 * c + i], acc[64 + 32 * c + i]);
+                        else v[i] = acc[32 * c + i] * weight;
+                    }
+                    const int nc = min(32, p.n_out - col);
+                    if (row_ok && nc > 0) store_chunk(out_ptr, col, v, nc, p.out_dtype, p.c_vec_ok);
+                }
+            }
+        }
+    }
+
+    // ------------------------------- teardown ---------------------------------------------
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// Byte tensor [d2][d1][d0] with d0 contiguous; box = 128 x box_rows x 1, 128-byte swizzle.
+int make_map(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1,
+             uint64_t stride2, uint32_t box_rows, int rank) {
+    EncodeTiledFn fn = get_encode_fn();
+    FG_REQUIRE(fn != nullptr, FG_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[3] = {d0, d1, d2};
+    cuuint64_t strides[2] = {stride1, stride2};
+    cuuint32_t box[3] = {128, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box,
+                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    FG_REQUIRE(r == CUDA_SUCCESS, FG_ERR_CUDA,
+               "cuTensorMapEncodeTiled failed (%d): base %p dims %llu x %llu x %llu strides %llu, %llu box rows %u",
+               (int)r, base, (unsigned long long)d0, (unsigned long long)d1, (unsigned long long)d2,
+               (unsigned long long)stride1, (unsigned long long)stride2, box_rows);
+    return FG_OK;
+}
+
+template <int BN, bool BS, bool SILU>
+int launch_inst(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int max_tiles, cudaStream_t st) {
+    using C = Cfg<BN>;
+    auto kernel = gemm_fp8_kernel<BN, BS, SILU>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        FG_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        attr_done = true;
+    }
+    int grid = fg_num_sms();
+    if (max_tiles < grid) grid = max_tiles;
+    if (grid < 1) grid = 1;
+    kernel<<<grid, C::THREADS, C::SMEM_BYTES, st>>>(ta, tb, p);
+    fg_count_launch(1);
+    FG_LAUNCH_CHECK();
+    return FG_OK;
+}
+
+int launch_gemm(GemmParams& p, const void* a, int64_t a_rows, int64_t ld_a, const void* b, int num_experts,
+                int64_t ld_b, bool block_scaled, bool fuse_silu, cudaStream_t st) {
+    FG_REQUIRE(p.K > 0 && p.K % 16 == 0, FG_ERR_UNSUPPORTED, "K = %d must be a positive multiple of 16", p.K);
+    FG_REQUIRE((uintptr_t)a % 16 == 0 && (uintptr_t)b % 16 == 0 && ld_a % 16 == 0 && ld_b % 16 == 0,
+               FG_ERR_UNSUPPORTED, "a and b must be 16-byte aligned with row strides that are multiples of 16 bytes");
+    FG_REQUIRE(ld_a >= p.K && ld_b >= p.K, FG_ERR_INVALID_ARGUMENT, "row stride smaller than K");
+    p.status = fg_status_word_device_ptr();
+    const int esz = p.out_dtype == FG_DTYPE_F32 ? 4 : 2;
+    p.c_vec_ok = ((uintptr_t)p.c % 16 == 0) && ((p.ld_c * esz) % 16 == 0);
+
+    const int64_t m_tiles = p.grouped ? a_rows / p.block_rows : fg_cdiv(p.M, BLOCK_M);
+    // Wide tiles when they still fill the machine, otherwise narrower ones.
+    const int out_per_256 = fuse_silu ? 128 : 256;
+    const int64_t tiles256 = m_tiles * fg_cdiv(p.n_out, out_per_256);
+    const bool wide = tiles256 >= fg_num_sms();
+    const int bn = wide ? 256 : 128;
+    const int out_tile = fuse_silu ? bn / 2 : bn;
+    const int64_t tiles = m_tiles * fg_cdiv(p.n_out, out_tile);
+    FG_REQUIRE(tiles < (1ll << 31), FG_ERR_UNSUPPORTED, "too many tiles");
+    if (tiles == 0) return FG_OK;
+
+    CUtensorMap ta, tb;
+    int rc = make_map(&ta, a, (uint64_t)p.K, (uint64_t)a_rows, 1, (uint64_t)ld_a, 0, (uint32_t)(p.grouped ? p.block_rows : BLOCK_M), 2);
+    if (rc != FG_OK) return rc;
+    rc = make_map(&tb, b, (uint64_t)p.K, (uint64_t)p.N, (uint64_t)num_experts, (uint64_t)ld_b,
+                  (uint64_t)ld_b * (uint64_t)p.N, (uint32_t)(fuse_silu ? bn / 2 : bn), 3);
+    if (rc != FG_OK) return rc;
+
+#define FG_DISPATCH(BN_)                                                                       \
+    if (block_scaled) {                                                                        \
+        if (fuse_silu) return launch_inst<BN_, true, true>(ta, tb, p, (int)tiles, st);         \
+        return launch_inst<BN_, true, false>(ta, tb, p, (int)tiles, st);                       \
+    } else {                                                                                   \
+        if (fuse_silu) return launch_inst<BN_, false, true>(ta, tb, p, (int)tiles, st);        \
+        return launch_inst<BN_, false, false>(ta, tb, p, (int)tiles, st);                      \
+    }
+    if (wide) {
+        FG_DISPATCH(256)
+    } else {
+        FG_DISPATCH(128)
+    }
+#undef FG_DISPATCH
+}
+
+bool dtype_ok(int d) { return d == FG_DTYPE_BF16 || d == FG_DTYPE_F16 || d == FG_DTYPE_F32; }
+
+}  // namespace
+
+extern "C" {
+
+int fg_scaled_mm_fp8(void* c, const void* a, const void* b, const float* sa, const float* sb, const void* bias,
+                     int64_t M, int64_t N, int64_t K, int64_t ld_a, int64_t ld_b, int64_t ld_c, int sa_mode,
+                     int sb_mode, int out_dtype, int bias_after_round, void* stream) {
+    FG_REQUIRE(M >= 0 && N >= 0 && K >= 0, FG_ERR_INVALID_ARGUMENT, "negative size");
+    if (M == 0 || N == 0) return FG_OK;
+    FG_REQUIRE(c && a && b && sa && sb, FG_ERR_INVALID_ARGUMENT, "null pointer");
+    FG_REQUIRE(dtype_ok(out_dtype), FG_ERR_INVALID_ARGUMENT, "bad out_dtype %d", out_dtype);
+    FG_REQUIRE((sa_mode == FG_SCALE_SCALAR || sa_mode == FG_SCALE_VECTOR) &&
+                   (sb_mode == FG_SCALE_SCALAR || sb_mode == FG_SCALE_VECTOR),
+               FG_ERR_INVALID_ARGUMENT, "scale modes must be scalar or vector");
+    FG_REQUIRE(N < (1ll << 31) && K < (1ll << 31) && M < (1ll << 31), FG_ERR_UNSUPPORTED, "dimension too large");
+    GemmParams p{};
+    p.M = M; p.N = (int)N; p.K = (int)K; p.n_out = (int)N;
+    p.c = c; p.ld_c = ld_c; p.out_dtype = out_dtype;
+    p.sa = sa; p.sb = sb; p.bias = bias; p.sa_mode = sa_mode; p.sb_mode = sb_mode;
+    p.bias_after_round = bias_after_round;
+    p.block_rows = BLOCK_M;
+    return launch_gemm(p, a, M, ld_a, b, 1, ld_b, false, false, (cudaStream_t)stream);
+}
+
+int fg_block_scaled_mm_fp8(void* c, const void* a, const void* b, const float* a_s, const float* b_s, int64_t M,
+                           int64_t N, int64_t K, int64_t ld_a, int64_t ld_b, int64_t ld_c, int64_t ld_as,
+                           int64_t bs_stride_n, int64_t bs_stride_k, int out_dtype, void* stream) {
+    FG_REQUIRE(M >= 0 && N >= 0 && K >= 0, FG_ERR_INVALID_ARGUMENT, "negative size");
+    if (M == 0 || N == 0) return FG_OK;
+    FG_REQUIRE(c && a && b && a_s && b_s, FG_ERR_INVALID_ARGUMENT, "null pointer");
+    FG_REQUIRE(dtype_ok(out_dtype), FG_ERR_INVALID_ARGUMENT, "bad out_dtype %d", out_dtype);
+    FG_REQUIRE(N < (1ll << 31) && K < (1ll << 31) && M < (1ll << 31), FG_ERR_UNSUPPORTED, "dimension too large");
+    GemmParams p{};
+    p.M = M; p.N = (int)N; p.K = (int)K; p.n_out = (int)N;
+    p.c = c; p.ld_c = ld_c; p.out_dtype = out_dtype;
+    p.sa = a_s; p.sb = b_s; p.ld_as = ld_as; p.bs_stride_n = bs_stride_n; p.bs_stride_k = bs_stride_k;
+    p.block_rows = BLOCK_M;
+    return launch_gemm(p, a, M, ld_a, b, 1, ld_b, true, false, (cudaStream_t)stream);
+}
+
+int fg_moe_grouped_gemm_fp8(void* c, const void* a, const void* w, const float* a_scale, const float* w_scale,
+                            const void* topk_weights, int topk_w_dtype, const int32_t* sorted_ids,
+                            const int32_t* expert_ids, const int32_t* num_post_pad, int64_t max_rows, int64_t numel,
+                            int num_experts, int64_t N, int64_t K, int64_t ld_a, int64_t ld_c, int block_rows,
+                            int scale_mode, int a_scale_per_row, int fuse_silu, int scatter, int mul_weight,
+                            int out_dtype, void* stream) {
+    FG_REQUIRE(max_rows >= 0 && N > 0 && K > 0 && num_experts > 0, FG_ERR_INVALID_ARGUMENT, "bad sizes");
+    FG_REQUIRE(c && a && w && a_scale && w_scale && sorted_ids && expert_ids && num_post_pad,
+               FG_ERR_INVALID_ARGUMENT, "null pointer");
+    FG_REQUIRE(dtype_ok(out_dtype), FG_ERR_INVALID_ARGUMENT, "bad out_dtype %d", out_dtype);
+    FG_REQUIRE(block_rows >= 8 && block_rows <= 128 && block_rows % 8 == 0, FG_ERR_UNSUPPORTED,
+               "block_rows %d must be a multiple of 8 in [8, 128]", block_rows);
+    FG_REQUIRE(!mul_weight || (topk_weights && dtype_ok(topk_w_dtype)), FG_ERR_INVALID_ARGUMENT,
+               "mul_weight needs topk_weights");
+    FG_REQUIRE(N < (1ll << 31) && K < (1ll << 31), FG_ERR_UNSUPPORTED, "dimension too large");
+    FG_REQUIRE(!fuse_silu || N % 2 == 0, FG_ERR_INVALID_ARGUMENT, "fused SiLU needs an even N");
+    const bool block = scale_mode == FG_SCALE_BLOCK;
+    FG_REQUIRE(!(block && fuse_silu) || (N / 2) % 128 == 0, FG_ERR_UNSUPPORTED,
+               "fused SiLU with block scales needs the intermediate size %lld to be a multiple of 128",
+               (long long)(N / 2));
+    if (max_rows == 0) return FG_OK;
+    GemmParams p{};
+    p.M = max_rows / block_rows * block_rows; p.N = (int)N; p.K = (int)K; p.n_out = fuse_silu ? (int)(N / 2) : (int)N;
+    p.c = c; p.ld_c = ld_c; p.out_dtype = out_dtype;
+    p.sa = a_scale; p.sb = w_scale;
+    if (block) {
+        const int64_t kb = fg_cdiv(K, 128), nb = fg_cdiv(N, 128);
+        p.ld_as = kb; p.bs_stride_k = 1; p.bs_stride_n = kb; p.bs_stride_e = kb * nb;
+    } else {
+        p.sa_mode = (scale_mode == FG_SCALE_VECTOR || a_scale_per_row) ? FG_SCALE_VECTOR : FG_SCALE_SCALAR;
+        p.sb_mode = scale_mode == FG_SCALE_VECTOR ? FG_SCALE_VECTOR : FG_SCALE_SCALAR;
+        p.sb_stride_e = N;
+    }
+    p.grouped = 1; p.sorted_ids = sorted_ids; p.expert_ids = expert_ids; p.num_post_pad = num_post_pad;
+    p.block_rows = block_rows; p.numel = numel; p.scatter = scatter; p.mul_weight = mul_weight;
+    p.topk_w = topk_weights; p.topk_w_dtype = topk_w_dtype;
+    return launch_gemm(p, a, p.M, ld_a, w, num_experts, K, block, fuse_silu != 0, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,327 @@
+// Fused-MoE glue kernels: moe_align_block_size (one launch, thread-block cluster with
+// distributed shared memory), silu_and_mul, moe_sum.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace {
+
+// ---------------------------------------------------------------------------------------
+// moe_align_block_size
+//
+// A cluster of up to 8 CTAs x 32 warps splits the numel route slots into contiguous
+// segments, one per warp, in index order.  Each warp histograms its segment into its own
+// shared-memory row; an exclusive scan over (cluster rank, warp) per expert, done through
+// distributed shared memory, gives every warp the rank its first slot of each expert has
+// inside that expert.  A warp then walks its segment in order, 32 slots at a time, ranking
+// equal experts inside the step with match_any, so the output order inside an expert is
+// ascending slot index: the same as a stable sort.  No global scratch, no global atomics.
+// ---------------------------------------------------------------------------------------
+constexpr int ALIGN_THREADS = 1024;
+constexpr int ALIGN_WARPS = ALIGN_THREADS / 32;
+
+struct AlignArgs {
+    const void* topk_ids;
+    int64_t numel;
+    int num_experts;
+    int block_size;
+    const int32_t* expert_map;
+    int expert_map_len;
+    int32_t* sorted_ids;
+    int64_t max_pad;
+    int32_t* expert_ids;
+    int64_t n_blocks;
+    int32_t* num_post_pad;
+};
+
+template <typename IdT>
+__global__ void __launch_bounds__(ALIGN_THREADS, 1) moe_align_kernel(AlignArgs a) {
+    cg::cluster_group cluster = cg::this_cluster();
+    const int n_ranks = (int)cluster.num_blocks();
+    const int rank = (int)cluster.block_rank();
+    const int E = a.num_experts;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    extern __shared__ int32_t smem[];
+    int32_t* warp_hist = smem;                    // [ALIGN_WARPS][E] counts, then in-CTA exclusive prefixes
+    int32_t* cta_total = smem + ALIGN_WARPS * E;  // [E] this CTA's count per expert (read by peers)
+    int32_t* base = cta_total + E;                // [E] first output slot for this CTA's first row of e
+    int32_t* pad_lo = base + E;                   // [E] first padding slot of e
+    int32_t* pad_hi = pad_lo + E;                 // [E] one past the last slot of e
+    __shared__ int32_t scan_tmp[ALIGN_WARPS];
+    __shared__ int32_t total_padded_s;
+
+    for (int i = threadIdx.x; i < ALIGN_WARPS * E; i += ALIGN_THREADS) warp_hist[i] = 0;
+    __syncthreads();
+
+    // Segment of this warp: contiguous, multiple of 32 slots, in global index order.
+    const int64_t n_segments = (int64_t)n_ranks * ALIGN_WARPS;
+    int64_t seg_len = (a.numel + n_segments - 1) / n_segments;
+    seg_len = (seg_len + 31) / 32 * 32;
+    const int64_t seg_id = (int64_t)rank * ALIGN_WARPS + warp;
+    const int64_t seg_begin = seg_id * seg_len < a.numel ? seg_id * seg_len : a.numel;
+    const int64_t seg_end = seg_begin + seg_len < a.numel ? seg_begin + seg_len : a.numel;
+    const IdT* ids = reinterpret_cast<const IdT*>(a.topk_ids);
+    int32_t* my_hist = warp_hist + warp * E;
+
+    // Phase 1: per-warp histogram.
+    for (int64_t i0 = seg_begin; i0 < seg_end; i0 += 32) {
+        const int64_t i = i0 + lane;
+        int e = -1;
+        if (i < seg_end) {
+            const long long v = (long long)ids[i];
+            if (v >= 0 && v < E) e = (int)v;
+        }
+        const unsigned peers = __match_any_sync(0xffffffffu, e);
+        if (e >= 0 && lane == (__ffs(peers) - 1)) my_hist[e] += __popc(peers);
+        __syncwarp();
+    }
+    __syncthreads();
+
+    // Phase 2a: exclusive scan over the warps of this CTA, per expert.
+    for (int e = threadIdx.x; e < E; e += ALIGN_THREADS) {
+        int32_t run = 0;
+        for (int w = 0; w < ALIGN_WARPS; ++w) {
+            const int32_t t = warp_hist[w * E + e];
+            warp_hist[w * E + e] = run;
+            run += t;
+        }
+        cta_total[e] = run;
+    }
+    cluster.sync();
+
+    // Phase 2b: counts of the other CTAs through distributed shared memory.
+    // Each thread owns experts e = threadIdx.x + j*ALIGN_THREADS (E <= 1024 keeps j == 0).
+    int32_t before = 0, total = 0;
+    const int e0 = threadIdx.x;
+    if (e0 < E) {
+        for (int r = 0; r < n_ranks; ++r) {
+            const int32_t* peer = cluster.map_shared_rank(cta_total, r);
+            const int32_t c = peer[e0];
+            if (r < rank) before += c;
+            total += c;
+        }
+    }
+    cluster.sync();  // nobody may exit (or reuse cta_total) while peers still read it
+
+    // Phase 2c: exclusive scan of the padded counts over experts (every CTA does the same).
+    const int32_t bs = a.block_size;
+    const int32_t padded = e0 < E ? (total + bs - 1) / bs * bs : 0;
+    int32_t incl = padded;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+    }
+    if (lane == 31) scan_tmp[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        int32_t v = scan_tmp[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int32_t t = __shfl_up_sync(0xffffffffu, v, o);
+            if (lane >= o) v += t;
+        }
+        scan_tmp[lane] = v;
+        if (lane == 31) total_padded_s = v;
+    }
+    __syncthreads();
+    const int32_t offset = incl - padded + (warp > 0 ? scan_tmp[warp - 1] : 0);
+    if (e0 < E) {
+        base[e0] = offset + before;
+        pad_lo[e0] = offset + total;
+        pad_hi[e0] = offset + padded;
+    }
+    __syncthreads();
+    const int32_t total_padded = total_padded_s;
+
+    // Phase 2d: expert id of every block, padding slots, tail.  Work is spread over the ranks.
+    if (e0 < E && (e0 % n_ranks) == rank) {
+        int32_t id = e0;
+        if (a.expert_map) id = a.expert_map[e0 < a.expert_map_len ? e0 : a.expert_map_len - 1];
+        for (int32_t b = offset / bs; b < (offset + padded) / bs; ++b) a.expert_ids[b] = id;
+    }
+    const int32_t numel32 = (int32_t)a.numel;
+    for (int e = warp + rank * ALIGN_WARPS; e < E; e += ALIGN_WARPS * n_ranks)
+        for (int32_t p = pad_lo[e] + lane; p < pad_hi[e]; p += 32) a.sorted_ids[p] = numel32;
+    {
+        const int64_t gtid = (int64_t)rank * ALIGN_THREADS + threadIdx.x;
+        const int64_t gthreads = (int64_t)n_ranks * ALIGN_THREADS;
+        for (int64_t p = total_padded + gtid; p < a.max_pad; p += gthreads) a.sorted_ids[p] = numel32;
+        // Unused trailing blocks are -1; through an expert_map they become expert_map[-1],
+        // i.e. its last entry, as Python indexing of the reference does.
+        int32_t tail_id = -1;
+        if (a.expert_map && a.expert_map_len > 0) tail_id = a.expert_map[a.expert_map_len - 1];
+        for (int64_t b = total_padded / bs + gtid; b < a.n_blocks; b += gthreads) a.expert_ids[b] = tail_id;
+        if (gtid == 0) a.num_post_pad[0] = total_padded;
+    }
+
+    // Phase 3: ordered scatter.  warp_hist[warp][e] is the running rank inside this CTA.
+    for (int64_t i0 = seg_begin; i0 < seg_end; i0 += 32) {
+        const int64_t i = i0 + lane;
+        int e = -1;
+        if (i < seg_end) {
+            const long long v = (long long)ids[i];
+            if (v >= 0 && v < E) e = (int)v;
+        }
+        const unsigned peers = __match_any_sync(0xffffffffu, e);
+        const int leader = __ffs(peers) - 1;
+        int32_t cur = 0;
+        if (e >= 0 && lane == leader) {
+            cur = my_hist[e];
+            my_hist[e] = cur + __popc(peers);
+        }
+        cur = __shfl_sync(0xffffffffu, cur, leader);
+        if (e >= 0) {
+            const int32_t pos = base[e] + cur + __popc(peers & ((1u << lane) - 1u));
+            a.sorted_ids[pos] = (int32_t)i;
+        }
+        __syncwarp();
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) silu_and_mul_kernel(const T* __restrict__ x, const T* __restrict__ y,
+                                                           T* __restrict__ out, int64_t M, int64_t N, int64_t ld_x,
+                                                           int64_t ld_y, int64_t ld_o) {
+    const int64_t vec_per_row = N / 8;
+    const int64_t total = M * vec_per_row;
+    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = v / vec_per_row, c = (v % vec_per_row) * 8;
+        float a[8], b[8], o[8];
+        fg_load8(x + r * ld_x + c, a);
+        fg_load8(y + r * ld_y + c, b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = __fdividef(a[i], 1.0f + __expf(-a[i])) * b[i];
+        fg_store8(out + r * ld_o + c, o);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) moe_sum_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t M,
+                                                      int topk, int64_t K) {
+    const int64_t vec_per_row = K / 8;
+    const int64_t total = M * vec_per_row;
+    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = v / vec_per_row, c = (v % vec_per_row) * 8;
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int k = 0; k < topk; ++k) {
+            float t[8];
+            fg_load8(in + (r * topk + k) * K + c, t);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] += t[i];
+        }
+        fg_store8(out + r * K + c, acc);
+    }
+}
+
+unsigned grid_for(int64_t work_items, int per_block) {
+    int64_t b = fg_cdiv(work_items, per_block);
+    const int64_t cap = (int64_t)fg_num_sms() * 16;
+    if (b > cap) b = cap;
+    if (b < 1) b = 1;
+    return (unsigned)b;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fg_moe_align_block_size(const void* topk_ids, int ids_are_i64, int64_t numel, int num_experts, int block_size,
+                            const int32_t* expert_map, int expert_map_len, int32_t* sorted_ids, int64_t max_pad,
+                            int32_t* expert_ids, int64_t n_blocks, int32_t* num_post_pad, void* stream) {
+    FG_REQUIRE(numel >= 0 && num_experts > 0 && block_size > 0, FG_ERR_INVALID_ARGUMENT,
+               "numel %lld, num_experts %d, block_size %d", (long long)numel, num_experts, block_size);
+    FG_REQUIRE(num_experts <= ALIGN_THREADS, FG_ERR_UNSUPPORTED, "num_experts %d exceeds the supported maximum %d",
+               num_experts, ALIGN_THREADS);
+    FG_REQUIRE(numel + (int64_t)num_experts * block_size < (1ll << 31), FG_ERR_UNSUPPORTED, "numel too large");
+    FG_REQUIRE(max_pad >= numel + (int64_t)num_experts * (block_size - 1), FG_ERR_INVALID_ARGUMENT,
+               "sorted_ids holds %lld entries, needs at least numel + E*(block_size-1) = %lld", (long long)max_pad,
+               (long long)(numel + (int64_t)num_experts * (block_size - 1)));
+    FG_REQUIRE(n_blocks >= fg_cdiv(max_pad, block_size) || n_blocks >= max_pad / block_size, FG_ERR_INVALID_ARGUMENT,
+               "expert_ids holds %lld entries, needs %lld", (long long)n_blocks, (long long)(max_pad / block_size));
+    FG_REQUIRE(sorted_ids && expert_ids && num_post_pad && (topk_ids || numel == 0), FG_ERR_INVALID_ARGUMENT,
+               "null pointer");
+    FG_REQUIRE(expert_map == nullptr || expert_map_len >= num_experts, FG_ERR_INVALID_ARGUMENT,
+               "expert_map has %d entries for %d experts", expert_map_len, num_experts);
+
+    AlignArgs a{topk_ids, numel, num_experts, block_size, expert_map, expert_map_len,
+                sorted_ids, max_pad, expert_ids, n_blocks, num_post_pad};
+    // One CTA handles 32 warps x 128 slots comfortably; grow the cluster with numel up to 8.
+    int ranks = 1;
+    while (ranks < 8 && (int64_t)ranks * ALIGN_THREADS * 4 < numel) ranks *= 2;
+    const size_t smem = (size_t)(ALIGN_WARPS + 4) * num_experts * sizeof(int32_t);
+
+    auto kernel = ids_are_i64 ? moe_align_kernel<int64_t> : moe_align_kernel<int32_t>;
+    FG_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ranks, 1, 1);
+    cfg.blockDim = dim3(ALIGN_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ranks;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    FG_CUDA(cudaLaunchKernelEx(&cfg, kernel, a));
+    fg_count_launch(1);
+    return FG_OK;
+}
+
+int fg_silu_and_mul(const void* x, const void* y, void* out, int64_t M, int64_t N, int64_t ld_x, int64_t ld_y,
+                    int64_t ld_out, int dtype, void* stream) {
+    FG_REQUIRE(M >= 0 && N >= 0, FG_ERR_INVALID_ARGUMENT, "negative size");
+    if (M == 0 || N == 0) return FG_OK;
+    const int esz = dtype == FG_DTYPE_F32 ? 4 : 2;
+    FG_REQUIRE(N % 8 == 0 && (ld_x * esz) % 16 == 0 && (ld_y * esz) % 16 == 0 && (ld_out * esz) % 16 == 0 &&
+                   (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)out % 16 == 0,
+               FG_ERR_UNSUPPORTED, "silu_and_mul needs N %% 8 == 0 and 16-byte aligned rows");
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned grid = grid_for(M * (N / 8), 256);
+    switch (dtype) {
+        case FG_DTYPE_BF16:
+            silu_and_mul_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)y,
+                                                      (__nv_bfloat16*)out, M, N, ld_x, ld_y, ld_out);
+            break;
+        case FG_DTYPE_F16:
+            silu_and_mul_kernel<<<grid, 256, 0, st>>>((const __half*)x, (const __half*)y, (__half*)out, M, N, ld_x,
+                                                      ld_y, ld_out);
+            break;
+        case FG_DTYPE_F32:
+            silu_and_mul_kernel<<<grid, 256, 0, st>>>((const float*)x, (const float*)y, (float*)out, M, N, ld_x, ld_y,
+                                                      ld_out);
+            break;
+        default: fg_set_error("unsupported dtype code %d", dtype); return FG_ERR_INVALID_ARGUMENT;
+    }
+    fg_count_launch(1);
+    FG_LAUNCH_CHECK();
+    return FG_OK;
+}
+
+int fg_moe_sum(const void* in, void* out, int64_t M, int topk, int64_t K, int dtype, void* stream) {
+    FG_REQUIRE(M >= 0 && K >= 0 && topk >= 0, FG_ERR_INVALID_ARGUMENT, "negative size");
+    if (M == 0 || K == 0) return FG_OK;
+    FG_REQUIRE(K % 8 == 0 && (uintptr_t)in % 16 == 0 && (uintptr_t)out % 16 == 0, FG_ERR_UNSUPPORTED,
+               "moe_sum needs K %% 8 == 0 and 16-byte aligned buffers");
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned grid = grid_for(M * (K / 8), 256);
+    switch (dtype) {
+        case FG_DTYPE_BF16:
+            moe_sum_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, M, topk, K);
+            break;
+        case FG_DTYPE_F16: moe_sum_kernel<<<grid, 256, 0, st>>>((const __half*)in, (__half*)out, M, topk, K); break;
+        case FG_DTYPE_F32: moe_sum_kernel<<<grid, 256, 0, st>>>((const float*)in, (float*)out, M, topk, K); break;
+        default: fg_set_error("unsupported dtype code %d", dtype); return FG_ERR_INVALID_ARGUMENT;
+    }
+    fg_count_launch(1);
+    FG_LAUNCH_CHECK();
+    return FG_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,366 @@
+// FP8 e4m3 activation quantisation kernels (HBM-bound; sm_100a).
+//
+// Three scale rules share one set of kernels:
+//   QM_ACT    act_quant          s = max(amax,1e-4) * fp32(1/448), y = x * (1/s)
+//   QM_GROUP  per-token-group    s = max(amax,eps) / 448,          q = x / s
+//   QM_TOKEN  per-token (MoE)    s = max(max(amax,1e-10)/448, 1/(448*512)), q = x / s
+// The results are bit-exact with IEEE fp32 evaluation of those formulas: products use
+// __fmul_rn, the quotient x / s is a correctly rounded division built from one correctly
+// rounded reciprocal per group and two FMAs per element (Markstein's correction), with a
+// plain __fdiv_rn for the one family of divisors (all-ones significand) where that
+// shortcut is not proven.
+#include "common.cuh"
+
+namespace {
+
+enum { QM_ACT = 0, QM_GROUP = 1, QM_TOKEN = 2 };
+
+struct QuantArgs {
+    const void* x;
+    uint8_t* q;
+    float* s;
+    int64_t rows;  // output rows
+    int64_t K;
+    int group;
+    int64_t ld_x, ld_q;
+    int64_t s_row_stride, s_col_stride;
+    float eps;
+    int pow2;
+    const int32_t* row_index;  // nullable gather
+    int32_t index_div;
+    int32_t index_limit;
+    const int32_t* n_rows_dev;  // nullable
+};
+
+__device__ __forceinline__ float ceil_pow2_bits(float v) {
+    // 2^ceil(log2(v)) for positive normal v: bump the exponent when any mantissa bit is set.
+    uint32_t b = __float_as_uint(v);
+    uint32_t e = (b >> 23) & 0xffu;
+    uint32_t m = b & 0x7fffffu;
+    e += (m != 0u) ? 1u : 0u;
+    return __uint_as_float(e << 23);
+}
+
+template <int MODE>
+__device__ __forceinline__ float make_scale(float amax, float eps, int pow2) {
+    if constexpr (MODE == QM_ACT) {
+        amax = fmaxf(amax, __uint_as_float(0x38d1b717u));                  // 1e-4
+        float s = __fmul_rn(amax, __uint_as_float(0x3b124925u));           // fp32(1/448)
+        return pow2 ? ceil_pow2_bits(s) : s;
+    } else if constexpr (MODE == QM_GROUP) {
+        float s = __fdiv_rn(fmaxf(amax, eps), 448.0f);
+        if (pow2) s = ceil_pow2_bits(fmaxf(fabsf(s), __uint_as_float(0x2edbe6ffu)));  // floor 1e-10
+        return s;
+    } else {
+        float s = __fdiv_rn(fmaxf(amax, __uint_as_float(0x2edbe6ffu)), 448.0f);
+        return fmaxf(s, __uint_as_float(0x36924925u));                      // 1/(448*512)
+    }
+}
+
+// Per-group constants for turning x into x/s (or x*(1/s) for QM_ACT).
+struct Divider {
+    float s, r;
+    bool exact_div;
+};
+
+template <int MODE>
+__device__ __forceinline__ Divider make_divider(float s) {
+    Divider d;
+    d.s = s;
+    d.r = __fdiv_rn(1.0f, s);
+    d.exact_div = (MODE != QM_ACT) && ((__float_as_uint(s) & 0x7fffffu) == 0x7fffffu);
+    return d;
+}
+
+template <int MODE>
+__device__ __forceinline__ float apply_divider(float x, const Divider& d) {
+    if constexpr (MODE == QM_ACT) {
+        return __fmul_rn(x, d.r);
+    } else {
+        if (d.exact_div) return __fdiv_rn(x, d.s);
+        float q0 = __fmul_rn(x, d.r);
+        float rem = __fmaf_rn(-q0, d.s, x);
+        return __fmaf_rn(rem, d.r, q0);
+    }
+}
+
+__device__ __forceinline__ int64_t resolve_rows(const QuantArgs& a) {
+    int64_t rows = a.rows;
+    if (a.n_rows_dev) {
+        int64_t v = *a.n_rows_dev;
+        rows = v < rows ? v : rows;
+    }
+    return rows;
+}
+
+// Source row of output row r, or -1 for an all-zero (padding) row.
+__device__ __forceinline__ int64_t source_row(const QuantArgs& a, int64_t r) {
+    if (!a.row_index) return r;
+    int32_t idx = a.row_index[r];
+    return (idx >= 0 && idx < a.index_limit) ? (int64_t)(idx / a.index_div) : -1;
+}
+
+// ---- small groups: a team of TPG lanes owns one group of TPG*8*VPT elements -------------
+template <typename T, int MODE, int TPG, int VPT>
+__global__ void __launch_bounds__(256) group_quant_kernel(QuantArgs a) {
+    constexpr int UNROLL = 2;
+    constexpr int GROUP = TPG * 8 * VPT;
+    const int64_t rows = resolve_rows(a);
+    const int64_t gpr = a.K / GROUP;
+    const int64_t total = rows * gpr;
+    const int lane_in_team = threadIdx.x % TPG;
+    const int64_t team = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / TPG;
+    const int64_t teams = (int64_t)gridDim.x * blockDim.x / TPG;
+    const T* x = reinterpret_cast<const T*>(a.x);
+    // Loop bounds are uniform across the warp (first team of the warp decides).
+    const int64_t warp_first = team - (threadIdx.x % 32) / TPG;
+    for (int64_t base = 0; warp_first + base < total; base += teams * UNROLL) {
+        float v[UNROLL][VPT][8];
+        int64_t g[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            g[u] = team + base + (int64_t)u * teams;
+            const bool live = g[u] < total;
+            int64_t src = -1, cg = 0;
+            if (live) {
+                cg = g[u] % gpr;
+                src = source_row(a, g[u] / gpr);
+            }
+#pragma unroll
+            for (int w = 0; w < VPT; ++w) {
+                if (src >= 0) {
+                    fg_load8(x + src * a.ld_x + cg * GROUP + (w * TPG + lane_in_team) * 8, v[u][w]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[u][w][i] = 0.0f;
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            float amax = 0.0f;
+#pragma unroll
+            for (int w = 0; w < VPT; ++w)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[u][w][i]));
+#pragma unroll
+            for (int o = TPG / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            const float s = make_scale<MODE>(amax, a.eps, a.pow2);
+            const Divider d = make_divider<MODE>(s);
+            if (g[u] < total) {
+                const int64_t row = g[u] / gpr, cg = g[u] % gpr;
+#pragma unroll
+                for (int w = 0; w < VPT; ++w) {
+                    float q[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) q[i] = apply_divider<MODE>(v[u][w][i], d);
+                    *reinterpret_cast<uint2*>(a.q + row * a.ld_q + cg * GROUP + (w * TPG + lane_in_team) * 8) =
+                        fg_pack_e4m3x8(q);
+                }
+                if (lane_in_team == 0) a.s[row * a.s_row_stride + cg * a.s_col_stride] = s;
+            }
+        }
+    }
+}
+
+// ---- any group size (multiple of 8), one CTA per group: per-token rows, block_size = K ...
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256) row_quant_kernel(QuantArgs a) {
+    constexpr int MAXV = 8;  // vectors of 8 cached in registers per thread
+    const int64_t rows = resolve_rows(a);
+    const int64_t gpr = a.K / a.group;
+    const int64_t g = blockIdx.x;
+    const int64_t row = g / gpr, cg = g % gpr;
+    if (row >= rows) return;
+    const int64_t src = source_row(a, row);
+    const T* x = reinterpret_cast<const T*>(a.x) + (src >= 0 ? src : 0) * a.ld_x + cg * a.group;
+    uint8_t* q = a.q + row * a.ld_q + cg * a.group;
+    const int nvec = a.group / 8;
+    const bool cached = nvec <= MAXV * 256;
+
+    float v[MAXV][8];
+    float amax = 0.0f;
+    if (src >= 0) {
+        if (cached) {
+#pragma unroll
+            for (int j = 0; j < MAXV; ++j) {
+                const int iv = threadIdx.x + j * 256;
+                if (iv < nvec) {
+                    fg_load8(x + (int64_t)iv * 8, v[j]);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
+                }
+            }
+        } else {
+            for (int iv = threadIdx.x; iv < nvec; iv += 256) {
+                float t[8];
+                fg_load8(x + (int64_t)iv * 8, t);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(t[i]));
+            }
+        }
+    }
+    __shared__ float red[8];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
+
+    const float s = make_scale<MODE>(amax, a.eps, a.pow2);
+    const Divider d = make_divider<MODE>(s);
+    if (threadIdx.x == 0) a.s[row * a.s_row_stride + cg * a.s_col_stride] = s;
+
+    if (src < 0) {
+        for (int iv = threadIdx.x; iv < nvec; iv += 256) *reinterpret_cast<uint2*>(q + (int64_t)iv * 8) = make_uint2(0u, 0u);
+        return;
+    }
+    if (cached) {
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+            const int iv = threadIdx.x + j * 256;
+            if (iv < nvec) {
+                float o[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = apply_divider<MODE>(v[j][i], d);
+                *reinterpret_cast<uint2*>(q + (int64_t)iv * 8) = fg_pack_e4m3x8(o);
+            }
+        }
+    } else {
+        for (int iv = threadIdx.x; iv < nvec; iv += 256) {
+            float t[8], o[8];
+            fg_load8(x + (int64_t)iv * 8, t);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = apply_divider<MODE>(t[i], d);
+            *reinterpret_cast<uint2*>(q + (int64_t)iv * 8) = fg_pack_e4m3x8(o);
+        }
+    }
+}
+
+template <typename T, int MODE>
+int launch_quant_t(const QuantArgs& a, cudaStream_t st) {
+    if (a.rows == 0 || a.K == 0) return FG_OK;
+    const int64_t groups = a.rows * (a.K / a.group);
+    auto small = [&](auto kernel, int tpg) -> int {
+        const int64_t threads = groups * tpg;
+        int64_t blocks = fg_cdiv(threads, 256 * 2);
+        const int64_t cap = (int64_t)fg_num_sms() * 16;
+        if (blocks > cap) blocks = cap;
+        if (blocks < 1) blocks = 1;
+        kernel<<<(unsigned)blocks, 256, 0, st>>>(a);
+        fg_count_launch(1);
+        FG_LAUNCH_CHECK();
+        return FG_OK;
+    };
+    switch (a.group) {
+        case 64: return small(group_quant_kernel<T, MODE, 8, 1>, 8);
+        case 128: return small(group_quant_kernel<T, MODE, 16, 1>, 16);
+        case 256: return small(group_quant_kernel<T, MODE, 32, 1>, 32);
+        case 512: return small(group_quant_kernel<T, MODE, 32, 2>, 32);
+        default: break;
+    }
+    FG_REQUIRE(groups < (1ll << 31), FG_ERR_UNSUPPORTED, "too many groups (%lld) for one launch", (long long)groups);
+    row_quant_kernel<T, MODE><<<(unsigned)groups, 256, 0, st>>>(a);
+    fg_count_launch(1);
+    FG_LAUNCH_CHECK();
+    return FG_OK;
+}
+
+template <int MODE>
+int launch_quant(int dtype, const QuantArgs& a, cudaStream_t st) {
+    switch (dtype) {
+        case FG_DTYPE_BF16: return launch_quant_t<__nv_bfloat16, MODE>(a, st);
+        case FG_DTYPE_F16: return launch_quant_t<__half, MODE>(a, st);
+        case FG_DTYPE_F32: return launch_quant_t<float, MODE>(a, st);
+        default: fg_set_error("unsupported input dtype code %d", dtype); return FG_ERR_INVALID_ARGUMENT;
+    }
+}
+
+int check_common(const QuantArgs& a, int dtype) {
+    FG_REQUIRE(a.rows >= 0 && a.K >= 0, FG_ERR_INVALID_ARGUMENT, "negative size");
+    FG_REQUIRE(a.group > 0 && a.group % 8 == 0, FG_ERR_UNSUPPORTED, "group size %d must be a positive multiple of 8", a.group);
+    FG_REQUIRE(a.K % a.group == 0, FG_ERR_INVALID_ARGUMENT, "last dimension %lld must be divisible by the group size %d",
+               (long long)a.K, a.group);
+    if (a.rows == 0 || a.K == 0) return FG_OK;
+    FG_REQUIRE(a.x && a.q && a.s, FG_ERR_INVALID_ARGUMENT, "null pointer");
+    const int esz = dtype == FG_DTYPE_F32 ? 4 : 2;
+    FG_REQUIRE(((uintptr_t)a.x % 16 == 0) && ((a.ld_x * esz) % 16 == 0), FG_ERR_UNSUPPORTED,
+               "input rows must be 16-byte aligned (ptr %p, row stride %lld elements)", a.x, (long long)a.ld_x);
+    FG_REQUIRE(((uintptr_t)a.q % 8 == 0) && (a.ld_q % 8 == 0), FG_ERR_UNSUPPORTED,
+               "output rows must be 8-byte aligned (ptr %p, row stride %lld)", (void*)a.q, (long long)a.ld_q);
+    return FG_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fg_act_quant_bf16_e4m3(const void* x, void* y, float* s, int64_t M, int64_t N, int block, int64_t ld_x,
+                           int64_t ld_y, int64_t ld_s, int round_pow2, void* stream) {
+    QuantArgs a{};
+    a.x = x; a.q = (uint8_t*)y; a.s = s; a.rows = M; a.K = N; a.group = block;
+    a.ld_x = ld_x; a.ld_q = ld_y; a.s_row_stride = ld_s; a.s_col_stride = 1;
+    a.eps = 0.0f; a.pow2 = round_pow2 != 0;
+    int rc = check_common(a, FG_DTYPE_BF16);
+    if (rc != FG_OK) return rc;
+    return launch_quant<QM_ACT>(FG_DTYPE_BF16, a, (cudaStream_t)stream);
+}
+
+int fg_per_token_group_quant_fp8(const void* x, int x_dtype, void* q, float* s, int64_t M, int64_t K, int group,
+                                 int64_t ld_x, int64_t ld_q, int64_t s_row_stride, int64_t s_col_stride, float eps,
+                                 int ue8m0, void* stream) {
+    QuantArgs a{};
+    a.x = x; a.q = (uint8_t*)q; a.s = s; a.rows = M; a.K = K; a.group = group;
+    a.ld_x = ld_x; a.ld_q = ld_q; a.s_row_stride = s_row_stride; a.s_col_stride = s_col_stride;
+    a.eps = eps; a.pow2 = ue8m0 != 0;
+    int rc = check_common(a, x_dtype);
+    if (rc != FG_OK) return rc;
+    return launch_quant<QM_GROUP>(x_dtype, a, (cudaStream_t)stream);
+}
+
+int fg_per_token_group_quant_fp8_gather(const void* x, int x_dtype, void* q, float* s, int64_t M, int64_t K,
+                                        int group, int64_t ld_x, int64_t ld_q, const int32_t* row_index,
+                                        int32_t index_div, int32_t index_limit, const int32_t* n_rows_dev,
+                                        void* stream) {
+    QuantArgs a{};
+    a.x = x; a.q = (uint8_t*)q; a.s = s; a.rows = M; a.K = K; a.group = group;
+    a.ld_x = ld_x; a.ld_q = ld_q; a.s_row_stride = group > 0 ? K / group : 0; a.s_col_stride = 1;
+    a.eps = 1e-10f; a.pow2 = 0;
+    a.row_index = row_index; a.index_div = index_div; a.index_limit = index_limit; a.n_rows_dev = n_rows_dev;
+    FG_REQUIRE(row_index == nullptr || index_div > 0, FG_ERR_INVALID_ARGUMENT, "index_div must be positive");
+    int rc = check_common(a, x_dtype);
+    if (rc != FG_OK) return rc;
+    return launch_quant<QM_GROUP>(x_dtype, a, (cudaStream_t)stream);
+}
+
+int fg_per_token_quant_fp8(const void* x, int x_dtype, void* q, float* s, int64_t M, int64_t K, int64_t ld_x,
+                           int64_t ld_q, const int32_t* row_index, int32_t index_div, int32_t index_limit,
+                           const int32_t* n_rows_dev, void* stream) {
+    QuantArgs a{};
+    a.x = x; a.q = (uint8_t*)q; a.s = s; a.rows = M; a.K = K; a.group = (int)K;
+    a.ld_x = ld_x; a.ld_q = ld_q; a.s_row_stride = 1; a.s_col_stride = 1;
+    a.eps = 1e-10f; a.pow2 = 0;
+    a.row_index = row_index; a.index_div = index_div; a.index_limit = index_limit; a.n_rows_dev = n_rows_dev;
+    FG_REQUIRE(K < (1ll << 31), FG_ERR_UNSUPPORTED, "row length %lld too large", (long long)K);
+    FG_REQUIRE(row_index == nullptr || index_div > 0, FG_ERR_INVALID_ARGUMENT, "index_div must be positive");
+    if (K == 0) return FG_OK;
+    int rc = check_common(a, x_dtype);
+    if (rc != FG_OK) return rc;
+    // Row-sized groups always take the one-CTA-per-row kernel.
+    cudaStream_t st = (cudaStream_t)stream;
+    if (M == 0) return FG_OK;
+    FG_REQUIRE(M < (1ll << 31), FG_ERR_UNSUPPORTED, "too many rows");
+    switch (x_dtype) {
+        case FG_DTYPE_BF16: row_quant_kernel<__nv_bfloat16, QM_TOKEN><<<(unsigned)M, 256, 0, st>>>(a); break;
+        case FG_DTYPE_F16: row_quant_kernel<__half, QM_TOKEN><<<(unsigned)M, 256, 0, st>>>(a); break;
+        case FG_DTYPE_F32: row_quant_kernel<float, QM_TOKEN><<<(unsigned)M, 256, 0, st>>>(a); break;
+        default: fg_set_error("unsupported input dtype code %d", x_dtype); return FG_ERR_INVALID_ARGUMENT;
+    }
+    fg_count_launch(1);
+    FG_LAUNCH_CHECK();
+    return FG_OK;
+}
+
+}  // extern "C"

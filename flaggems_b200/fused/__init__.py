@@ -1,0 +1,12 @@
+from .act_quant import act_quant_triton  # noqa: F401
+from .cutlass_scaled_mm import cutlass_scaled_mm  # noqa: F401
+from .fused_moe import (  # noqa: F401
+    MoEActivation,
+    fused_experts_impl,
+    inplace_fused_experts,
+    moe_kernel_quantize_input,
+    outplace_fused_experts,
+)
+from .moe_align_block_size import moe_align_block_size, moe_align_block_size_triton  # noqa: F401
+from .moe_sum import moe_sum  # noqa: F401
+from .silu_and_mul import silu_and_mul, silu_and_mul_out  # noqa: F401

@@ -1,0 +1,271 @@
+"""Fused MoE layer on FP8 weights: quantise -> align -> grouped GEMM1 (+SiLU*up) ->
+quantise -> grouped GEMM2 (x router weight) -> top-k sum.
+
+Mirrors the FP8 path of src/flag_gems/fused/fused_moe.py of the reference:
+``fused_experts_impl`` (:1821-2185), ``inplace_fused_experts`` / ``outplace_fused_experts``
+(:2188-2290), ``_fp8_quantize`` / ``moe_kernel_quantize_input`` (:629-698, :749-773),
+``MoEActivation`` (:538-577).  The two grouped GEMMs are ``fg_moe_grouped_gemm_fp8``
+(tcgen05); rows are first gathered into expert-sorted padded order while they are
+quantised, so the GEMMs read their A operand with plain TMA boxes.
+
+Only the FP8 w8a8 modes are implemented (block 128x128, per-token x per-channel);
+the int8 / int4 / MX / bias / non-SiLU options of the reference signature raise
+NotImplementedError.
+"""
+import logging
+from enum import Enum
+from typing import Optional
+
+import torch
+
+from .. import _cabi
+from .moe_align_block_size import moe_align_block_size
+from .moe_sum import moe_sum
+from .silu_and_mul import silu_and_mul_out
+
+logger = logging.getLogger(__name__)
+
+# Rows per grouped-GEMM tile; moe_align_block_size is run with this block size inside
+# the layer (the public moe_align_block_size accepts any block size).
+_TILE_ROWS = 128
+_CHUNK_SIZE = 32 * 1024
+
+
+class MoEActivation(Enum):
+    SILU = "silu"
+    GELU = "gelu"
+    RELU2 = "relu2"
+    SWIGLUOAI = "swigluoai"
+    SWIGLUSTEP = "swiglustep"
+    SILU_NO_MUL = "silu_no_mul"
+    GELU_NO_MUL = "gelu_no_mul"
+    RELU2_NO_MUL = "relu2_no_mul"
+
+    @property
+    def is_gated(self) -> bool:
+        return not self.value.endswith("_no_mul")
+
+    @classmethod
+    def from_str(cls, s: str) -> "MoEActivation":
+        for member in cls:
+            if member.value == s:
+                return member
+        valid = [m.value for m in cls]
+        raise ValueError(f"Unknown MoE activation: {s!r}. Valid activations: {valid}")
+
+    @staticmethod
+    def adjust_N_for_activation(N: int, activation: "MoEActivation") -> int:
+        return N if not activation.is_gated else N // 2
+
+
+def _per_token_quant(x, row_index=None, index_div=1, index_limit=0, n_rows_dev=None, out_rows=None):
+    """Dynamic per-row FP8 quantisation (reference: fused_moe.py:673-684), optionally
+    gathering rows through ``row_index``."""
+    k = x.shape[-1]
+    x2 = x.reshape(-1, k)
+    rows = x2.shape[0] if out_rows is None else out_rows
+    q = torch.empty((rows, k), dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty((rows, 1), dtype=torch.float32, device=x.device)
+    if rows and k:
+        _cabi.check(
+            _cabi.lib().fg_per_token_quant_fp8(
+                _cabi.ptr(x2), _cabi.DTYPE_CODE[x.dtype], _cabi.ptr(q), _cabi.ptr(s), rows, k,
+                x2.stride(0), k, _cabi.ptr(row_index), index_div, index_limit, _cabi.ptr(n_rows_dev),
+                _cabi.stream_ptr(x.device),
+            )
+        )
+    return q, s
+
+
+def _group_quant(x, group, row_index=None, index_div=1, index_limit=0, n_rows_dev=None, out_rows=None):
+    """Per-token-group FP8 quantisation (reference: fused_moe.py:647-659), optionally
+    gathering rows through ``row_index``."""
+    k = x.shape[-1]
+    x2 = x.reshape(-1, k)
+    rows = x2.shape[0] if out_rows is None else out_rows
+    q = torch.empty((rows, k), dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty((rows, k // group), dtype=torch.float32, device=x.device)
+    if rows and k:
+        _cabi.check(
+            _cabi.lib().fg_per_token_group_quant_fp8_gather(
+                _cabi.ptr(x2), _cabi.DTYPE_CODE[x.dtype], _cabi.ptr(q), _cabi.ptr(s), rows, k, group,
+                x2.stride(0), k, _cabi.ptr(row_index), index_div, index_limit, _cabi.ptr(n_rows_dev),
+                _cabi.stream_ptr(x.device),
+            )
+        )
+    return q, s
+
+
+def _fp8_quantize(A, A_scale, per_act_token, block_shape=None):
+    """FP8 e4m3 quantisation of MoE activations: block-wise or per-token
+    (reference: fused_moe.py:629-698).  The per-tensor branches are not implemented."""
+    _cabi.require_cuda(A)
+    with torch.cuda.device(A.device):
+        if block_shape is not None:
+            assert not per_act_token
+            assert len(block_shape) == 2
+            block_k = block_shape[1]
+            assert A.size(-1) % block_k == 0
+            q, s = _group_quant(A, block_k)
+            return q.reshape(A.shape), s.reshape(A.shape[:-1] + (A.size(-1) // block_k,))
+        if per_act_token:
+            q, s = _per_token_quant(A)
+            return q.reshape(A.shape), s.reshape(A.shape[:-1] + (1,))
+    raise NotImplementedError("per-tensor FP8 activation quantisation is not implemented")
+
+
+def moe_kernel_quantize_input(A, A_scale, quant_dtype, per_act_token_quant, block_shape=None, ocp_mx_scheme=None):
+    """Quantise MoE input activations before a GEMM (reference: fused_moe.py:749-773)."""
+    if ocp_mx_scheme is not None:
+        raise NotImplementedError("OCP MX schemes are not implemented")
+    if quant_dtype is None:
+        return A, A_scale
+    if quant_dtype == torch.float8_e4m3fn:
+        return _fp8_quantize(A, A_scale, per_act_token_quant, block_shape)
+    raise NotImplementedError(f"quant dtype {quant_dtype} is not implemented")
+
+
+def _grouped_gemm(c, a, w, a_scale, w_scale, topk_weights, sorted_ids, expert_ids, num_post_pad, numel,
+                  scale_mode, fuse_silu, scatter, mul_weight):
+    e, n, k = w.shape
+    c = c.view(-1, c.shape[-1])
+    _cabi.check(
+        _cabi.lib().fg_moe_grouped_gemm_fp8(
+            _cabi.ptr(c), _cabi.ptr(a), _cabi.ptr(w), _cabi.ptr(a_scale), _cabi.ptr(w_scale),
+            _cabi.ptr(topk_weights), _cabi.DTYPE_CODE.get(topk_weights.dtype, -1) if topk_weights is not None else 0,
+            _cabi.ptr(sorted_ids), _cabi.ptr(expert_ids), _cabi.ptr(num_post_pad),
+            a.shape[0], numel, e, n, k, a.stride(0), c.stride(0), _TILE_ROWS, scale_mode, 1,
+            1 if fuse_silu else 0, 1 if scatter else 0, 1 if mul_weight else 0,
+            _cabi.DTYPE_CODE[c.dtype], _cabi.stream_ptr(a.device),
+        )
+    )
+
+
+def fused_experts_impl(
+    hidden_states: torch.Tensor,
+    w1: torch.Tensor,
+    w2: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    inplace: bool = False,
+    activation: str = "silu",
+    apply_router_weight_on_input: bool = False,
+    use_fp8_w8a8: bool = False,
+    use_int8_w8a8: bool = False,
+    use_int8_w8a16: bool = False,
+    use_int4_w4a16: bool = False,
+    ocp_mx_scheme: Optional[str] = None,
+    per_channel_quant: bool = False,
+    global_num_experts: int = -1,
+    expert_map: Optional[torch.Tensor] = None,
+    w1_scale: Optional[torch.Tensor] = None,
+    w2_scale: Optional[torch.Tensor] = None,
+    w1_zp: Optional[torch.Tensor] = None,
+    w2_zp: Optional[torch.Tensor] = None,
+    a1_scale: Optional[torch.Tensor] = None,
+    a2_scale: Optional[torch.Tensor] = None,
+    block_shape: Optional[list] = None,
+    w1_bias: Optional[torch.Tensor] = None,
+    w2_bias: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    logger.debug("GEMS FUSED MOE")
+    assert activation == "silu", f"Only 'silu' activation is supported, got {activation}"
+    MoEActivation.from_str(activation)
+    if use_int8_w8a8 or use_int8_w8a16 or use_int4_w4a16 or ocp_mx_scheme is not None:
+        raise NotImplementedError("only the FP8 w8a8 modes of fused_experts_impl are implemented")
+    if not use_fp8_w8a8:
+        raise NotImplementedError("unquantised (bf16/fp16) expert weights are not implemented; pass use_fp8_w8a8=True")
+    if w1_zp is not None or w2_zp is not None or w1_bias is not None or w2_bias is not None:
+        raise NotImplementedError("zero points and expert biases are not implemented")
+    if apply_router_weight_on_input:
+        raise NotImplementedError("apply_router_weight_on_input is not implemented")
+    if block_shape is None and not per_channel_quant:
+        raise NotImplementedError("per-tensor FP8 scales are not implemented; use per_channel_quant or block_shape")
+    if a1_scale is not None or a2_scale is not None:
+        raise NotImplementedError("static activation scales are not implemented (dynamic quantisation only)")
+
+    assert hidden_states.size(1) == w1.size(2), f"Hidden size mismatch {hidden_states.size(1)} != {w1.size(2)}"
+    assert topk_weights.size() == topk_ids.size(), "topk shape mismatch"
+    assert hidden_states.is_contiguous(), "Hidden_states must be contiguous"
+    assert w1.stride(-1) == 1, "Stride of last dimension must be 1"
+    assert w2.stride(-1) == 1, "Stride of last dimension must be 1"
+    assert hidden_states.dtype in [torch.float32, torch.float16, torch.bfloat16]
+    assert w1_scale is not None and w2_scale is not None, "FP8 weights need w1_scale and w2_scale"
+    assert w1.is_contiguous() and w2.is_contiguous(), "expert weights must be contiguous"
+    assert topk_weights.stride(1) == 1
+    _cabi.require_cuda(hidden_states, w1, w2, topk_weights, topk_ids, w1_scale, w2_scale, expert_map)
+    if w1.dtype != torch.float8_e4m3fn or w2.dtype != torch.float8_e4m3fn:
+        raise NotImplementedError("expert weights must be float8_e4m3fn")
+
+    num_tokens, hidden = hidden_states.shape
+    e, n, _ = w1.shape
+    k_out = w2.size(1)
+    inter = n // 2
+    assert w2.size(2) == inter, "w2 inner size must be half of w1's output size"
+    if global_num_experts == -1:
+        global_num_experts = e
+    top_k = topk_ids.size(1)
+    dtype = hidden_states.dtype
+
+    if block_shape is not None:
+        assert len(block_shape) == 2
+        if list(block_shape) != [128, 128]:
+            raise NotImplementedError(f"block_shape {block_shape}: only [128, 128] is implemented")
+        assert hidden % 128 == 0 and inter % 128 == 0, "block-FP8 needs hidden and intermediate sizes divisible by 128"
+        scale_mode = _cabi.SCALE_BLOCK
+        w1s = w1_scale.float().contiguous()
+        w2s = w2_scale.float().contiguous()
+        assert w1s.shape == (e, (n + 127) // 128, hidden // 128), f"w1_scale shape {tuple(w1s.shape)}"
+        assert w2s.shape == (e, (k_out + 127) // 128, inter // 128), f"w2_scale shape {tuple(w2s.shape)}"
+    else:
+        scale_mode = _cabi.SCALE_VECTOR
+        w1s = w1_scale.float().reshape(e, -1).contiguous()
+        w2s = w2_scale.float().reshape(e, -1).contiguous()
+        assert w1s.shape == (e, n) and w2s.shape == (e, k_out), "per-channel scales must be [E, N]"
+
+    out = hidden_states if inplace else torch.empty_like(hidden_states)
+    if num_tokens == 0:
+        return out
+    tw = topk_weights if topk_weights.dtype in _cabi.DTYPE_CODE else topk_weights.float()
+    tw = tw.contiguous()
+
+    with torch.cuda.device(hidden_states.device):
+        for begin in range(0, num_tokens, _CHUNK_SIZE):
+            end = min(begin + _CHUNK_SIZE, num_tokens)
+            h = hidden_states[begin:end]
+            ids = topk_ids[begin:end]
+            w = tw[begin:end].reshape(-1)
+            t = end - begin
+            numel = t * top_k
+
+            sorted_ids, expert_ids, post_pad = moe_align_block_size(ids, _TILE_ROWS, global_num_experts, expert_map)
+            rows = sorted_ids.numel() // _TILE_ROWS * _TILE_ROWS
+
+            if scale_mode == _cabi.SCALE_BLOCK:
+                a1, a1s = _group_quant(h, 128, sorted_ids, top_k, numel, post_pad, rows)
+            else:
+                a1, a1s = _per_token_quant(h, sorted_ids, top_k, numel, post_pad, rows)
+            act = torch.empty((rows, inter), dtype=dtype, device=h.device)
+            _grouped_gemm(act, a1, w1, a1s, w1s, None, sorted_ids, expert_ids, post_pad, numel,
+                          scale_mode, fuse_silu=True, scatter=False, mul_weight=False)
+            if scale_mode == _cabi.SCALE_BLOCK:
+                a2, a2s = _group_quant(act, 128, None, 1, 0, post_pad, rows)
+            else:
+                a2, a2s = _per_token_quant(act, None, 1, 0, post_pad, rows)
+            routed = torch.empty((t, top_k, k_out), dtype=dtype, device=h.device)
+            _grouped_gemm(routed, a2, w2, a2s, w2s, w, sorted_ids, expert_ids, post_pad, numel,
+                          scale_mode, fuse_silu=False, scatter=True, mul_weight=True)
+            moe_sum(routed, out[begin:end])
+    return out
+
+
+def inplace_fused_experts(hidden_states, w1, w2, topk_weights, topk_ids, **kwargs) -> None:
+    """Same semantics as ``fused_experts_impl(..., inplace=True)`` (reference :2188-2238)."""
+    kwargs.pop("inplace", None)
+    fused_experts_impl(hidden_states, w1, w2, topk_weights, topk_ids, inplace=True, **kwargs)
+
+
+def outplace_fused_experts(hidden_states, w1, w2, topk_weights, topk_ids, **kwargs) -> torch.Tensor:
+    """Same semantics as ``fused_experts_impl(..., inplace=False)`` (reference :2241-2290)."""
+    kwargs.pop("inplace", None)
+    return fused_experts_impl(hidden_states, w1, w2, topk_weights, topk_ids, inplace=False, **kwargs)

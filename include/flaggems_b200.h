@@ -1,0 +1,165 @@
+/*
+ * flaggems_b200 — C ABI of the B200 (sm_100a) FP8 quantized-inference kernels.
+ *
+ * Every entry point takes raw device pointers, explicit sizes and strides
+ * (strides in ELEMENTS unless a name says bytes) and the CUDA stream to launch
+ * on (a cudaStream_t passed as void*; NULL = legacy default stream).  Nothing is
+ * allocated inside unless stated, nothing is retained after return, and there is
+ * no host synchronisation.  Return value: FG_OK or a negative FG_ERR_* code;
+ * fg_last_error() gives the text for the calling thread.
+ *
+ * Each declaration names the function of the reference (FlagGems, paths relative
+ * to its repository root) whose device work it replaces.
+ */
+#ifndef FLAGGEMS_B200_H
+#define FLAGGEMS_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FG_OK 0
+#define FG_ERR_INVALID_ARGUMENT (-1)
+#define FG_ERR_UNSUPPORTED (-2)
+#define FG_ERR_CUDA (-3)
+#define FG_ERR_DEVICE_STATUS (-4)
+
+/* element type codes */
+#define FG_DTYPE_BF16 0
+#define FG_DTYPE_F16 1
+#define FG_DTYPE_F32 2
+
+/* scale layout codes of fg_scaled_mm_fp8 / fg_moe_grouped_gemm_fp8 */
+#define FG_SCALE_SCALAR 0 /* one fp32 value                        */
+#define FG_SCALE_VECTOR 1 /* one value per row of A / column of C  */
+#define FG_SCALE_BLOCK 2  /* 1x128 groups of A, 128x128 blocks of B */
+
+int fg_version(void);
+const char* fg_last_error(void);
+
+/* Reads and clears the device-side status word of the current device (this call
+ * synchronises the device).  *status is 0 when no kernel reported a bounded wait
+ * that ran out.  Returns FG_OK, or FG_ERR_DEVICE_STATUS when *status != 0. */
+int fg_device_status(unsigned int* status);
+
+/* Number of kernel launches issued by this library in the calling process. */
+uint64_t fg_launch_count(void);
+
+/* ---- activation quantisation --------------------------------------------- */
+
+/* act_quant_triton: src/flag_gems/fused/act_quant.py:111-174 (kernel :45-108).
+ * x bf16 [M,N] (row stride ld_x), y e4m3 [M,N], s fp32 [M, N/block] (row stride
+ * ld_s).  amax clamped to 1e-4, s = amax * fp32(1/448), round_pow2 != 0 rounds s
+ * up to a power of two by the exponent/mantissa test (:22-41), y = x * (1/s). */
+int fg_act_quant_bf16_e4m3(const void* x, void* y, float* s, int64_t M, int64_t N, int block,
+                           int64_t ld_x, int64_t ld_y, int64_t ld_s, int round_pow2, void* stream);
+
+/* per_token_group_quant_fp8: src/flag_gems/ops/per_token_group_quant_fp8.py:227-336
+ * (kernels :34-216).  x [M,K] of x_dtype, q e4m3 [M,K] (row stride ld_q),
+ * s[m*s_row_stride + g*s_col_stride] fp32 (any layout, column-major included).
+ * s = max(amax, eps) / 448 (IEEE divide), ue8m0 != 0: s = 2^ceil(log2(max(|s|,1e-10))),
+ * q = x / s. */
+int fg_per_token_group_quant_fp8(const void* x, int x_dtype, void* q, float* s, int64_t M, int64_t K,
+                                 int group, int64_t ld_x, int64_t ld_q, int64_t s_row_stride,
+                                 int64_t s_col_stride, float eps, int ue8m0, void* stream);
+
+/* Per-token branch of _fp8_quantize: src/flag_gems/fused/fused_moe.py:673-684.
+ * s[m] = max(max(rowamax,1e-10)/448, 1/(448*512)), q = x / s.
+ * row_index (nullable): when given, output row r reads input row row_index[r] / index_div
+ * if row_index[r] < index_limit and is written as zeros otherwise (the gather of routed
+ * rows into expert-sorted order); n_rows_dev (nullable) is a device int giving how many
+ * output rows to produce (at most M). */
+int fg_per_token_quant_fp8(const void* x, int x_dtype, void* q, float* s, int64_t M, int64_t K,
+                           int64_t ld_x, int64_t ld_q, const int32_t* row_index, int32_t index_div,
+                           int32_t index_limit, const int32_t* n_rows_dev, void* stream);
+
+/* Same gather options for the per-group form (used by the block-FP8 MoE path;
+ * src/flag_gems/fused/fused_moe.py:647-659 feeding :2016-2023). Scales are written
+ * row-major [M, K/group]. */
+int fg_per_token_group_quant_fp8_gather(const void* x, int x_dtype, void* q, float* s, int64_t M,
+                                        int64_t K, int group, int64_t ld_x, int64_t ld_q,
+                                        const int32_t* row_index, int32_t index_div,
+                                        int32_t index_limit, const int32_t* n_rows_dev,
+                                        void* stream);
+
+/* ---- fused-MoE glue -------------------------------------------------------- */
+
+/* moe_align_block_size / moe_align_block_size_triton:
+ * src/flag_gems/fused/moe_align_block_size.py:789-820, :520-664 (stages :404-517).
+ * topk_ids: numel route slots, int32 (ids_are_i64 == 0) or int64.  Writes
+ * sorted_ids[max_pad] (route indices grouped by expert, ascending inside an expert,
+ * each expert padded to block_size with the value numel), expert_ids[n_blocks]
+ * (-1 past the used blocks) and num_post_pad[0].  expert_map (nullable, length
+ * expert_map_len): every expert_ids entry v becomes expert_map[v] with Python
+ * index semantics for v == -1 (:817-818). */
+int fg_moe_align_block_size(const void* topk_ids, int ids_are_i64, int64_t numel, int num_experts,
+                            int block_size, const int32_t* expert_map, int expert_map_len,
+                            int32_t* sorted_ids, int64_t max_pad, int32_t* expert_ids,
+                            int64_t n_blocks, int32_t* num_post_pad, void* stream);
+
+/* silu_and_mul_out / _silu_and_mul_kernel: src/flag_gems/fused/silu_and_mul.py:26-31,66-69,
+ * src/flag_gems/fused/fused_moe.py:795-800.  out = dtype(x32/(1+exp(-x32)) * y32). */
+int fg_silu_and_mul(const void* x, const void* y, void* out, int64_t M, int64_t N, int64_t ld_x,
+                    int64_t ld_y, int64_t ld_out, int dtype, void* stream);
+
+/* moe_sum: src/flag_gems/fused/moe_sum.py:70-90 (kernel :24-67).
+ * in [M, topk, K] contiguous, out [M, K]; fp32 sum in slot order. */
+int fg_moe_sum(const void* in, void* out, int64_t M, int topk, int64_t K, int dtype, void* stream);
+
+/* ---- scaled FP8 matrix products (tcgen05 / TMEM / TMA) ---------------------- */
+
+/* cutlass_scaled_mm (scalar / per-token / per-channel scales):
+ * src/flag_gems/fused/cutlass_scaled_mm.py:475-526, dispatch :371-431, kernel :207-314;
+ * aten _scaled_mm: src/flag_gems/ops/scaled_mm.py:333-452 (bias_after_round = 0).
+ * a e4m3 [M,K] row-major (ld_a), b e4m3 given as its [N,K] K-contiguous storage
+ * (ld_b = elements between consecutive n, i.e. b.stride(1) of the column-major
+ * [K,N] view), c [M,N] of out_dtype (ld_c).  c = out(sb[n] * (sa[m] * acc)) then
+ * + bias in the output type (bias_after_round != 0) or + bias in fp32 before the
+ * cast.  sa_mode/sb_mode: FG_SCALE_SCALAR or FG_SCALE_VECTOR.  K % 16 == 0. */
+int fg_scaled_mm_fp8(void* c, const void* a, const void* b, const float* sa, const float* sb,
+                     const void* bias, int64_t M, int64_t N, int64_t K, int64_t ld_a, int64_t ld_b,
+                     int64_t ld_c, int sa_mode, int sb_mode, int out_dtype, int bias_after_round,
+                     void* stream);
+
+/* w8a8_block_fp8_matmul / fp8_matmul / blockwise cutlass_scaled_mm:
+ * src/flag_gems/ops/w8a8_block_fp8_matmul.py:173-232 (kernel :51-122),
+ * src/flag_gems/ops/fp8_matmul.py:137-205,
+ * src/flag_gems/fused/cutlass_scaled_mm.py:153-194.
+ * a e4m3 [M,K], b e4m3 [N,K]; a_s fp32 [M, ceil(K/128)] (row stride ld_as);
+ * b_s[nb*bs_stride_n + kb*bs_stride_k] fp32; block sizes fixed at 128x128.
+ * C[m,n] = out(sum_kb (A_kb . B_kb) * a_s[m,kb] * b_s[n/128,kb]). */
+int fg_block_scaled_mm_fp8(void* c, const void* a, const void* b, const float* a_s,
+                           const float* b_s, int64_t M, int64_t N, int64_t K, int64_t ld_a,
+                           int64_t ld_b, int64_t ld_c, int64_t ld_as, int64_t bs_stride_n,
+                           int64_t bs_stride_k, int out_dtype, void* stream);
+
+/* Grouped expert GEMM of the fused MoE layer: fused_moe_kernel /
+ * invoke_fused_moe_triton_kernel / dispatch_fused_moe_kernel,
+ * src/flag_gems/fused/fused_moe.py:1015-1509, :1602-1727, :1730-1818.
+ *
+ * a: e4m3 [rows, K] already in expert-sorted padded order (row r belongs to route
+ * slot sorted_ids[r]); w: e4m3 [E, N, K]; block b of block_rows sorted rows uses
+ * expert expert_ids[b] (blocks with -1 produce zeros, :1350-1364); only rows below
+ * num_post_pad[0] are processed.  scale_mode: FG_SCALE_SCALAR (per-tensor: a_scale[0]
+ * or per-row when a_scale_per_row, w_scale[e]), FG_SCALE_VECTOR (a_scale[r] per
+ * sorted row, w_scale[e*N + n]) or FG_SCALE_BLOCK (a_scale [rows, K/128],
+ * w_scale [E, ceil(N/128), K/128]).
+ * fuse_silu != 0: N = 2*I, output c[r, 0:I] = silu(gate) * up in sorted order
+ * (FUSE_SILU branch :1186-1347); else c gets N columns.
+ * scatter != 0: row r is written to c row sorted_ids[r] (skipped when
+ * sorted_ids[r] >= numel) instead of row r; mul_weight != 0 multiplies by
+ * topk_weights[sorted_ids[r]] in fp32 before the cast (:1485-1493). */
+int fg_moe_grouped_gemm_fp8(void* c, const void* a, const void* w, const float* a_scale,
+                            const float* w_scale, const void* topk_weights, int topk_w_dtype,
+                            const int32_t* sorted_ids, const int32_t* expert_ids,
+                            const int32_t* num_post_pad, int64_t max_rows, int64_t numel,
+                            int num_experts, int64_t N, int64_t K, int64_t ld_a, int64_t ld_c,
+                            int block_rows, int scale_mode, int a_scale_per_row, int fuse_silu,
+                            int scatter, int mul_weight, int out_dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLAGGEMS_B200_H */

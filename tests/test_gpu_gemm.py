@@ -1,0 +1,218 @@
+"""GPU parity: scaled FP8 GEMMs (tcgen05) vs the CPU fp32 oracle, rtol/atol 1e-2."""
+import os
+
+import pytest
+import torch
+
+import flag_gems
+import oracle
+from flaggems_b200 import _cabi
+
+pytestmark = pytest.mark.gpu
+FP8 = torch.float8_e4m3fn
+TOL = dict(rtol=1e-2, atol=1e-2)
+
+
+def _close(got, want, **tol):
+    tol = tol or TOL
+    torch.testing.assert_close(got.cpu().float(), want.float(), **tol)
+
+
+def _llama_like(m, n, k, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    w = torch.randn(n, k, generator=g) * 0.02
+    wq, sw = oracle.quantize_weight_per_channel(w)
+    aq, sa = oracle.per_token_quant_fp8(a)
+    return aq, sa, wq, sw, g
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 256, 128), (16, 512, 4096), (128, 4096, 4096), (256, 4096, 4096),
+                                   (1024, 6144, 4096), (33, 200, 496), (83, 7752, 3888), (129, 136, 144),
+                                   (512, 4096, 14336)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_cutlass_scaled_mm_per_token_per_channel(m, n, k, bias):
+    aq, sa, wq, sw, g = _llama_like(m, n, k)
+    b = torch.randn(n, generator=g).bfloat16() if bias else None
+    c = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    wq_c = wq.cuda()
+    flag_gems.cutlass_scaled_mm(c, aq.cuda(), wq_c.t(), sa.cuda().view(-1), sw.cuda(),
+                                None if b is None else b.cuda())
+    ref = oracle.scaled_mm(aq, wq.t(), sa, sw, b)
+    _close(c, ref)
+
+
+@pytest.mark.parametrize("pa,pb", [(False, False), (True, False), (False, True)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16])
+def test_cutlass_scaled_mm_scale_kinds(pa, pb, out_dtype):
+    m, n, k = 192, 384, 512
+    g = torch.Generator().manual_seed(1)
+    a = torch.randn(m, k, generator=g).clamp(-448, 448).to(FP8)
+    w = torch.randn(n, k, generator=g).clamp(-448, 448).to(FP8)
+    sa = torch.rand(m if pa else 1, generator=g) * 0.02 + 0.01
+    sb = torch.rand(n if pb else 1, generator=g) * 0.02 + 0.01
+    c = torch.empty(m, n, dtype=out_dtype, device="cuda")
+    flag_gems.cutlass_scaled_mm(c, a.cuda(), w.cuda().t(), sa.cuda(), sb.cuda())
+    _close(c, oracle.scaled_mm(a, w.t(), sa, sb, None, out_dtype))
+
+
+def test_cutlass_scaled_mm_baseline_config0():
+    """configs[0]: act_quant(A[256,4096], block=K) feeding W[4096,4096] per-channel."""
+    g = torch.Generator().manual_seed(0)
+    a = torch.randn(256, 4096, generator=g).bfloat16()
+    w = torch.randn(4096, 4096, generator=g) * 0.02
+    wq, sw = oracle.quantize_weight_per_channel(w)
+    aq, sa = flag_gems.act_quant_triton(a.cuda(), 4096)
+    aq_r, sa_r = oracle.act_quant(a, 4096)
+    assert torch.equal(aq.cpu().view(torch.uint8), aq_r.view(torch.uint8))
+    c = torch.empty(256, 4096, dtype=torch.bfloat16, device="cuda")
+    flag_gems.cutlass_scaled_mm(c, aq, wq.cuda().t(), sa.view(-1), sw.cuda(), None)
+    _close(c, oracle.scaled_mm(aq_r, wq.t(), sa_r, sw))
+
+
+def test_scaled_mm_golden_fixtures(golden_dir):
+    for c in torch.load(os.path.join(golden_dir, "scaled_mm.pt")):
+        a = c["a"].view(FP8)
+        w = c["b_nk"].view(FP8)
+        m, n = a.shape[0], w.shape[0]
+        out = torch.empty(m, n, dtype=torch.float32, device="cuda")
+        flag_gems.cutlass_scaled_mm(out, a.cuda(), w.cuda().t(), c["sa"].reshape(-1).cuda(),
+                                    c["sb"].reshape(-1).cuda())
+        ref = c["c_f32_nobias"]
+        _close(out, ref, rtol=1e-3, atol=1e-3 * float(ref.abs().max()))
+
+
+def test_scaled_mm_asserts():
+    a = torch.zeros(16, 128, dtype=FP8, device="cuda")
+    w = torch.zeros(32, 128, dtype=FP8, device="cuda")
+    s = torch.ones(1, device="cuda")
+    c = torch.empty(16, 32, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(AssertionError):
+        flag_gems.cutlass_scaled_mm(c, a, w.t().contiguous(), s, s)  # b not column-major
+    with pytest.raises(AssertionError):
+        flag_gems.cutlass_scaled_mm(c, a, torch.zeros(64, 32, dtype=FP8, device="cuda").t().t(), s, s)
+    with pytest.raises(AssertionError):
+        flag_gems.cutlass_scaled_mm(c, a, w.t(), s.double(), s)
+
+
+@pytest.mark.parametrize("m,n,k", [(16, 16, 16), (17, 31, 32), (64, 48, 80)])
+@pytest.mark.parametrize("mode", ["scalar", "rowwise_1d", "rowwise_2d"])
+@pytest.mark.parametrize("out_dtype,use_bias", [(torch.bfloat16, False), (torch.float16, True), (torch.float32, True)])
+def test_aten_scaled_mm(m, n, k, mode, out_dtype, use_bias):
+    """Shapes, scale modes and tolerance of tests/test_scaled_mm.py:144 (fp8 rows)."""
+    g = torch.Generator().manual_seed(2)
+    mat1 = (torch.randn(m, k, generator=g) * 0.25).to(FP8)
+    mat2 = (torch.randn(k, n, generator=g) * 0.25).to(FP8)
+    if mode == "scalar":
+        sa, sb = torch.tensor([0.75]), torch.tensor([1.25])
+    else:
+        sa, sb = torch.linspace(0.75, 1.25, m), torch.linspace(1.25, 0.75, n)
+        if mode == "rowwise_2d":
+            sa, sb = sa.reshape(m, 1), sb.reshape(1, n)
+    bias = (torch.randn(n, generator=g) * 0.25).to(out_dtype) if use_bias else None
+    ref = oracle.scaled_mm(mat1, mat2, sa, sb, bias, out_dtype, bias_after_round=False)
+    with flag_gems.use_gems():
+        res = torch._scaled_mm(mat1.cuda(), mat2.cuda(), sa.cuda(), sb.cuda(),
+                               bias=None if bias is None else bias.cuda(),
+                               scale_result=torch.tensor([2.0], device="cuda"),
+                               out_dtype=out_dtype, use_fast_accum=True)
+    assert res.dtype == out_dtype
+    _close(res, ref)
+    out = torch.empty(m, n, dtype=out_dtype, device="cuda")
+    with flag_gems.use_gems():
+        ret = torch.ops.aten._scaled_mm.out(mat1.cuda(), mat2.cuda(), sa.cuda(), sb.cuda(),
+                                            bias=None if bias is None else bias.cuda(), out_dtype=out_dtype,
+                                            out=out)
+    assert ret.data_ptr() == out.data_ptr()
+    _close(out, ref)
+
+
+# ---- block-scaled ------------------------------------------------------------------------
+
+def _block_case(m, n, k, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    w = torch.randn(n, k, generator=g) * 0.02
+    aq, a_s = oracle.per_token_group_quant_fp8(a, 128)
+    wq, w_s = oracle.quantize_weight_block(w, 128)
+    return aq, a_s, wq, w_s
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 512), (64, 128, 128), (256, 256, 256), (83, 7752, 3840),
+                                   (1, 2112, 7168), (64, 4096, 7168), (512, 2112, 7168), (300, 1536, 1024)])
+def test_w8a8_block_fp8_matmul(m, n, k):
+    aq, a_s, wq, w_s = _block_case(m, n, k)
+    out = flag_gems.w8a8_block_fp8_matmul(aq.cuda(), wq.cuda(), a_s.cuda(), w_s.cuda(), [128, 128])
+    assert out.dtype == torch.bfloat16 and out.shape == (m, n)
+    _close(out, oracle.block_scaled_mm(aq, wq, a_s, w_s))
+
+
+def test_w8a8_block_reference_test_recipe():
+    """Recipe of tests/test_w8a8_block_fp8_matmul.py: randn->fp8 operands, scales 0.01*rand+0.005,
+    fp16 output, rtol 1e-3 / atol 1e-4*K (fp16 rounding aside)."""
+    g = torch.Generator().manual_seed(3)
+    for (m, n, k) in [(128, 256, 512), (84, 7168, 3840)]:
+        a = torch.randn(m, k, generator=g).clamp(-448, 448).to(FP8)
+        b = torch.randn(n, k, generator=g).clamp(-448, 448).to(FP8)
+        a_s = 0.01 * torch.rand(m, k // 128, generator=g) + 0.005
+        b_s = 0.01 * torch.rand((n + 127) // 128, k // 128, generator=g) + 0.005
+        out = flag_gems.w8a8_block_fp8_matmul(a.cuda(), b.cuda(), a_s.cuda(), b_s.cuda(), [128, 128], torch.float16)
+        ref = oracle.block_scaled_mm(a, b, a_s, b_s, out_dtype=torch.float32)
+        _close(out, ref, rtol=2e-3, atol=1e-4 * k)
+
+
+def test_block_scaled_golden_and_negative_scales(golden_dir):
+    for c in torch.load(os.path.join(golden_dir, "block_scaled_mm.pt")):
+        a, b = c["a"].view(FP8), c["b"].view(FP8)
+        out = flag_gems.w8a8_block_fp8_matmul(a.cuda(), b.cuda(), c["a_s"].cuda(), c["b_s"].cuda(), [128, 128],
+                                              torch.float32)
+        _close(out, c["c"], rtol=1e-3, atol=1e-3 * float(c["c"].abs().max()))
+    g = torch.Generator().manual_seed(4)
+    a = torch.randn(40, 256, generator=g).clamp(-448, 448).to(FP8)
+    b = torch.randn(384, 256, generator=g).clamp(-448, 448).to(FP8)
+    a_s = torch.randn(40, 2, generator=g) * 0.01      # the reference's MoE test draws signed scales
+    b_s = torch.randn(3, 2, generator=g) * 0.01
+    out = flag_gems.w8a8_block_fp8_matmul(a.cuda(), b.cuda(), a_s.cuda(), b_s.cuda(), [128, 128], torch.float32)
+    ref = oracle.block_scaled_mm(a, b, a_s, b_s, out_dtype=torch.float32)
+    _close(out, ref, rtol=1e-3, atol=1e-3 * float(ref.abs().max()))
+
+
+def test_fp8_matmul_and_blockwise_cutlass_form():
+    aq, a_s, wq, w_s = _block_case(200, 1024, 2048, seed=5)
+    ref = oracle.block_scaled_mm(aq, wq, a_s, w_s)
+    out = flag_gems.fp8_matmul(aq.cuda(), a_s.cuda(), wq.cuda(), w_s.cuda())
+    _close(out, ref)
+    c = torch.empty(200, 1024, dtype=torch.bfloat16, device="cuda")
+    flag_gems.cutlass_scaled_mm(c, aq.cuda(), wq.cuda().t(), a_s.cuda(), w_s.cuda().t().contiguous())
+    _close(c, ref)
+
+
+def test_gemm_full_size_linearity():
+    """configs[1]/[2] sizes without a CPU oracle pass: doubling every scale doubles the output
+    exactly (powers of two commute with every rounding), and a sampled block of rows/columns
+    matches the oracle."""
+    g = torch.Generator().manual_seed(6)
+    m, n, k = 4096, 4096, 7168
+    aq = torch.randn(m, k, generator=g).clamp(-448, 448).to(FP8).cuda()
+    wq = torch.randn(n, k, generator=g).clamp(-448, 448).to(FP8).cuda()
+    a_s = (torch.rand(m, k // 128, generator=g) * 1e-2 + 1e-3).cuda()
+    w_s = (torch.rand(n // 128, k // 128, generator=g) * 1e-2 + 1e-3).cuda()
+    o1 = flag_gems.w8a8_block_fp8_matmul(aq, wq, a_s, w_s, [128, 128])
+    o2 = flag_gems.w8a8_block_fp8_matmul(aq, wq, a_s * 2, w_s, [128, 128])
+    assert torch.equal(o2.float(), o1.float() * 2)
+    rows = torch.arange(1000, 1064)
+    ref = oracle.block_scaled_mm(aq[rows].cpu(), wq[512:768].cpu(), a_s[rows].cpu(), w_s[4:6].cpu())
+    _close(o1[rows][:, 512:768], ref)
+    sa = (torch.rand(m, generator=g) * 1e-2 + 1e-3).cuda()
+    sb = (torch.rand(n, generator=g) * 1e-2 + 1e-3).cuda()
+    c1 = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    c2 = torch.empty_like(c1)
+    flag_gems.cutlass_scaled_mm(c1, aq, wq.t(), sa, sb)
+    flag_gems.cutlass_scaled_mm(c2, aq, wq.t(), sa * 2, sb)
+    assert torch.equal(c2.float(), c1.float() * 2)
+    ref = oracle.scaled_mm(aq[rows].cpu(), wq[512:768].cpu().t(), sa[rows].cpu(), sb[512:768].cpu())
+    _close(c1[rows][:, 512:768], ref)
+
+
+def test_no_device_errors_recorded():
+    assert _cabi.device_status() == 0
