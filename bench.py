@@ -1,0 +1,482 @@
+"""Benchmark of the FP8 quantized-inference hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+Prints ONE JSON line.  The default workload is the DeepSeek-V3-shaped fused MoE layer of
+BASELINE.json configs[4] (hidden 7168, expert intermediate 2048, 256 routed experts, top-8,
+one shared expert, T=8192 tokens in total, FP8 weights with 128x128 block scales): the one
+configuration of the metric that is defined at 1, 2, 4 and 8 GPUs, so every N reports the same
+quantity (tokens/s of the whole layer, strong scaling: the 8192 tokens and 256 experts are
+split over the ranks, dispatch/combine by all-to-all).  At N=1 the same line also carries the
+other half of the metric under "extra": FP8 scaled-mm TFLOP/s on the Llama-3-8B shapes
+(configs[1]) and block-scaled shapes (configs[2]), and act_quant GB/s.
+
+A step = one forward pass of the layer over the step's tokens.  "value" is measured with the
+inputs resident in HBM; "e2e" goes through the public layer call with pinned HOST buffers,
+host->device copies of the step's activations/router outputs and the device->host read of the
+result inside the timed region.  Inputs are synthetic (seeded), weights random-initialised and
+quantised as the configuration describes.  Weights (1.4-11.3 GB per rank) exceed the 126 MB
+L2, so no explicit L2 flush is needed between iterations.
+
+--impl reference times the CPU restatement of the reference's algorithm (oracle/) on the host
+cores for the same metric on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+HIDDEN, INTER, EXPERTS, TOPK, TOKENS = 7168, 2048, 256, 8, 8192
+FP8 = torch.float8_e4m3fn
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"],
+                    bf16_tflops_sustained=d.get("bf16_tflops_sustained", d["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+# ---------------------------------------------------------------------------------------------
+# synthetic inputs
+# ---------------------------------------------------------------------------------------------
+def make_router(tokens, experts, topk, seed=0):
+    """Zipf(s=1.1) expert popularity over a seeded permutation, Gumbel top-k per token,
+    weights = softmax of the selected scores (renormalised), bf16."""
+    g = torch.Generator().manual_seed(seed)
+    p = torch.arange(1, experts + 1).float() ** -1.1
+    p = p[torch.randperm(experts, generator=g)]
+    u = torch.rand(tokens, experts, generator=g).clamp_min(1e-9)
+    score = torch.log(p / p.sum()) - torch.log(-torch.log(u))
+    sc, ids = torch.topk(score, topk)
+    return torch.softmax(sc, -1).bfloat16(), ids
+
+
+def block_quant_weight_gpu(w):
+    """[N, K] fp32 on the device -> (fp8 [N, K], fp32 [N/128, K/128]) with 128x128 block scales."""
+    n, k = w.shape
+    t = w.view(n // 128, 128, k // 128, 128)
+    s = t.abs().amax(dim=(1, 3)).clamp_min(1e-10) / torch.tensor(448.0, device=w.device)
+    q = (t / s[:, None, :, None]).clamp(-448, 448).view(n, k).to(FP8)
+    return q, s
+
+
+def make_expert_weights(n_experts, first_expert, device, seed=0):
+    w1 = torch.empty(n_experts, 2 * INTER, HIDDEN, dtype=FP8, device=device)
+    w2 = torch.empty(n_experts, HIDDEN, INTER, dtype=FP8, device=device)
+    s1 = torch.empty(n_experts, 2 * INTER // 128, HIDDEN // 128, device=device)
+    s2 = torch.empty(n_experts, HIDDEN // 128, INTER // 128, device=device)
+    g = torch.Generator(device=device)
+    for e in range(n_experts):
+        g.manual_seed(seed * 1000003 + first_expert + e)
+        w1[e], s1[e] = block_quant_weight_gpu(torch.randn(2 * INTER, HIDDEN, device=device, generator=g) * 0.02)
+        w2[e], s2[e] = block_quant_weight_gpu(torch.randn(HIDDEN, INTER, device=device, generator=g) * 0.02)
+    return w1, w2, s1, s2
+
+
+def make_shared_weights(device, seed=0):
+    g = torch.Generator(device=device)
+    g.manual_seed(seed * 1000003 + 999983)
+    a, sa = block_quant_weight_gpu(torch.randn(2 * INTER, HIDDEN, device=device, generator=g) * 0.02)
+    b, sb = block_quant_weight_gpu(torch.randn(HIDDEN, INTER, device=device, generator=g) * 0.02)
+    return a, b, sa, sb
+
+
+# ---------------------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active")
+                                                         for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------
+# timing helpers
+# ---------------------------------------------------------------------------------------------
+def time_events(fn, iters):
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / iters
+
+
+def time_graph(fn, iters=10, warm=3, reps=3):
+    """Device time of fn per call, launch overhead excluded: `iters` calls captured in one CUDA
+    graph and replayed (events on the replay stream)."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    st = torch.cuda.Stream()
+    st.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(st):
+        with torch.cuda.graph(graph, stream=st):
+            for _ in range(iters):
+                fn()
+    best = None
+    for _ in range(reps):
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        graph.replay()
+        e.record()
+        torch.cuda.synchronize()
+        t = s.elapsed_time(e) / iters
+        best = t if best is None else min(best, t)
+    return best
+
+
+# ---------------------------------------------------------------------------------------------
+# extras at N=1: the dense half of the metric
+# ---------------------------------------------------------------------------------------------
+def dense_extras(peaks):
+    import flag_gems
+
+    out = {"scaled_mm_tflops": {}, "block_scaled_mm_tflops": {}, "quant_gbs": {}}
+    fp8_peak = 2.0 * peaks["bf16_tflops"]
+    g = torch.Generator(device="cuda")
+    g.manual_seed(0)
+    for (name, n, k) in [("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336)]:
+        w = (torch.randn(n, k, device="cuda", generator=g) * 0.02)
+        sw = w.abs().amax(1).clamp_min(1e-10) / 448.0
+        wq = (w / sw[:, None]).clamp(-448, 448).to(FP8)
+        del w
+        for m in (128, 1024, 4096, 8192):
+            a = torch.randn(m, k, device="cuda", generator=g).bfloat16()
+            aq, sa = flag_gems.fused.fused_moe._fp8_quantize(a, None, True, None)
+            c = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+            ms = time_graph(lambda: flag_gems.cutlass_scaled_mm(c, aq, wq.t(), sa.view(-1), sw))
+            tf = 2.0 * m * n * k / ms / 1e9
+            out["scaled_mm_tflops"][f"{name}_M{m}_N{n}_K{k}"] = {
+                "tflops": round(tf, 1), "us": round(ms * 1e3, 1), "frac_of_2x_measured_bf16": round(tf / fp8_peak, 3),
+                "frac_of_nominal_4500": round(tf / 4500.0, 3)}
+    k = 7168
+    for n in (2112, 4096, 18432, 24576):
+        w = torch.randn((n + 127) // 128 * 128, k, device="cuda", generator=g) * 0.02
+        wq, ws = block_quant_weight_gpu(w)
+        wq = wq[:n].contiguous()
+        del w
+        for m in (512, 4096, 16384):
+            a = torch.randn(m, k, device="cuda", generator=g).bfloat16()
+            aq, a_s = flag_gems.per_token_group_quant_fp8(a, 128)
+            ms = time_graph(lambda: flag_gems.w8a8_block_fp8_matmul(aq, wq, a_s, ws, [128, 128]), iters=5)
+            tf = 2.0 * m * n * k / ms / 1e9
+            out["block_scaled_mm_tflops"][f"M{m}_N{n}_K{k}"] = {
+                "tflops": round(tf, 1), "us": round(ms * 1e3, 1), "frac_of_2x_measured_bf16": round(tf / fp8_peak, 3),
+                "frac_of_nominal_4500": round(tf / 4500.0, 3)}
+    for (m, kk) in ((256, 4096), (16384, 7168)):
+        x = torch.randn(m, kk, device="cuda", generator=g).bfloat16()
+        by = m * kk * (2 + 1 + 4 / 128)
+        for nm, fn in (("act_quant_g128", lambda: flag_gems.act_quant_triton(x, 128)),
+                       ("per_token_group_quant_g128", lambda: flag_gems.per_token_group_quant_fp8(x, 128))):
+            ms = time_graph(fn)
+            out["quant_gbs"][f"{nm}_M{m}_K{kk}"] = {"gbs": round(by / ms / 1e6, 1), "us": round(ms * 1e3, 1),
+                                                   "frac_of_measured_hbm": round(by / ms / 1e6 / peaks["hbm_gbs"], 3)}
+    ids = make_router(TOKENS, EXPERTS, TOPK)[1].cuda()
+    ms = time_graph(lambda: flag_gems.moe_align_block_size(ids, 64, EXPERTS), iters=20)
+    out["moe_align_us"] = {"T8192_top8_E256_bs64": round(ms * 1e3, 1)}
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm (oracle)
+# ---------------------------------------------------------------------------------------------
+def cpu_layer_sample(hidden, tw, ti, fetch_expert, shared):
+    """The oracle's layer on a few tokens.  fetch_expert(e) -> (w1, w2, s1, s2) CPU tensors."""
+    import oracle
+
+    experts = sorted(set(ti.reshape(-1).tolist()))
+    remap = {e: i for i, e in enumerate(experts)}
+    ws = [fetch_expert(e) for e in experts]
+    w1 = torch.stack([w[0] for w in ws])
+    w2 = torch.stack([w[1] for w in ws])
+    s1 = torch.stack([w[2] for w in ws])
+    s2 = torch.stack([w[3] for w in ws])
+    ti2 = ti.clone().apply_(lambda e: remap[e])
+    t0 = time.perf_counter()
+    add = oracle.dense_block_fp8_mlp(hidden, *shared)
+    out = oracle.fused_moe_block_fp8(hidden, w1, w2, s1, s2, tw, ti2, addend=add)
+    return out, time.perf_counter() - t0
+
+
+def cpu_weight_pool(pool=8, seed=0):
+    import oracle
+
+    g = torch.Generator().manual_seed(seed)
+    sets = []
+    for _ in range(pool):
+        w1, s1 = oracle.quantize_weight_block(torch.randn(2 * INTER, HIDDEN, generator=g) * 0.02)
+        w2, s2 = oracle.quantize_weight_block(torch.randn(HIDDEN, INTER, generator=g) * 0.02)
+        sets.append((w1, w2, s1, s2))
+    return sets
+
+
+def run_reference(args):
+    """CPU arm: oracle on all host threads, one bounded sample of tokens per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    sample = args.cpu_tokens
+    pool = cpu_weight_pool()
+    shared = pool[0]
+    tw, ti = make_router(TOKENS, EXPERTS, TOPK)
+    g = torch.Generator().manual_seed(1)
+    times = []
+    for step in range(args.warmup + args.steps):
+        lo = (step * sample) % (TOKENS - sample)
+        hidden = torch.randn(sample, HIDDEN, generator=g).bfloat16()
+        _, dt = cpu_layer_sample(hidden, tw[lo:lo + sample], ti[lo:lo + sample], lambda e: pool[e % len(pool)], shared)
+        if step >= args.warmup:
+            times.append(dt)
+    ms = 1e3 * sum(times) / len(times)
+    value = sample / (ms / 1e3)
+    desc = (f"{sample} tokens per step of the T={TOKENS} workload (router, shapes and top-{TOPK} as configured; "
+            f"expert weights drawn from a pool of {len(pool)} generated weight sets), oracle/ torch-CPU fp32")
+    line = {
+        "impl": "reference", "metric": "fused_moe_tokens_per_s", "value": round(value, 3), "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 3),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3",
+        "data": "synthetic", "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": round(value, 3), "unit": "tokens/s", "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": desc},
+        "e2e": {"value": round(value, 3), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n):
+    return {"workload": "deepseek_v3_moe_layer (BASELINE configs[4])", "hidden": HIDDEN, "intermediate": INTER,
+            "experts": EXPERTS, "top_k": TOPK, "shared_experts": 1, "tokens_global": TOKENS,
+            "weight_format": "fp8_e4m3 128x128 block scales", "activation_format": "fp8_e4m3 1x128 group scales",
+            "router": "zipf(1.1) gumbel top-8, seed 0", "parallelism": f"ep{n}",
+            "l2": "weights per rank (>=1.4 GB) exceed L2; no explicit flush"}
+
+
+# ---------------------------------------------------------------------------------------------
+# main arm
+# ---------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch.distributed as dist
+
+    import flag_gems  # noqa: F401
+    from flaggems_b200 import _cabi
+    from flaggems_b200.ep import ExpertParallelMoE
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback "
+                         "(use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    assert world == args.gpus or world == 1, f"WORLD_SIZE {world} != --gpus {args.gpus}"
+    peaks = load_peaks()
+
+    e_loc, t_loc = EXPERTS // world, TOKENS // world
+    w1, w2, s1, s2 = make_expert_weights(e_loc, rank * e_loc, dev)
+    shared = make_shared_weights(dev)
+    layer = ExpertParallelMoE(w1, w2, s1, s2, EXPERTS, rank, world, shared=shared)
+    tw_all, ti_all = make_router(TOKENS, EXPERTS, TOPK)
+    sl = slice(rank * t_loc, (rank + 1) * t_loc)
+    g = torch.Generator().manual_seed(100 + rank)
+    hidden_h = torch.randn(t_loc, HIDDEN, generator=g).bfloat16().pin_memory()
+    tw_h, ti_h = tw_all[sl].contiguous().pin_memory(), ti_all[sl].contiguous().pin_memory()
+    out_h = torch.empty(t_loc, HIDDEN, dtype=torch.bfloat16).pin_memory()
+    hidden_d, tw_d, ti_d = hidden_h.to(dev), tw_h.to(dev), ti_h.to(dev)
+
+    def step_resident():
+        return layer(hidden_d, tw_d, ti_d)
+
+    def step_e2e():
+        h = hidden_h.to(dev, non_blocking=True)
+        w = tw_h.to(dev, non_blocking=True)
+        i = ti_h.to(dev, non_blocking=True)
+        out_h.copy_(layer(h, w, i), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    def timed(fn, steps):
+        barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(steps):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        ms = s.elapsed_time(e) / steps
+        barrier()
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    launches0 = _cabi.launch_count()
+    with ClockSampler(local_rank) as clocks:
+        ms = timed(step_resident, args.steps)
+    launches = _cabi.launch_count() - launches0
+    for _ in range(2):
+        step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+    status = _cabi.device_status()
+
+    # dominant kernel: the grouped GEMM1 (block-scaled, fused SiLU) on this rank's routed rows,
+    # timed alone on the launching stream with CUDA events.
+    from flaggems_b200.fused.fused_moe import _TILE_ROWS, _group_quant, _grouped_gemm
+    from flaggems_b200.fused.moe_align_block_size import moe_align_block_size
+
+    if world == 1:
+        ids_local, n_rows, hid_src, div = ti_d, t_loc * TOPK, hidden_d, TOPK
+    else:
+        # rows this rank's experts receive: recompute the global routing (identical on every rank)
+        owner = ti_all // e_loc
+        mask = owner == rank
+        n_rows = int(mask.sum())
+        ids_local = (ti_all[mask] % e_loc).to(torch.int32).to(dev)
+        hid_src, div = torch.randn(n_rows, HIDDEN, device=dev).bfloat16(), 1
+    sorted_ids, expert_ids, post_pad = moe_align_block_size(ids_local, _TILE_ROWS, e_loc)
+    rows = sorted_ids.numel() // _TILE_ROWS * _TILE_ROWS
+    a1, a1s = _group_quant(hid_src, 128, sorted_ids, div, n_rows, post_pad, rows)
+    act = torch.empty((rows, INTER), dtype=torch.bfloat16, device=dev)
+
+    def gemm1():
+        _grouped_gemm(act, a1, w1, a1s, layer.ops.w1_scale, None, sorted_ids, expert_ids, post_pad, n_rows,
+                      _cabi.SCALE_BLOCK, fuse_silu=True, scatter=False, mul_weight=False)
+
+    for _ in range(3):
+        gemm1()
+    gemm1_ms = time_events(gemm1, max(args.steps, 5))
+    gemm1_flops = 2.0 * n_rows * (2 * INTER) * HIDDEN
+    achieved = gemm1_flops / gemm1_ms / 1e9
+    fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+    roofline = {"bound": "tensor", "kernel": "gemm_fp8_kernel<BN, block_scaled, fuse_silu> (MoE GEMM1)",
+                "achieved": round(achieved, 1), "peak": round(fp8_peak, 1), "unit": "TFLOP/s",
+                "frac": round(achieved / fp8_peak, 4), "traffic": None,
+                "peak_source": f"2 x {peaks['source']} sustained dense bf16 cuBLAS TF/s (fp8 tensor rate is twice bf16)",
+                "frac_of_nominal_4500": round(achieved / 4500.0, 4), "launch_ms": round(gemm1_ms, 4),
+                "algorithmic_flops_per_launch": gemm1_flops, "rows": n_rows}
+
+    value = TOKENS / (ms / 1e3)
+    e2e_value = TOKENS / (ms_e2e / 1e3)
+    h2d = hidden_h.numel() * 2 + tw_h.numel() * 2 + ti_h.numel() * 8
+    d2h = out_h.numel() * 2
+    line = {
+        "metric": "fused_moe_tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+        "config": workload_config(world), "clocks": clocks.summary(),
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d * world,
+                "d2h_bytes_per_step": d2h * world, "ms_per_step": round(ms_e2e, 4)},
+        "gpu_launches": int(launches), "roofline": roofline, "device_status": status,
+        "layer_tflops": round((2.0 * TOKENS * TOPK * 3 * HIDDEN * INTER + 2.0 * TOKENS * 3 * HIDDEN * INTER) / ms / 1e9, 1),
+    }
+
+    if rank == 0 and world == 1:
+        # CPU baseline on a bounded sample of the same tokens, with the same weights (copied from
+        # the device), doubling as a parity check of the GPU result at the full configuration.
+        torch.set_num_threads(os.cpu_count() or 1)
+        n = args.cpu_tokens
+        out_d = layer(hidden_d, tw_d, ti_d)
+
+        def fetch(e):
+            return w1[e].cpu(), w2[e].cpu(), s1[e].cpu(), s2[e].cpu()
+
+        ref, dt = cpu_layer_sample(hidden_h[:n].clone(), tw_h[:n].clone(), ti_h[:n].clone(), fetch,
+                                   tuple(t.cpu() for t in shared))
+        err = (out_d[:n].cpu().float() - ref.float()).abs()
+        tol = 1e-2 + 1e-2 * ref.float().abs()
+        line["cpu_baseline"] = {"value": round(n / dt, 3), "unit": "tokens/s", "cores": torch.get_num_threads(),
+                                "kind": "port",
+                                "sample": f"first {n} tokens of the step (all experts they route to, same weights), "
+                                          f"oracle/ torch-CPU fp32, {dt:.1f} s"}
+        line["parity_sample"] = {"tokens": n, "max_abs_err": float(err.max()),
+                                 "within_rtol1e-2_atol1e-2": bool((err <= tol).all())}
+        if not args.no_extras:
+            line["extra"] = dense_extras(peaks)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-tokens", type=int, default=16, help="tokens in the bounded CPU sample")
+    ap.add_argument("--no-extras", action="store_true", help="skip the dense GEMM / quant figures at N=1")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

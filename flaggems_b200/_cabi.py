@@ -33,6 +33,9 @@ _SIGS = {
         c_int, [_P, c_int, c_int64, c_int, c_int, _P, c_int, _P, c_int64, _P, c_int64, _P, _P]),
     "fg_silu_and_mul": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int, _P]),
     "fg_moe_sum": (c_int, [_P, _P, c_int64, c_int, c_int64, c_int, _P]),
+    "fg_moe_sum_indexed": (c_int, [_P, _P, c_int64, c_int, c_int64, c_int, _P, _P, _P]),
+    "fg_gather_rows_fp8": (
+        c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, _P, c_int32, c_int32, _P, _P]),
     "fg_scaled_mm_fp8": (
         c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                 c_int, c_int, c_int, c_int, _P]),

@@ -202,7 +202,8 @@ __global__ void __launch_bounds__(256) silu_and_mul_kernel(const T* __restrict__
 
 template <typename T>
 __global__ void __launch_bounds__(256) moe_sum_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t M,
-                                                      int topk, int64_t K) {
+                                                      int topk, int64_t K, const int32_t* __restrict__ row_index,
+                                                      const T* __restrict__ addend) {
     const int64_t vec_per_row = K / 8;
     const int64_t total = M * vec_per_row;
     for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += (int64_t)gridDim.x * blockDim.x) {
@@ -210,11 +211,44 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(const T* __restrict__ in, 
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         for (int k = 0; k < topk; ++k) {
             float t[8];
-            fg_load8(in + (r * topk + k) * K + c, t);
+            const int64_t src = row_index ? (int64_t)row_index[r * topk + k] : r * topk + k;
+            if (src < 0) continue;
+            fg_load8(in + src * K + c, t);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] += t[i];
+        }
+        if (addend) {
+            float t[8];
+            fg_load8(addend + r * K + c, t);
 #pragma unroll
             for (int i = 0; i < 8; ++i) acc[i] += t[i];
         }
         fg_store8(out + r * K + c, acc);
+    }
+}
+
+// Copies rows of FP8 bytes and their fp32 scale rows through an index (pure data movement).
+__global__ void __launch_bounds__(256) gather_rows_kernel(const uint8_t* __restrict__ src_q,
+                                                          const float* __restrict__ src_s, uint8_t* __restrict__ dst_q,
+                                                          float* __restrict__ dst_s, int64_t rows, int64_t K,
+                                                          int64_t s_cols, const int32_t* __restrict__ row_index,
+                                                          int32_t index_div, int32_t index_limit,
+                                                          const int32_t* __restrict__ n_rows_dev) {
+    if (n_rows_dev) {
+        const int64_t v = *n_rows_dev;
+        rows = v < rows ? v : rows;
+    }
+    const int warps_per_block = blockDim.x / 32;
+    const int lane = threadIdx.x & 31;
+    for (int64_t r = (int64_t)blockIdx.x * warps_per_block + (threadIdx.x >> 5); r < rows;
+         r += (int64_t)gridDim.x * warps_per_block) {
+        const int32_t idx = row_index[r];
+        const bool real = idx >= 0 && idx < index_limit;
+        const int64_t src = real ? idx / index_div : 0;
+        const uint4* sq = reinterpret_cast<const uint4*>(src_q + src * K);
+        uint4* dq = reinterpret_cast<uint4*>(dst_q + r * K);
+        for (int64_t v = lane; v < K / 16; v += 32) dq[v] = real ? sq[v] : make_uint4(0u, 0u, 0u, 0u);
+        for (int64_t v = lane; v < s_cols; v += 32) dst_s[r * s_cols + v] = real ? src_s[src * s_cols + v] : 1.0f;
     }
 }
 
@@ -256,7 +290,13 @@ int fg_moe_align_block_size(const void* topk_ids, int ids_are_i64, int64_t numel
     const size_t smem = (size_t)(ALIGN_WARPS + 4) * num_experts * sizeof(int32_t);
 
     auto kernel = ids_are_i64 ? moe_align_kernel<int64_t> : moe_align_kernel<int32_t>;
-    FG_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    // Opt in to large dynamic shared memory once per kernel and size (a host-side attribute,
+    // kept out of the steady-state call path).
+    static size_t smem_set[2] = {48 * 1024, 48 * 1024};
+    if (smem > smem_set[ids_are_i64 ? 1 : 0]) {
+        FG_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        smem_set[ids_are_i64 ? 1 : 0] = smem;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ranks, 1, 1);
     cfg.blockDim = dim3(ALIGN_THREADS, 1, 1);
@@ -304,21 +344,53 @@ int fg_silu_and_mul(const void* x, const void* y, void* out, int64_t M, int64_t 
     return FG_OK;
 }
 
-int fg_moe_sum(const void* in, void* out, int64_t M, int topk, int64_t K, int dtype, void* stream) {
+int fg_moe_sum_indexed(const void* in, void* out, int64_t M, int topk, int64_t K, int dtype,
+                       const int32_t* row_index, const void* addend, void* stream) {
     FG_REQUIRE(M >= 0 && K >= 0 && topk >= 0, FG_ERR_INVALID_ARGUMENT, "negative size");
     if (M == 0 || K == 0) return FG_OK;
-    FG_REQUIRE(K % 8 == 0 && (uintptr_t)in % 16 == 0 && (uintptr_t)out % 16 == 0, FG_ERR_UNSUPPORTED,
-               "moe_sum needs K %% 8 == 0 and 16-byte aligned buffers");
+    FG_REQUIRE(K % 8 == 0 && (uintptr_t)in % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)addend % 16 == 0,
+               FG_ERR_UNSUPPORTED, "moe_sum needs K %% 8 == 0 and 16-byte aligned buffers");
     cudaStream_t st = (cudaStream_t)stream;
     const unsigned grid = grid_for(M * (K / 8), 256);
     switch (dtype) {
         case FG_DTYPE_BF16:
-            moe_sum_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, M, topk, K);
+            moe_sum_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, M, topk, K, row_index,
+                                                 (const __nv_bfloat16*)addend);
             break;
-        case FG_DTYPE_F16: moe_sum_kernel<<<grid, 256, 0, st>>>((const __half*)in, (__half*)out, M, topk, K); break;
-        case FG_DTYPE_F32: moe_sum_kernel<<<grid, 256, 0, st>>>((const float*)in, (float*)out, M, topk, K); break;
+        case FG_DTYPE_F16:
+            moe_sum_kernel<<<grid, 256, 0, st>>>((const __half*)in, (__half*)out, M, topk, K, row_index,
+                                                 (const __half*)addend);
+            break;
+        case FG_DTYPE_F32:
+            moe_sum_kernel<<<grid, 256, 0, st>>>((const float*)in, (float*)out, M, topk, K, row_index,
+                                                 (const float*)addend);
+            break;
         default: fg_set_error("unsupported dtype code %d", dtype); return FG_ERR_INVALID_ARGUMENT;
     }
+    fg_count_launch(1);
+    FG_LAUNCH_CHECK();
+    return FG_OK;
+}
+
+int fg_moe_sum(const void* in, void* out, int64_t M, int topk, int64_t K, int dtype, void* stream) {
+    return fg_moe_sum_indexed(in, out, M, topk, K, dtype, nullptr, nullptr, stream);
+}
+
+int fg_gather_rows_fp8(const void* src_q, const float* src_s, void* dst_q, float* dst_s, int64_t rows, int64_t K,
+                       int64_t s_cols, const int32_t* row_index, int32_t index_div, int32_t index_limit,
+                       const int32_t* n_rows_dev, void* stream) {
+    FG_REQUIRE(rows >= 0 && K >= 0 && s_cols >= 0, FG_ERR_INVALID_ARGUMENT, "negative size");
+    if (rows == 0) return FG_OK;
+    FG_REQUIRE(src_q && dst_q && row_index && index_div > 0 && (s_cols == 0 || (src_s && dst_s)),
+               FG_ERR_INVALID_ARGUMENT, "null pointer or bad index_div");
+    FG_REQUIRE(K % 16 == 0 && (uintptr_t)src_q % 16 == 0 && (uintptr_t)dst_q % 16 == 0, FG_ERR_UNSUPPORTED,
+               "gather_rows needs K %% 16 == 0 and 16-byte aligned buffers");
+    int64_t blocks = fg_cdiv(rows, 8);
+    const int64_t cap = (int64_t)fg_num_sms() * 8;
+    if (blocks > cap) blocks = cap;
+    gather_rows_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+        (const uint8_t*)src_q, src_s, (uint8_t*)dst_q, dst_s, rows, K, s_cols, row_index, index_div, index_limit,
+        n_rows_dev);
     fg_count_launch(1);
     FG_LAUNCH_CHECK();
     return FG_OK;

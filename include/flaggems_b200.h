@@ -108,6 +108,23 @@ int fg_silu_and_mul(const void* x, const void* y, void* out, int64_t M, int64_t 
  * in [M, topk, K] contiguous, out [M, K]; fp32 sum in slot order. */
 int fg_moe_sum(const void* in, void* out, int64_t M, int topk, int64_t K, int dtype, void* stream);
 
+/* moe_sum with the rows of `in` addressed through row_index[m*topk + k] (negative = skip) and
+ * an optional addend [M,K] joined in fp32 before the cast.  Combine step of the
+ * expert-parallel layer: the top-k sum of src/flag_gems/fused/moe_sum.py:57-67 applied to
+ * rows that came back from other ranks in dispatch order, plus the shared-expert output.
+ * (The reference has no dispatch/combine; its own multi-GPU hook is expert_map.) */
+int fg_moe_sum_indexed(const void* in, void* out, int64_t M, int topk, int64_t K, int dtype,
+                       const int32_t* row_index, const void* addend, void* stream);
+
+/* Copies FP8 rows [*, K] and their fp32 scale rows [*, s_cols] into a new row order:
+ * output row r takes source row row_index[r] / index_div when 0 <= row_index[r] < index_limit,
+ * else zeros (scales 1).  The A-operand gather the reference does inside fused_moe_kernel
+ * (offs_token // top_k, src/flag_gems/fused/fused_moe.py:1101-1110), done ahead of the GEMM so
+ * the GEMM reads contiguous tiles by TMA.  n_rows_dev (nullable): device count of rows. */
+int fg_gather_rows_fp8(const void* src_q, const float* src_s, void* dst_q, float* dst_s, int64_t rows,
+                       int64_t K, int64_t s_cols, const int32_t* row_index, int32_t index_div,
+                       int32_t index_limit, const int32_t* n_rows_dev, void* stream);
+
 /* ---- scaled FP8 matrix products (tcgen05 / TMEM / TMA) ---------------------- */
 
 /* cutlass_scaled_mm (scalar / per-token / per-channel scales):

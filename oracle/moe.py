@@ -91,6 +91,7 @@ def fused_moe_block_fp8(
     fuse_silu: bool = True,
     expert_lo: int = 0,
     expert_hi: Optional[int] = None,
+    addend: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Block-FP8 (128x128 weight blocks, 1x128 activation groups) MoE layer.
 
@@ -104,7 +105,8 @@ def fused_moe_block_fp8(
     activation as the FUSE_SILU kernel branch does (:1346-1347), False rounds
     them to bf16 first as the golden and the unfused path do.
     Only experts in [expert_lo, expert_hi) contribute (expert-parallel shards);
-    w1/w2 then hold just those experts.
+    w1/w2 then hold just those experts.  ``addend`` [T, H] (the shared-expert output)
+    joins the top-k sum in fp32 before the single cast to the output dtype.
     """
     t, h = hidden.shape
     topk = topk_ids.shape[1]
@@ -122,7 +124,10 @@ def fused_moe_block_fp8(
         r = block_scaled_mm(aq, w2[le], asc, w2_scale[le], block, block, torch.float32)
         r = (r * topk_weights[tok, slot].float().unsqueeze(1)).to(hidden.dtype)
         out[tok, slot] = r.float()
-    return moe_sum(out).to(hidden.dtype)
+    acc = moe_sum(out)
+    if addend is not None:
+        acc = acc + addend.float()
+    return acc.to(hidden.dtype)
 
 
 def fused_moe_per_channel_fp8(

@@ -1,0 +1,161 @@
+"""Expert-parallel layer: host logic (routing order, counts, all-to-all, inverse permutation,
+combine) on 2 CPU ranks over gloo.  The device work is swapped for CPU-oracle stand-ins here;
+the result must equal the single-rank oracle of the whole layer bit for bit."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FP8 = torch.float8_e4m3fn
+
+
+class OracleOps:
+    """Test double for CudaMoEOps: same methods, computed by the CPU oracle."""
+
+    def __init__(self, w1, w2, s1, s2, shared=None):
+        self.w1, self.w2, self.s1, self.s2, self.shared = w1, w2, s1, s2, shared
+
+    def route_order(self, dest, world):
+        return torch.sort(dest, stable=True).indices.to(torch.int32)
+
+    def quant_gather(self, hidden, order, topk):
+        import oracle
+
+        return oracle.per_token_group_quant_fp8(hidden[order.long() // topk], 128)
+
+    def local_routed(self, hidden, topk_ids, weight, topk):
+        xq, xs = self.quant_gather(hidden, torch.arange(topk_ids.numel()), topk)
+        return self.expert_compute(xq, xs, topk_ids.reshape(-1).int(), weight, hidden.dtype)
+
+    def expert_compute(self, xq, xs, le, wt, dtype):
+        import oracle
+        from oracle.moe import _silu_mul_f32
+
+        y = torch.zeros(xq.shape[0], self.w2.shape[1], dtype=dtype)
+        for e in range(self.w1.shape[0]):
+            rows = torch.nonzero(le == e).flatten()
+            if rows.numel() == 0:
+                continue
+            z = oracle.block_scaled_mm(xq[rows], self.w1[e], xs[rows], self.s1[e], out_dtype=torch.float32)
+            act = _silu_mul_f32(z, True, dtype)
+            aq, a_s = oracle.per_token_group_quant_fp8(act, 128)
+            r = oracle.block_scaled_mm(aq, self.w2[e], a_s, self.s2[e], out_dtype=torch.float32)
+            y[rows] = (r * wt[rows].unsqueeze(1)).to(dtype)
+        return y
+
+    def shared_expert(self, hidden):
+        import oracle
+
+        return None if self.shared is None else oracle.dense_block_fp8_mlp(hidden, *self.shared)
+
+    def combine(self, rows, inv, tokens, topk, addend):
+        idx = torch.arange(tokens * topk) if inv is None else inv.long()
+        acc = torch.zeros(tokens, rows.shape[1])
+        for k in range(topk):
+            acc += rows[idx.view(tokens, topk)[:, k]].float()
+        if addend is not None:
+            acc += addend.float()
+        return acc.to(rows.dtype)
+
+
+def make_case(seed=0, t=48, h=256, i=128, e=8, topk=3, with_shared=True):
+    import oracle
+
+    g = torch.Generator().manual_seed(seed)
+    hidden = torch.randn(t, h, generator=g).bfloat16()
+    w1 = torch.empty(e, 2 * i, h, dtype=FP8)
+    w2 = torch.empty(e, h, i, dtype=FP8)
+    s1 = torch.empty(e, 2 * i // 128, h // 128)
+    s2 = torch.empty(e, h // 128, i // 128)
+    for x in range(e):
+        w1[x], s1[x] = oracle.quantize_weight_block(torch.randn(2 * i, h, generator=g) * 0.05)
+        w2[x], s2[x] = oracle.quantize_weight_block(torch.randn(h, i, generator=g) * 0.05)
+    shared = None
+    if with_shared:
+        a, sa = oracle.quantize_weight_block(torch.randn(2 * i, h, generator=g) * 0.05)
+        b, sb = oracle.quantize_weight_block(torch.randn(h, i, generator=g) * 0.05)
+        shared = (a, b, sa, sb)
+    # skewed router so that ranks receive different amounts
+    p = torch.arange(1, e + 1).float() ** -1.1
+    score = torch.log(p / p.sum()) - torch.log(-torch.log(torch.rand(t, e, generator=g).clamp_min(1e-9)))
+    sc, ti = torch.topk(score, topk)
+    tw = torch.softmax(sc, -1).bfloat16()
+    return hidden, w1, w2, s1, s2, tw, ti, shared
+
+
+def expected(case):
+    import oracle
+
+    hidden, w1, w2, s1, s2, tw, ti, shared = case
+    add = None if shared is None else oracle.dense_block_fp8_mlp(hidden, *shared)
+    return oracle.fused_moe_block_fp8(hidden, w1, w2, s1, s2, tw, ti, addend=add)
+
+
+def _worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from flaggems_b200.ep import ExpertParallelMoE
+
+        case = make_case()
+        hidden, w1, w2, s1, s2, tw, ti, shared = case
+        e, t = w1.shape[0], hidden.shape[0]
+        el, tl = e // world, t // world
+        lo = rank * el
+        ops = OracleOps(w1[lo:lo + el], w2[lo:lo + el], s1[lo:lo + el], s2[lo:lo + el], shared)
+        layer = ExpertParallelMoE(w1[lo:lo + el], w2[lo:lo + el], s1[lo:lo + el], s2[lo:lo + el], e, rank, world,
+                                  ops=ops)
+        sl = slice(rank * tl, (rank + 1) * tl)
+        out = layer(hidden[sl].contiguous(), tw[sl].contiguous(), ti[sl].contiguous())
+        ref = expected(case)[sl]
+        send, recv = layer.last_counts
+        q.put((rank, bool(torch.equal(out, ref)), float((out.float() - ref.float()).abs().max()), send, recv))
+    finally:
+        dist.destroy_process_group()
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+@pytest.mark.timeout(300)
+def test_two_rank_layer_equals_single_rank_oracle():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=240) for _ in range(world)]
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    res.sort()
+    for rank, equal, err, send, recv in res:
+        assert equal, f"rank {rank}: max abs err {err}"
+        assert sum(send) == 24 * 3
+    # what rank 0 sends to rank 1 is what rank 1 receives from rank 0
+    assert res[0][3][1] == res[1][4][0] and res[1][3][0] == res[0][4][1]
+
+
+def test_single_rank_layer_with_oracle_ops():
+    from flaggems_b200.ep import ExpertParallelMoE
+
+    case = make_case(seed=3, t=20, e=4, topk=2)
+    hidden, w1, w2, s1, s2, tw, ti, shared = case
+    layer = ExpertParallelMoE(w1, w2, s1, s2, 4, ops=OracleOps(w1, w2, s1, s2, shared))
+    assert torch.equal(layer(hidden, tw, ti), expected(case))
