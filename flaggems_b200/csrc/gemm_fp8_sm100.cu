@@ -9,9 +9,10 @@
 //   warp 1      MMA issuer: tcgen05.mma kind::f8f6f4, M=128, N=BN, K=32 per instruction, fp32
 //               accumulators in TMEM (two buffers of BN columns), tcgen05.commit to release
 //               ring stages and to publish accumulators.
-//   warps 2..   epilogue: tcgen05.ld TMEM -> registers, scales / SiLU / router weight / bias,
-//               conversion and global stores.  BN/32 warps; each thread owns one tile row and
-//               128 accumulator columns.
+//   warps 4..   epilogue: tcgen05.ld TMEM -> registers, scales / SiLU / router weight / bias,
+//               conversion and global stores.  BN/32 warps (one or two warpgroups); each thread
+//               owns one tile row and 128 accumulator columns.  (Warps 2-3 only pad the first
+//               warpgroup so that setmaxnreg can move registers from it to the epilogue.)
 //
 // Block-scaled mode: the accumulator of every 128-wide K block is published separately and
 // the epilogue warps fold it into fp32 registers as acc += partial * (As[m,kb] * Bs[nb,kb])
@@ -65,7 +66,15 @@ struct GemmParams {
 template <int BN>
 struct Cfg {
     static constexpr int EPI_WARPS = BN / 32;
-    static constexpr int THREADS = 64 + 32 * EPI_WARPS;
+    static constexpr int FIRST_EPI_WARP = 4;  // warps 0-3: TMA, MMA, two spare (one warpgroup)
+    static constexpr int THREADS = 32 * (FIRST_EPI_WARP + EPI_WARPS);
+    // With 384 threads the launch-time register file share is 168 per thread; the epilogue
+    // warpgroups raise theirs with setmaxnreg after the producer warpgroup has shrunk its own.
+    // The pool is what the CTA got at launch (384 x 168 = 64512), and setmaxnreg.inc blocks
+    // until the pool can pay: 128 x REGS_PRODUCER + 256 x REGS_EPILOGUE must not exceed it.
+    static constexpr bool REBALANCE_REGS = BN == 256;
+    static constexpr int REGS_PRODUCER = 40, REGS_EPILOGUE = 232;
+    static_assert(128 * REGS_PRODUCER + 256 * REGS_EPILOGUE <= 384 * 168, "setmaxnreg.inc would wait forever");
     static constexpr int A_BYTES = BLOCK_M * BLOCK_K;
     static constexpr int B_BYTES = BN * BLOCK_K;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -202,7 +211,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     const int a_rows_step = p.grouped ? p.block_rows : BLOCK_M;
     const uint32_t stage_tx = (uint32_t)(a_rows_step * BLOCK_K + C::B_BYTES);
 
-    if (warp == 0) {
+    if (warp < C::FIRST_EPI_WARP) {
+      if constexpr (C::REBALANCE_REGS) setmaxnreg_dec<C::REGS_PRODUCER>();
+      if (warp == 0) {
         // ------------------------------- TMA producer -------------------------------------
         if (lane == 0) {
             int stage = 0;
@@ -278,9 +289,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 }
             }
         }
+      }
     } else {
         // ------------------------------- epilogue -----------------------------------------
-        const int ew = warp - 2;
+        if constexpr (C::REBALANCE_REGS) setmaxnreg_inc<C::REGS_EPILOGUE>();
+        const int ew = warp - C::FIRST_EPI_WARP;
         const int quad = warp & 3;                  // TMEM lanes this warp may touch: [32*quad, +32)
         const int half = C::EPI_WARPS == 8 ? ew / 4 : 0;
         const int r_in_tile = quad * 32 + lane;
@@ -388,9 +401,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 if (lane == 0) mbar_arrive(&tmem_empty[buf]);
                 ++acc_iter;
             } else {
-                float acc[128];
+                // 128 fp32 accumulators per thread, kept as 64 packed pairs for FFMA2.
+                uint64_t acc[64];
 #pragma unroll
-                for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
+                for (int i = 0; i < 64; ++i) acc[i] = 0ull;
                 // Block row of Bs for this thread's columns (two of them with fused SiLU).
                 const float* bs_e = p.sb + (int64_t)expert * p.bs_stride_e;
                 int nb0, nb1;
@@ -404,32 +418,46 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 nb0 = min(nb0, max_nb);
                 nb1 = min(nb1, max_nb);
                 const float* as_row = p.sa + srow * p.ld_as;
-                float as_next = as_row[0];
+                const float* bs0 = bs_e + nb0 * p.bs_stride_n;
+                const float* bs1 = bs_e + nb1 * p.bs_stride_n;
+                float as_next = as_row[0], b0_next = __ldg(bs0), b1_next = FUSE_SILU ? __ldg(bs1) : 0.0f;
+                auto chunk_col = [&](int c) -> uint32_t {
+                    if constexpr (FUSE_SILU) return (uint32_t)((c < 2 ? 0 : BN / 2) + 64 * half + 32 * (c & 1));
+                    else return (uint32_t)(128 * half + 32 * c);
+                };
                 for (int kb = 0; kb < num_k_blocks; ++kb) {
-                    const float a_s = as_next;
-                    if (kb + 1 < num_k_blocks) as_next = as_row[kb + 1];
-                    const float sc0 = a_s * __ldg(bs_e + nb0 * p.bs_stride_n + kb * p.bs_stride_k);
-                    const float sc1 = FUSE_SILU ? a_s * __ldg(bs_e + nb1 * p.bs_stride_n + kb * p.bs_stride_k) : sc0;
+                    const float sc0f = as_next * b0_next;
+                    const float sc1f = FUSE_SILU ? as_next * b1_next : sc0f;
+                    if (kb + 1 < num_k_blocks) {  // next block's scales travel while this block is folded in
+                        as_next = as_row[kb + 1];
+                        b0_next = __ldg(bs0 + (int64_t)(kb + 1) * p.bs_stride_k);
+                        if constexpr (FUSE_SILU) b1_next = __ldg(bs1 + (int64_t)(kb + 1) * p.bs_stride_k);
+                    }
+                    const uint64_t sc0 = pack_f32x2(sc0f, sc0f), sc1 = pack_f32x2(sc1f, sc1f);
                     const uint32_t buf = acc_iter & 1u;
                     ok = mbar_wait(&tmem_full[buf], (acc_iter >> 1) & 1u, abort_flag, p.status, 5);
                     if (!ok) break;
                     tc_fence_after_sync();
                     const uint32_t tbuf = lane_addr + buf * BN;
+                    // Two staging buffers: the load of chunk c+1 is in flight while chunk c is folded.
+                    uint32_t raw[2][32];
+                    tmem_ld_32x32b_x32(tbuf + chunk_col(0), raw[0]);
+                    tmem_ld_wait();
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
-                        uint32_t raw[32];
-                        uint32_t tcol;
-                        if constexpr (FUSE_SILU) tcol = (c < 2 ? 0 : BN / 2) + 64 * half + 32 * (c & 1);
-                        else tcol = 128 * half + 32 * c;
-                        tmem_ld_32x32b_x32(tbuf + tcol, raw);
-                        tmem_ld_wait();
-                        const float sc = (FUSE_SILU && c >= 2) ? sc1 : sc0;
+                        if (c < 3) tmem_ld_32x32b_x32(tbuf + chunk_col(c + 1), raw[(c + 1) & 1]);
+                        const uint64_t sc = (FUSE_SILU && c >= 2) ? sc1 : sc0;
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) acc[32 * c + i] = fmaf(__uint_as_float(raw[i]), sc, acc[32 * c + i]);
+                        for (int i = 0; i < 16; ++i) ffma2(acc[16 * c + i], raw[c & 1][2 * i], raw[c & 1][2 * i + 1], sc);
+                        if (c < 3) tmem_ld_wait();
+                        if (c == 2) {
+                            // Every column of this buffer is now in registers: hand it back to the
+                            // MMA warp before the last chunk is folded.
+                            tc_fence_before_sync();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+                        }
                     }
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&tmem_empty[buf]);
                     ++acc_iter;
                 }
                 if (!ok) break;
@@ -438,9 +466,16 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     const int col = out_col_base + 32 * c;
                     float v[32];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        if constexpr (FUSE_SILU) v[i] = silu_mul(acc[32 * c + i], acc[64 + 32 * c + i]);
-                        else v[i] = acc[32 * c + i] * weight;
+                    for (int i = 0; i < 16; ++i) {
+                        const uint64_t a = acc[16 * c + i];
+                        if constexpr (FUSE_SILU) {
+                            const uint64_t u = acc[32 + 16 * c + i];
+                            v[2 * i] = silu_mul(f32x2_lo(a), f32x2_lo(u));
+                            v[2 * i + 1] = silu_mul(f32x2_hi(a), f32x2_hi(u));
+                        } else {
+                            v[2 * i] = f32x2_lo(a) * weight;
+                            v[2 * i + 1] = f32x2_hi(a) * weight;
+                        }
                     }
                     const int nc = min(32, p.n_out - col);
                     if (row_ok && nc > 0) store_chunk(out_ptr, col, v, nc, p.out_dtype, p.c_vec_ok);

@@ -153,6 +153,31 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
         : "r"(taddr)
         : "memory");
 }
+// Packed fp32 pair: acc.{lo,hi} += v.{lo,hi} * scale.{lo,hi} in one issue slot (sm_100 FFMA2).
+__device__ __forceinline__ void ffma2(uint64_t& acc, uint32_t v_lo, uint32_t v_hi, uint64_t scale2) {
+    uint64_t v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(v_lo), "r"(v_hi));
+    // volatile: must stay behind the tcgen05.wait::ld that makes v_lo/v_hi valid
+    asm volatile("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(v), "l"(scale2));
+}
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+    uint64_t v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(__float_as_uint(lo)), "r"(__float_as_uint(hi)));
+    return v;
+}
+__device__ __forceinline__ float f32x2_lo(uint64_t v) { return __uint_as_float((uint32_t)(v & 0xffffffffull)); }
+__device__ __forceinline__ float f32x2_hi(uint64_t v) { return __uint_as_float((uint32_t)(v >> 32)); }
+
+// Register-file rebalancing between warpgroups (all four warps of a warpgroup must execute it).
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 }  // namespace fgptx

@@ -101,35 +101,40 @@ __device__ __forceinline__ int64_t source_row(const QuantArgs& a, int64_t r) {
 }
 
 // ---- small groups: a team of TPG lanes owns one group of TPG*8*VPT elements -------------
+// Groups are numbered row-major (row * groups_per_row + column group).  A team walks them with
+// a constant stride and keeps (row, column group) incrementally: no division in the loop.
 template <typename T, int MODE, int TPG, int VPT>
 __global__ void __launch_bounds__(256) group_quant_kernel(QuantArgs a) {
     constexpr int UNROLL = 2;
     constexpr int GROUP = TPG * 8 * VPT;
     const int64_t rows = resolve_rows(a);
-    const int64_t gpr = a.K / GROUP;
+    const int gpr = (int)(a.K / GROUP);
     const int64_t total = rows * gpr;
     const int lane_in_team = threadIdx.x % TPG;
     const int64_t team = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / TPG;
     const int64_t teams = (int64_t)gridDim.x * blockDim.x / TPG;
+    const int64_t stride = teams * UNROLL;
     const T* x = reinterpret_cast<const T*>(a.x);
-    // Loop bounds are uniform across the warp (first team of the warp decides).
+    // Trip count from the first team of the warp, so the whole warp runs the same iterations.
     const int64_t warp_first = team - (threadIdx.x % 32) / TPG;
-    for (int64_t base = 0; warp_first + base < total; base += teams * UNROLL) {
+    const int64_t iters = warp_first < total ? (total - warp_first + stride - 1) / stride : 0;
+    const int step_row = (int)(stride / gpr), step_cg = (int)(stride % gpr);
+    int row[UNROLL], cg[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+        const int64_t g0 = team + (int64_t)u * teams;
+        row[u] = (int)(g0 / gpr);
+        cg[u] = (int)(g0 % gpr);
+    }
+    for (int64_t it = 0; it < iters; ++it) {
         float v[UNROLL][VPT][8];
-        int64_t g[UNROLL];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            g[u] = team + base + (int64_t)u * teams;
-            const bool live = g[u] < total;
-            int64_t src = -1, cg = 0;
-            if (live) {
-                cg = g[u] % gpr;
-                src = source_row(a, g[u] / gpr);
-            }
+            const int64_t src = row[u] < rows ? source_row(a, row[u]) : -1;
 #pragma unroll
             for (int w = 0; w < VPT; ++w) {
                 if (src >= 0) {
-                    fg_load8(x + src * a.ld_x + cg * GROUP + (w * TPG + lane_in_team) * 8, v[u][w]);
+                    fg_load8(x + src * a.ld_x + cg[u] * GROUP + (w * TPG + lane_in_team) * 8, v[u][w]);
                 } else {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) v[u][w][i] = 0.0f;
@@ -147,17 +152,22 @@ __global__ void __launch_bounds__(256) group_quant_kernel(QuantArgs a) {
             for (int o = TPG / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
             const float s = make_scale<MODE>(amax, a.eps, a.pow2);
             const Divider d = make_divider<MODE>(s);
-            if (g[u] < total) {
-                const int64_t row = g[u] / gpr, cg = g[u] % gpr;
+            if (row[u] < rows) {
 #pragma unroll
                 for (int w = 0; w < VPT; ++w) {
                     float q[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) q[i] = apply_divider<MODE>(v[u][w][i], d);
-                    *reinterpret_cast<uint2*>(a.q + row * a.ld_q + cg * GROUP + (w * TPG + lane_in_team) * 8) =
-                        fg_pack_e4m3x8(q);
+                    *reinterpret_cast<uint2*>(a.q + (int64_t)row[u] * a.ld_q + cg[u] * GROUP +
+                                              (w * TPG + lane_in_team) * 8) = fg_pack_e4m3x8(q);
                 }
-                if (lane_in_team == 0) a.s[row * a.s_row_stride + cg * a.s_col_stride] = s;
+                if (lane_in_team == 0) a.s[(int64_t)row[u] * a.s_row_stride + (int64_t)cg[u] * a.s_col_stride] = s;
+            }
+            cg[u] += step_cg;
+            row[u] += step_row;
+            if (cg[u] >= gpr) {
+                cg[u] -= gpr;
+                row[u] += 1;
             }
         }
     }

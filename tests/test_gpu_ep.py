@@ -1,0 +1,84 @@
+"""Expert-parallel layer on real GPUs (NCCL): every rank's output must equal the single-GPU layer
+on the same tokens bit for bit, and the single-GPU layer must match the CPU oracle."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from tests.test_ep_gloo import expected, make_case  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+def _layer_single(case, dev):
+    from flaggems_b200.ep import ExpertParallelMoE
+
+    hidden, w1, w2, s1, s2, tw, ti, shared = case
+    layer = ExpertParallelMoE(w1.to(dev), w2.to(dev), s1.to(dev), s2.to(dev), w1.shape[0],
+                              shared=tuple(t.to(dev) for t in shared))
+    return layer(hidden.to(dev), tw.to(dev), ti.to(dev))
+
+
+def test_single_gpu_layer_matches_oracle():
+    case = make_case(seed=5, t=160, h=512, i=256, e=16, topk=4)
+    out = _layer_single(case, torch.device("cuda", 0))
+    ref = expected(case).float()
+    torch.testing.assert_close(out.cpu().float(), ref, rtol=1e-2, atol=max(1e-2, 1e-2 * float(ref.abs().max())))
+
+
+def _worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from flaggems_b200 import _cabi
+        from flaggems_b200.ep import ExpertParallelMoE
+
+        case = make_case(seed=5, t=160, h=512, i=256, e=16, topk=4)
+        hidden, w1, w2, s1, s2, tw, ti, shared = case
+        e, t = w1.shape[0], hidden.shape[0]
+        el, tl = e // world, t // world
+        lo = rank * el
+        layer = ExpertParallelMoE(w1[lo:lo + el].to(dev), w2[lo:lo + el].to(dev), s1[lo:lo + el].to(dev),
+                                  s2[lo:lo + el].to(dev), e, rank, world, shared=tuple(x.to(dev) for x in shared))
+        sl = slice(rank * tl, (rank + 1) * tl)
+        outs = [layer(hidden[sl].to(dev), tw[sl].to(dev), ti[sl].to(dev)) for _ in range(2)]
+        single = _layer_single(case, dev)[sl]
+        q.put((rank, bool(torch.equal(outs[0], single)), bool(torch.equal(outs[0], outs[1])),
+               float((outs[0].float() - single.float()).abs().max()), _cabi.device_status()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_ep_equals_single_gpu(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=500) for _ in range(world))
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    for rank, equal, repeat, err, status in res:
+        assert status == 0
+        assert repeat, f"rank {rank}: two runs differ"
+        assert equal, f"rank {rank}: differs from the single-GPU layer, max abs err {err}"
