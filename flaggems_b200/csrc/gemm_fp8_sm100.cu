@@ -439,24 +439,22 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     if (!ok) break;
                     tc_fence_after_sync();
                     const uint32_t tbuf = lane_addr + buf * BN;
-                    // Two staging buffers: the load of chunk c+1 is in flight while chunk c is folded.
-                    uint32_t raw[2][32];
-                    tmem_ld_32x32b_x32(tbuf + chunk_col(0), raw[0]);
-                    tmem_ld_wait();
+                    // Two rounds of 64 columns: one load instruction, one wait, 32 packed FMAs each.
+                    uint32_t raw[64];
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        if (c < 3) tmem_ld_32x32b_x32(tbuf + chunk_col(c + 1), raw[(c + 1) & 1]);
-                        const uint64_t sc = (FUSE_SILU && c >= 2) ? sc1 : sc0;
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) ffma2(acc[16 * c + i], raw[c & 1][2 * i], raw[c & 1][2 * i + 1], sc);
-                        if (c < 3) tmem_ld_wait();
-                        if (c == 2) {
+                    for (int r = 0; r < 2; ++r) {
+                        tmem_ld_32x32b_x64(tbuf + chunk_col(2 * r), raw);
+                        tmem_ld_wait();
+                        if (r == 1) {
                             // Every column of this buffer is now in registers: hand it back to the
-                            // MMA warp before the last chunk is folded.
+                            // MMA warp before the last half is folded.
                             tc_fence_before_sync();
                             __syncwarp();
                             if (lane == 0) mbar_arrive(&tmem_empty[buf]);
                         }
+                        const uint64_t sc = (FUSE_SILU && r == 1) ? sc1 : sc0;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) ffma2(acc[32 * r + i], raw[2 * i], raw[2 * i + 1], sc);
                     }
                     ++acc_iter;
                 }
