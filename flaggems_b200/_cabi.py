@@ -35,7 +35,17 @@ _SIGS = {
     "fg_moe_sum": (c_int, [_P, _P, c_int64, c_int, c_int64, c_int, _P]),
     "fg_moe_sum_indexed": (c_int, [_P, _P, c_int64, c_int, c_int64, c_int, _P, _P, _P]),
     "fg_gather_rows_fp8": (
-        c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, _P, c_int32, c_int32, _P, _P]),
+        c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int64, _P, c_int32, c_int32, _P, _P]),
+    "fg_moe_align_block_size_ex": (
+        c_int, [_P, c_int, c_int64, c_int, c_int, _P, c_int, _P, c_int64, _P, c_int64, _P, c_int64, c_int, _P, _P]),
+    "fg_ep_pack_rows_fp8": (
+        c_int, [_P, c_int, c_int64, c_int64, c_int64, _P, c_int, _P, c_int, c_int, c_int, _P, _P, c_int64, _P, _P]),
+    "fg_moe_routed_workspace_bytes": (c_int64, [c_int64, c_int, c_int64, c_int64]),
+    "fg_moe_routed_block_fp8_local": (
+        c_int, [_P, _P, c_int, _P, c_int, _P, c_int, c_int64, c_int, _P, _P, _P, _P, c_int, c_int64, c_int64,
+                _P, c_int64, _P]),
+    "fg_moe_routed_block_fp8_packed": (
+        c_int, [_P, _P, c_int64, c_int64, _P, _P, _P, _P, c_int, c_int64, c_int64, _P, c_int64, c_int, _P]),
     "fg_scaled_mm_fp8": (
         c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                 c_int, c_int, c_int, c_int, _P]),
@@ -43,7 +53,7 @@ _SIGS = {
         c_int, [_P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                 c_int64, c_int64, c_int, _P]),
     "fg_moe_grouped_gemm_fp8": (
-        c_int, [_P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, c_int64, c_int64, c_int, c_int64, c_int64,
+        c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int64, _P, _P, _P, c_int64, c_int64, c_int, c_int64, c_int64,
                 c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P]),
 }
 
@@ -91,6 +101,25 @@ def ptr(t):
 
 def stream_ptr(device=None):
     return torch.cuda.current_stream(device).cuda_stream
+
+
+class _NoGuard:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def device_guard(t):
+    """Context that makes t's device current; free when it already is."""
+    idx = t.device.index
+    if idx is None or idx == torch.cuda.current_device():
+        return _NO_GUARD
+    return torch.cuda.device(idx)
 
 
 def require_cuda(*tensors):

@@ -60,6 +60,7 @@ struct GemmParams {
     int scatter, mul_weight;
     const void* topk_w;
     int topk_w_dtype;
+    int64_t topk_w_stride;  // elements between the weights of consecutive route slots
     unsigned int* status;
 };
 
@@ -321,7 +322,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                         row_ok = real;
                         out_row = sid;
                     }
-                    if (p.mul_weight && real) weight = load_as_float(p.topk_w, p.topk_w_dtype, sid);
+                    if (p.mul_weight && real) weight = load_as_float(p.topk_w, p.topk_w_dtype, (int64_t)sid * p.topk_w_stride);
                 }
             } else {
                 row_ok = row < p.M;
@@ -633,7 +634,8 @@ int fg_block_scaled_mm_fp8(void* c, const void* a, const void* b, const float* a
 }
 
 int fg_moe_grouped_gemm_fp8(void* c, const void* a, const void* w, const float* a_scale, const float* w_scale,
-                            const void* topk_weights, int topk_w_dtype, const int32_t* sorted_ids,
+                            const void* topk_weights, int topk_w_dtype, int64_t topk_w_stride,
+                            const int32_t* sorted_ids,
                             const int32_t* expert_ids, const int32_t* num_post_pad, int64_t max_rows, int64_t numel,
                             int num_experts, int64_t N, int64_t K, int64_t ld_a, int64_t ld_c, int block_rows,
                             int scale_mode, int a_scale_per_row, int fuse_silu, int scatter, int mul_weight,
@@ -667,7 +669,7 @@ int fg_moe_grouped_gemm_fp8(void* c, const void* a, const void* w, const float* 
     }
     p.grouped = 1; p.sorted_ids = sorted_ids; p.expert_ids = expert_ids; p.num_post_pad = num_post_pad;
     p.block_rows = block_rows; p.numel = numel; p.scatter = scatter; p.mul_weight = mul_weight;
-    p.topk_w = topk_weights; p.topk_w_dtype = topk_w_dtype;
+    p.topk_w = topk_weights; p.topk_w_dtype = topk_w_dtype; p.topk_w_stride = topk_w_stride > 0 ? topk_w_stride : 1;
     return launch_gemm(p, a, p.M, ld_a, w, num_experts, K, block, fuse_silu != 0, (cudaStream_t)stream);
 }
 

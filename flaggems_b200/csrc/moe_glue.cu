@@ -34,6 +34,9 @@ struct AlignArgs {
     int32_t* expert_ids;
     int64_t n_blocks;
     int32_t* num_post_pad;
+    int64_t ids_stride;       // elements between consecutive ids (1 = dense)
+    int32_t id_div;           // bucket = id / id_div
+    int32_t* expert_counts;   // nullable: rows per bucket before padding
 };
 
 template <typename IdT>
@@ -71,7 +74,7 @@ __global__ void __launch_bounds__(ALIGN_THREADS, 1) moe_align_kernel(AlignArgs a
         const int64_t i = i0 + lane;
         int e = -1;
         if (i < seg_end) {
-            const long long v = (long long)ids[i];
+            const long long v = (long long)ids[i * a.ids_stride] / a.id_div;
             if (v >= 0 && v < E) e = (int)v;
         }
         const unsigned peers = __match_any_sync(0xffffffffu, e);
@@ -133,6 +136,7 @@ __global__ void __launch_bounds__(ALIGN_THREADS, 1) moe_align_kernel(AlignArgs a
         base[e0] = offset + before;
         pad_lo[e0] = offset + total;
         pad_hi[e0] = offset + padded;
+        if (a.expert_counts && rank == 0) a.expert_counts[e0] = total;
     }
     __syncthreads();
     const int32_t total_padded = total_padded_s;
@@ -163,7 +167,7 @@ __global__ void __launch_bounds__(ALIGN_THREADS, 1) moe_align_kernel(AlignArgs a
         const int64_t i = i0 + lane;
         int e = -1;
         if (i < seg_end) {
-            const long long v = (long long)ids[i];
+            const long long v = (long long)ids[i * a.ids_stride] / a.id_div;
             if (v >= 0 && v < E) e = (int)v;
         }
         const unsigned peers = __match_any_sync(0xffffffffu, e);
@@ -231,7 +235,8 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(const T* __restrict__ in, 
 __global__ void __launch_bounds__(256) gather_rows_kernel(const uint8_t* __restrict__ src_q,
                                                           const float* __restrict__ src_s, uint8_t* __restrict__ dst_q,
                                                           float* __restrict__ dst_s, int64_t rows, int64_t K,
-                                                          int64_t s_cols, const int32_t* __restrict__ row_index,
+                                                          int64_t s_cols, int64_t src_q_stride, int64_t src_s_stride,
+                                                          const int32_t* __restrict__ row_index,
                                                           int32_t index_div, int32_t index_limit,
                                                           const int32_t* __restrict__ n_rows_dev) {
     if (n_rows_dev) {
@@ -245,10 +250,10 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint8_t* __restr
         const int32_t idx = row_index[r];
         const bool real = idx >= 0 && idx < index_limit;
         const int64_t src = real ? idx / index_div : 0;
-        const uint4* sq = reinterpret_cast<const uint4*>(src_q + src * K);
+        const uint4* sq = reinterpret_cast<const uint4*>(src_q + src * src_q_stride);
         uint4* dq = reinterpret_cast<uint4*>(dst_q + r * K);
         for (int64_t v = lane; v < K / 16; v += 32) dq[v] = real ? sq[v] : make_uint4(0u, 0u, 0u, 0u);
-        for (int64_t v = lane; v < s_cols; v += 32) dst_s[r * s_cols + v] = real ? src_s[src * s_cols + v] : 1.0f;
+        for (int64_t v = lane; v < s_cols; v += 32) dst_s[r * s_cols + v] = real ? src_s[src * src_s_stride + v] : 1.0f;
     }
 }
 
@@ -267,6 +272,16 @@ extern "C" {
 int fg_moe_align_block_size(const void* topk_ids, int ids_are_i64, int64_t numel, int num_experts, int block_size,
                             const int32_t* expert_map, int expert_map_len, int32_t* sorted_ids, int64_t max_pad,
                             int32_t* expert_ids, int64_t n_blocks, int32_t* num_post_pad, void* stream) {
+    return fg_moe_align_block_size_ex(topk_ids, ids_are_i64, numel, num_experts, block_size, expert_map,
+                                      expert_map_len, sorted_ids, max_pad, expert_ids, n_blocks, num_post_pad, 1, 1,
+                                      nullptr, stream);
+}
+
+int fg_moe_align_block_size_ex(const void* topk_ids, int ids_are_i64, int64_t numel, int num_experts, int block_size,
+                               const int32_t* expert_map, int expert_map_len, int32_t* sorted_ids, int64_t max_pad,
+                               int32_t* expert_ids, int64_t n_blocks, int32_t* num_post_pad, int64_t ids_stride,
+                               int id_div, int32_t* expert_counts, void* stream) {
+    FG_REQUIRE(ids_stride >= 1 && id_div >= 1, FG_ERR_INVALID_ARGUMENT, "ids_stride and id_div must be >= 1");
     FG_REQUIRE(numel >= 0 && num_experts > 0 && block_size > 0, FG_ERR_INVALID_ARGUMENT,
                "numel %lld, num_experts %d, block_size %d", (long long)numel, num_experts, block_size);
     FG_REQUIRE(num_experts <= ALIGN_THREADS, FG_ERR_UNSUPPORTED, "num_experts %d exceeds the supported maximum %d",
@@ -283,7 +298,7 @@ int fg_moe_align_block_size(const void* topk_ids, int ids_are_i64, int64_t numel
                "expert_map has %d entries for %d experts", expert_map_len, num_experts);
 
     AlignArgs a{topk_ids, numel, num_experts, block_size, expert_map, expert_map_len,
-                sorted_ids, max_pad, expert_ids, n_blocks, num_post_pad};
+                sorted_ids, max_pad, expert_ids, n_blocks, num_post_pad, ids_stride, id_div, expert_counts};
     // One CTA handles 32 warps x 128 slots comfortably; grow the cluster with numel up to 8.
     int ranks = 1;
     while (ranks < 8 && (int64_t)ranks * ALIGN_THREADS * 4 < numel) ranks *= 2;
@@ -377,8 +392,10 @@ int fg_moe_sum(const void* in, void* out, int64_t M, int topk, int64_t K, int dt
 }
 
 int fg_gather_rows_fp8(const void* src_q, const float* src_s, void* dst_q, float* dst_s, int64_t rows, int64_t K,
-                       int64_t s_cols, const int32_t* row_index, int32_t index_div, int32_t index_limit,
-                       const int32_t* n_rows_dev, void* stream) {
+                       int64_t s_cols, int64_t src_q_stride, int64_t src_s_stride, const int32_t* row_index,
+                       int32_t index_div, int32_t index_limit, const int32_t* n_rows_dev, void* stream) {
+    FG_REQUIRE(src_q_stride >= K && src_q_stride % 16 == 0 && src_s_stride >= s_cols, FG_ERR_INVALID_ARGUMENT,
+               "bad source strides");
     FG_REQUIRE(rows >= 0 && K >= 0 && s_cols >= 0, FG_ERR_INVALID_ARGUMENT, "negative size");
     if (rows == 0) return FG_OK;
     FG_REQUIRE(src_q && dst_q && row_index && index_div > 0 && (s_cols == 0 || (src_s && dst_s)),
@@ -389,8 +406,8 @@ int fg_gather_rows_fp8(const void* src_q, const float* src_s, void* dst_q, float
     const int64_t cap = (int64_t)fg_num_sms() * 8;
     if (blocks > cap) blocks = cap;
     gather_rows_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
-        (const uint8_t*)src_q, src_s, (uint8_t*)dst_q, dst_s, rows, K, s_cols, row_index, index_div, index_limit,
-        n_rows_dev);
+        (const uint8_t*)src_q, src_s, (uint8_t*)dst_q, dst_s, rows, K, s_cols, src_q_stride, src_s_stride, row_index,
+        index_div, index_limit, n_rows_dev);
     fg_count_launch(1);
     FG_LAUNCH_CHECK();
     return FG_OK;

@@ -30,7 +30,30 @@ struct QuantArgs {
     int32_t index_div;
     int32_t index_limit;
     const int32_t* n_rows_dev;  // nullable
+    // Optional per-row trailer of the expert-parallel dispatch format (see fg_ep_pack_rows_fp8):
+    // written once per output row at byte offset meta_off of the row of q.
+    const void* meta_ids;  // nullable: route slot -> global expert id
+    int meta_ids_i64;
+    const void* meta_w;  // route slot -> router weight
+    int meta_w_dtype;
+    int32_t meta_mod;  // experts per rank
+    int64_t meta_off;
+    int32_t* inv;  // nullable: inv[route slot] = output row
 };
+
+__device__ __forceinline__ void write_row_meta(const QuantArgs& a, int64_t out_row) {
+    const int32_t slot = a.row_index[out_row];
+    const long long e = a.meta_ids_i64 ? (long long)reinterpret_cast<const int64_t*>(a.meta_ids)[slot]
+                                       : (long long)reinterpret_cast<const int32_t*>(a.meta_ids)[slot];
+    float w;
+    if (a.meta_w_dtype == FG_DTYPE_BF16) w = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.meta_w)[slot]);
+    else if (a.meta_w_dtype == FG_DTYPE_F16) w = __half2float(reinterpret_cast<const __half*>(a.meta_w)[slot]);
+    else w = reinterpret_cast<const float*>(a.meta_w)[slot];
+    uint8_t* m = a.q + out_row * a.ld_q + a.meta_off;
+    *reinterpret_cast<int32_t*>(m) = (int32_t)(e % a.meta_mod);
+    *reinterpret_cast<float*>(m + 4) = w;
+    if (a.inv) a.inv[slot] = (int32_t)out_row;
+}
 
 __device__ __forceinline__ float ceil_pow2_bits(float v) {
     // 2^ceil(log2(v)) for positive normal v: bump the exponent when any mantissa bit is set.
@@ -161,7 +184,10 @@ __global__ void __launch_bounds__(256) group_quant_kernel(QuantArgs a) {
                     *reinterpret_cast<uint2*>(a.q + (int64_t)row[u] * a.ld_q + cg[u] * GROUP +
                                               (w * TPG + lane_in_team) * 8) = fg_pack_e4m3x8(q);
                 }
-                if (lane_in_team == 0) a.s[(int64_t)row[u] * a.s_row_stride + (int64_t)cg[u] * a.s_col_stride] = s;
+                if (lane_in_team == 0) {
+                    a.s[(int64_t)row[u] * a.s_row_stride + (int64_t)cg[u] * a.s_col_stride] = s;
+                    if (a.meta_ids && cg[u] == 0) write_row_meta(a, row[u]);
+                }
             }
             cg[u] += step_cg;
             row[u] += step_row;
@@ -340,6 +366,29 @@ int fg_per_token_group_quant_fp8_gather(const void* x, int x_dtype, void* q, flo
     a.eps = 1e-10f; a.pow2 = 0;
     a.row_index = row_index; a.index_div = index_div; a.index_limit = index_limit; a.n_rows_dev = n_rows_dev;
     FG_REQUIRE(row_index == nullptr || index_div > 0, FG_ERR_INVALID_ARGUMENT, "index_div must be positive");
+    int rc = check_common(a, x_dtype);
+    if (rc != FG_OK) return rc;
+    return launch_quant<QM_GROUP>(x_dtype, a, (cudaStream_t)stream);
+}
+
+int fg_ep_pack_rows_fp8(const void* x, int x_dtype, int64_t T, int64_t K, int64_t ld_x, const void* topk_ids,
+                        int ids_are_i64, const void* topk_w, int topk_w_dtype, int topk, int experts_per_rank,
+                        const int32_t* order, void* packed, int64_t row_bytes, int32_t* inv, void* stream) {
+    FG_REQUIRE(T >= 0 && K > 0 && topk > 0 && experts_per_rank > 0, FG_ERR_INVALID_ARGUMENT, "bad sizes");
+    FG_REQUIRE(K % 128 == 0, FG_ERR_UNSUPPORTED, "row length %lld must be a multiple of 128", (long long)K);
+    FG_REQUIRE(row_bytes >= K + 4 * (K / 128) + 8 && row_bytes % 16 == 0, FG_ERR_INVALID_ARGUMENT,
+               "row_bytes %lld too small or not a multiple of 16", (long long)row_bytes);
+    FG_REQUIRE(T * topk < (1ll << 31), FG_ERR_UNSUPPORTED, "too many route slots");
+    if (T == 0) return FG_OK;
+    FG_REQUIRE(x && topk_ids && topk_w && order && packed, FG_ERR_INVALID_ARGUMENT, "null pointer");
+    QuantArgs a{};
+    a.x = x; a.q = (uint8_t*)packed; a.s = reinterpret_cast<float*>((uint8_t*)packed + K);
+    a.rows = T * topk; a.K = K; a.group = 128;
+    a.ld_x = ld_x; a.ld_q = row_bytes; a.s_row_stride = row_bytes / 4; a.s_col_stride = 1;
+    a.eps = 1e-10f; a.pow2 = 0;
+    a.row_index = order; a.index_div = topk; a.index_limit = (int32_t)(T * topk); a.n_rows_dev = nullptr;
+    a.meta_ids = topk_ids; a.meta_ids_i64 = ids_are_i64; a.meta_w = topk_w; a.meta_w_dtype = topk_w_dtype;
+    a.meta_mod = experts_per_rank; a.meta_off = K + 4 * (K / 128); a.inv = inv;
     int rc = check_common(a, x_dtype);
     if (rc != FG_OK) return rc;
     return launch_quant<QM_GROUP>(x_dtype, a, (cudaStream_t)stream);

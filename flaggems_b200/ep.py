@@ -35,8 +35,37 @@ from .ops.per_token_group_quant_fp8 import per_token_group_quant_fp8
 from .ops.w8a8_block_fp8_matmul import w8a8_block_fp8_matmul
 
 
+def balanced_expert_placement(counts: torch.Tensor, world: int) -> torch.Tensor:
+    """Static expert placement from routing statistics: returns ``slot`` with
+    ``slot[logical_expert] = rank * E_loc + local_index`` such that every rank holds exactly
+    E/world experts and the routed rows per rank are as even as a greedy longest-first
+    assignment makes them.  With a skewed router (a few experts take most of the rows) the
+    contiguous placement leaves one rank with several times the average load; the layer's
+    step time is the slowest rank's.  The placement only renames experts: per-row arithmetic
+    is untouched."""
+    e = counts.numel()
+    assert e % world == 0
+    cap = e // world
+    load = [0] * world
+    used = [0] * world
+    slot = torch.empty(e, dtype=torch.int64)
+    for ex in torch.argsort(counts.cpu(), descending=True, stable=True).tolist():
+        r = min((r for r in range(world) if used[r] < cap), key=lambda r: (load[r], r))
+        slot[ex] = r * cap + used[r]
+        used[r] += 1
+        load[r] += int(counts[ex])
+    return slot
+
+
+def packed_row_bytes(hidden: int) -> int:
+    """Bytes of one dispatch row: FP8 payload, 1x128 group scales, int32 local expert, fp32 router
+    weight, padded to 16 bytes (so that rows can be read by TMA where they land)."""
+    return (hidden + 4 * (hidden // 128) + 8 + 15) // 16 * 16
+
+
 class CudaMoEOps:
-    """Device work of the layer: every method launches kernels of the C-ABI library."""
+    """Device work of the layer: every method launches kernels of the C-ABI library.  Workspaces
+    are cached between steps, so a steady-state step allocates only its outputs."""
 
     def __init__(self, w1, w2, w1_scale, w2_scale, shared=None):
         self.w1, self.w2 = w1, w2
@@ -46,56 +75,64 @@ class CudaMoEOps:
         self.num_local_experts = w1.shape[0]
         self.inter = w2.shape[2]
         self.hidden = w1.shape[2]
+        self.row_bytes = packed_row_bytes(self.hidden)
+        self._ws = None
 
-    def route_order(self, dest, world):
-        """Route slots ordered by destination rank, ascending slot index inside a rank."""
-        order, _, _ = moe_align_block_size(dest, 1, world)
-        return order[: dest.numel()]
+    def _workspace(self, n_rows, device):
+        need = _cabi.lib().fg_moe_routed_workspace_bytes(n_rows, self.num_local_experts, self.hidden, self.inter)
+        if self._ws is None or self._ws.numel() < need or self._ws.device != device:
+            self._ws = torch.empty(int(need * 1.25) + 256, dtype=torch.uint8, device=device)
+        return self._ws
 
-    def local_routed(self, hidden, topk_ids, weight, topk):
-        """Single-rank form: all experts are local, rows go straight into expert-sorted order.
-        Returns the routed results as [T*topk, H] in route-slot order."""
-        t = hidden.shape[0]
+    def plan_and_pack(self, hidden, topk_ids, topk_w, world):
+        """Orders the route slots by destination rank (stable), counts rows per destination and
+        writes the packed dispatch rows in that order.  Returns (packed [numel, row_bytes] uint8,
+        counts int32 [world] on the device, inv int32 [numel]: row of each route slot)."""
+        t, topk = topk_ids.shape
         numel = t * topk
-        sorted_ids, expert_ids, post_pad = moe_align_block_size(topk_ids, _TILE_ROWS, self.num_local_experts)
-        rows = sorted_ids.numel() // _TILE_ROWS * _TILE_ROWS
-        a1, a1s = _group_quant(hidden, 128, sorted_ids, topk, numel, post_pad, rows)
-        act = torch.empty((rows, self.inter), dtype=hidden.dtype, device=hidden.device)
-        _grouped_gemm(act, a1, self.w1, a1s, self.w1_scale, None, sorted_ids, expert_ids, post_pad, numel,
-                      _cabi.SCALE_BLOCK, fuse_silu=True, scatter=False, mul_weight=False)
-        a2, a2s = _group_quant(act, 128, None, 1, 0, post_pad, rows)
-        y = torch.empty((numel, self.w2.shape[1]), dtype=hidden.dtype, device=hidden.device)
-        _grouped_gemm(y, a2, self.w2, a2s, self.w2_scale, weight, sorted_ids, expert_ids, post_pad, numel,
-                      _cabi.SCALE_BLOCK, fuse_silu=False, scatter=True, mul_weight=True)
-        return y
+        dev = hidden.device
+        order = torch.empty(numel, dtype=torch.int32, device=dev)
+        blocks = torch.empty(numel + 1, dtype=torch.int32, device=dev)
+        meta = torch.empty(world + 1, dtype=torch.int32, device=dev)  # [0]: post_pad, [1:]: counts
+        inv = torch.empty(numel, dtype=torch.int32, device=dev)
+        packed = torch.empty((numel, self.row_bytes), dtype=torch.uint8, device=dev)
+        L, st = _cabi.lib(), _cabi.stream_ptr(dev)
+        ids64 = 1 if topk_ids.dtype == torch.int64 else 0
+        _cabi.check(L.fg_moe_align_block_size_ex(
+            _cabi.ptr(topk_ids), ids64, numel, world, 1, None, 0, _cabi.ptr(order), numel, _cabi.ptr(blocks),
+            numel + 1, _cabi.ptr(meta), 1, self.num_local_experts, meta.data_ptr() + 4, st))
+        _cabi.check(L.fg_ep_pack_rows_fp8(
+            _cabi.ptr(hidden), _cabi.DTYPE_CODE[hidden.dtype], t, self.hidden, hidden.stride(0),
+            _cabi.ptr(topk_ids), ids64, _cabi.ptr(topk_w), _cabi.DTYPE_CODE[topk_w.dtype], topk,
+            self.num_local_experts, _cabi.ptr(order), _cabi.ptr(packed), self.row_bytes, _cabi.ptr(inv), st))
+        return packed, meta[1:], inv
 
-    def quant_gather(self, hidden, order, topk):
-        numel = order.numel()
-        return _group_quant(hidden, 128, order, topk, hidden.shape[0] * topk, None, numel)
-
-    def expert_compute(self, xq, xs, local_expert, weight, out_dtype):
-        """xq/xs: R received FP8 rows + scales, local_expert int32 [R], weight fp32 [R]."""
-        r = xq.shape[0]
-        y = torch.empty((r, self.w2.shape[1]), dtype=out_dtype, device=xq.device)
+    def experts_packed(self, packed, out_dtype):
+        """Routed-expert pipeline on R received packed rows; result [R, H] in arrival order."""
+        r = packed.shape[0]
+        y = torch.empty((r, self.w2.shape[1]), dtype=out_dtype, device=packed.device)
         if r == 0:
             return y
-        sorted_ids, expert_ids, post_pad = moe_align_block_size(local_expert, _TILE_ROWS, self.num_local_experts)
-        rows = sorted_ids.numel() // _TILE_ROWS * _TILE_ROWS
-        k = xq.shape[1]
-        a1 = torch.empty((rows, k), dtype=torch.float8_e4m3fn, device=xq.device)
-        a1s = torch.empty((rows, xs.shape[1]), dtype=torch.float32, device=xq.device)
-        _cabi.check(
-            _cabi.lib().fg_gather_rows_fp8(
-                _cabi.ptr(xq), _cabi.ptr(xs), _cabi.ptr(a1), _cabi.ptr(a1s), rows, k, xs.shape[1],
-                _cabi.ptr(sorted_ids), 1, r, _cabi.ptr(post_pad), _cabi.stream_ptr(xq.device),
-            )
-        )
-        act = torch.empty((rows, self.inter), dtype=out_dtype, device=xq.device)
-        _grouped_gemm(act, a1, self.w1, a1s, self.w1_scale, None, sorted_ids, expert_ids, post_pad, r,
-                      _cabi.SCALE_BLOCK, fuse_silu=True, scatter=False, mul_weight=False)
-        a2, a2s = _group_quant(act, 128, None, 1, 0, post_pad, rows)
-        _grouped_gemm(y, a2, self.w2, a2s, self.w2_scale, weight, sorted_ids, expert_ids, post_pad, r,
-                      _cabi.SCALE_BLOCK, fuse_silu=False, scatter=True, mul_weight=True)
+        ws = self._workspace(r, packed.device)
+        _cabi.check(_cabi.lib().fg_moe_routed_block_fp8_packed(
+            _cabi.ptr(y), _cabi.ptr(packed), r, self.row_bytes, _cabi.ptr(self.w1), _cabi.ptr(self.w2),
+            _cabi.ptr(self.w1_scale), _cabi.ptr(self.w2_scale), self.num_local_experts, self.hidden, self.inter,
+            _cabi.ptr(ws), ws.numel(), _cabi.DTYPE_CODE[out_dtype], _cabi.stream_ptr(packed.device)))
+        return y
+
+    def local_routed(self, hidden, topk_ids, topk_w):
+        """Single-rank form: all experts are local.  Result [T*topk, H] in route-slot order."""
+        t, topk = topk_ids.shape
+        y = torch.empty((t * topk, self.w2.shape[1]), dtype=hidden.dtype, device=hidden.device)
+        if t == 0:
+            return y
+        ws = self._workspace(t * topk, hidden.device)
+        _cabi.check(_cabi.lib().fg_moe_routed_block_fp8_local(
+            _cabi.ptr(y), _cabi.ptr(hidden), _cabi.DTYPE_CODE[hidden.dtype], _cabi.ptr(topk_ids),
+            1 if topk_ids.dtype == torch.int64 else 0, _cabi.ptr(topk_w), _cabi.DTYPE_CODE[topk_w.dtype], t, topk,
+            _cabi.ptr(self.w1), _cabi.ptr(self.w2), _cabi.ptr(self.w1_scale), _cabi.ptr(self.w2_scale),
+            self.num_local_experts, self.hidden, self.inter, _cabi.ptr(ws), ws.numel(),
+            _cabi.stream_ptr(hidden.device)))
         return y
 
     def shared_expert(self, hidden):
@@ -144,6 +181,13 @@ class ExpertParallelMoE:
         self.ops = ops if ops is not None else CudaMoEOps(w1, w2, w1_scale, w2_scale, shared)
         self._side = None
         self.last_counts = None  # (send_counts, recv_counts) of the latest step, for reporting
+        self.trace = None  # set to a list to collect (phase name, CUDA event) marks of a step
+
+    def _mark(self, name, device):
+        if self.trace is not None and device.type == "cuda":
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(torch.cuda.current_stream(device))
+            self.trace.append((name, ev))
 
     # -- collectives ---------------------------------------------------------------------
     def _all_to_all(self, send, send_counts, recv_counts):
@@ -154,7 +198,7 @@ class ExpertParallelMoE:
     def _exchange_counts(self, send_counts_dev):
         recv_counts_dev = torch.empty_like(send_counts_dev)
         dist.all_to_all_single(recv_counts_dev, send_counts_dev, group=self.group)
-        both = torch.stack([send_counts_dev, recv_counts_dev]).cpu()  # the step's one host sync
+        both = torch.stack([send_counts_dev, recv_counts_dev]).cpu()  # the step's one host wait
         return both[0].tolist(), both[1].tolist()
 
     # -- forward ---------------------------------------------------------------------------
@@ -162,50 +206,50 @@ class ExpertParallelMoE:
         assert hidden.dim() == 2 and hidden.is_contiguous()
         assert topk_weights.shape == topk_ids.shape and topk_ids.shape[0] == hidden.shape[0]
         tokens, topk = topk_ids.shape
-        numel = tokens * topk
         ops = self.ops
-        flat_ids = topk_ids.reshape(-1)
-        flat_w = topk_weights.reshape(-1).float()
+        dev = hidden.device
+        topk_ids = topk_ids.contiguous()
+        topk_weights = topk_weights.contiguous()
+        if topk_weights.dtype not in _cabi.DTYPE_CODE:
+            topk_weights = topk_weights.float()
 
         # The shared expert only needs the local tokens: overlap it with the dispatch.
         shared_out, side = None, None
         if getattr(ops, "shared", None) is not None:
             if hidden.is_cuda:
                 if self._side is None:
-                    self._side = ops.side_stream(hidden.device)
+                    self._side = ops.side_stream(dev)
                 side = self._side
-                side.wait_stream(torch.cuda.current_stream(hidden.device))
+                side.wait_stream(torch.cuda.current_stream(dev))
                 with torch.cuda.stream(side):
                     shared_out = ops.shared_expert(hidden)
             else:
                 shared_out = ops.shared_expert(hidden)
 
+        self._mark("start", dev)
         if self.world == 1:
-            y = ops.local_routed(hidden, topk_ids, flat_w, topk)
+            y = ops.local_routed(hidden, topk_ids, topk_weights)
             inv = None
+            self._mark("experts", dev)
         else:
-            dest = (flat_ids // self.num_local_experts).to(torch.int32)
-            order = ops.route_order(dest, self.world)
-            send_counts_dev = torch.bincount(dest, minlength=self.world).to(torch.int64)
-            send_counts, recv_counts = self._exchange_counts(send_counts_dev)
+            packed, counts_dev, inv = ops.plan_and_pack(hidden, topk_ids, topk_weights, self.world)
+            self._mark("route+pack", dev)
+            send_counts, recv_counts = self._exchange_counts(counts_dev)
             self.last_counts = (send_counts, recv_counts)
-            order_l = order.long()
-            xq, xs = ops.quant_gather(hidden, order, topk)
-            meta = torch.stack([(flat_ids[order_l] % self.num_local_experts).to(torch.int32),
-                                flat_w[order_l].view(torch.int32)], dim=1).contiguous()
-            xq_r = self._all_to_all(xq.view(torch.uint8), send_counts, recv_counts).view(torch.float8_e4m3fn)
-            xs_r = self._all_to_all(xs, send_counts, recv_counts)
-            meta_r = self._all_to_all(meta, send_counts, recv_counts)
-            y_r = ops.expert_compute(xq_r, xs_r, meta_r[:, 0].contiguous(),
-                                     meta_r[:, 1].contiguous().view(torch.float32), hidden.dtype)
+            self._mark("counts", dev)
+            packed_r = self._all_to_all(packed, send_counts, recv_counts)
+            self._mark("dispatch", dev)
+            y_r = ops.experts_packed(packed_r, hidden.dtype)
+            self._mark("experts", dev)
             y = self._all_to_all(y_r, recv_counts, send_counts)
-            inv = torch.empty(numel, dtype=torch.int32, device=hidden.device)
-            inv[order_l] = torch.arange(numel, dtype=torch.int32, device=hidden.device)
+            self._mark("combine_a2a", dev)
 
         if side is not None:
             main = torch.cuda.current_stream(hidden.device)
             main.wait_stream(side)
             shared_out.record_stream(main)
-        return ops.combine(y, inv, tokens, topk, shared_out)
+        out = ops.combine(y, inv, tokens, topk, shared_out)
+        self._mark("sum", dev)
+        return out
 
     __call__ = forward

@@ -39,7 +39,7 @@ def act_quant_triton(
     n_blocks = n // block_size
     y = torch.empty_like(x, dtype=torch.float8_e4m3fn)
     s = x.new_empty(*x.size()[:-1], n_blocks, dtype=torch.float32)
-    with torch.cuda.device(x.device):
+    with _cabi.device_guard(x):
         _cabi.check(
             _cabi.lib().fg_act_quant_bf16_e4m3(
                 _cabi.ptr(x2), _cabi.ptr(y), _cabi.ptr(s), m, n, block_size,

@@ -56,7 +56,7 @@ def cutlass_scaled_mm(
     stream = _cabi.stream_ptr(a.device)
 
     vector_scales = (a_scale.numel() == 1 or a_scale.numel() == m) and (b_scale.numel() == 1 or b_scale.numel() == n)
-    with torch.cuda.device(a.device):
+    with _cabi.device_guard(a):
         if vector_scales:
             assert a_scale.is_contiguous(), "a_scale must be contiguous"
             assert b_scale.is_contiguous(), "b_scale must be contiguous"

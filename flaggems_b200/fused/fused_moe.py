@@ -100,7 +100,7 @@ def _fp8_quantize(A, A_scale, per_act_token, block_shape=None):
     """FP8 e4m3 quantisation of MoE activations: block-wise or per-token
     (reference: fused_moe.py:629-698).  The per-tensor branches are not implemented."""
     _cabi.require_cuda(A)
-    with torch.cuda.device(A.device):
+    with _cabi.device_guard(A):
         if block_shape is not None:
             assert not per_act_token
             assert len(block_shape) == 2
@@ -133,6 +133,7 @@ def _grouped_gemm(c, a, w, a_scale, w_scale, topk_weights, sorted_ids, expert_id
         _cabi.lib().fg_moe_grouped_gemm_fp8(
             _cabi.ptr(c), _cabi.ptr(a), _cabi.ptr(w), _cabi.ptr(a_scale), _cabi.ptr(w_scale),
             _cabi.ptr(topk_weights), _cabi.DTYPE_CODE.get(topk_weights.dtype, -1) if topk_weights is not None else 0,
+            1,
             _cabi.ptr(sorted_ids), _cabi.ptr(expert_ids), _cabi.ptr(num_post_pad),
             a.shape[0], numel, e, n, k, a.stride(0), c.stride(0), _TILE_ROWS, scale_mode, 1,
             1 if fuse_silu else 0, 1 if scatter else 0, 1 if mul_weight else 0,
@@ -229,7 +230,7 @@ def fused_experts_impl(
     tw = topk_weights if topk_weights.dtype in _cabi.DTYPE_CODE else topk_weights.float()
     tw = tw.contiguous()
 
-    with torch.cuda.device(hidden_states.device):
+    with _cabi.device_guard(hidden_states):
         for begin in range(0, num_tokens, _CHUNK_SIZE):
             end = min(begin + _CHUNK_SIZE, num_tokens)
             h = hidden_states[begin:end]

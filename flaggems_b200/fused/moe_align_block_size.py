@@ -32,7 +32,7 @@ def _launch(topk_ids, num_experts, block_size, sorted_token_ids, expert_ids, num
     emap = None
     if expert_map is not None:
         emap = expert_map.to(torch.int32).contiguous()
-    with torch.cuda.device(topk_ids.device):
+    with _cabi.device_guard(topk_ids):
         _cabi.check(
             _cabi.lib().fg_moe_align_block_size(
                 _cabi.ptr(ids), 1 if ids.dtype == torch.int64 else 0, ids.numel(), num_experts, block_size,

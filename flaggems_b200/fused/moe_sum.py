@@ -22,7 +22,7 @@ def moe_sum(input: torch.Tensor, output: torch.Tensor):
         raise NotImplementedError(f"unsupported dtype {input.dtype}")
     src = input if input.is_contiguous() else input.contiguous()
     dst = output if output.is_contiguous() else torch.empty_like(output, memory_format=torch.contiguous_format)
-    with torch.cuda.device(input.device):
+    with _cabi.device_guard(input):
         _cabi.check(
             _cabi.lib().fg_moe_sum(_cabi.ptr(src), _cabi.ptr(dst), m, topk, k, _cabi.DTYPE_CODE[input.dtype],
                                    _cabi.stream_ptr(input.device))

@@ -35,7 +35,7 @@ def silu_and_mul_out(A, B, out):
     else:
         assert out.is_contiguous(), "out must be 2-D row-major or contiguous"
         o2, ldo = out, n
-    with torch.cuda.device(A.device):
+    with _cabi.device_guard(A):
         _cabi.check(
             _cabi.lib().fg_silu_and_mul(
                 _cabi.ptr(a2), _cabi.ptr(b2), _cabi.ptr(o2), m, n, lda, ldb, ldo,

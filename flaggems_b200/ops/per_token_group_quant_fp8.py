@@ -57,7 +57,7 @@ def per_token_group_quant_fp8(
     else:
         s_row, s_col = k // group_size, 1
     xq2 = x_q.view(-1, k)
-    with torch.cuda.device(x.device):
+    with _cabi.device_guard(x):
         _cabi.check(
             _cabi.lib().fg_per_token_group_quant_fp8(
                 _cabi.ptr(x2), _cabi.DTYPE_CODE[x.dtype], _cabi.ptr(xq2), _cabi.ptr(x_s),

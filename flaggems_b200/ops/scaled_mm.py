@@ -93,7 +93,7 @@ def _scaled_mm_impl(self, mat2, scale_a, scale_b, bias, out_dtype, out):
     if bias is not None and bias.dtype != output_dtype:
         bias = bias.to(output_dtype)
     dst = out if out.stride(1) == 1 else torch.empty((m, n), dtype=output_dtype, device=out.device)
-    with torch.cuda.device(self.device):
+    with _cabi.device_guard(self):
         _cabi.check(
             _cabi.lib().fg_scaled_mm_fp8(
                 _cabi.ptr(dst), _cabi.ptr(self), _cabi.ptr(mat2), _cabi.ptr(scale_a), _cabi.ptr(scale_b),

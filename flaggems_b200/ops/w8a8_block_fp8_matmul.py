@@ -53,7 +53,7 @@ def w8a8_block_fp8_matmul(
         As2 = As2.float().contiguous()
     if Bs.dtype != torch.float32:
         Bs = Bs.float()
-    with torch.cuda.device(A.device):
+    with _cabi.device_guard(A):
         _cabi.check(
             _cabi.lib().fg_block_scaled_mm_fp8(
                 _cabi.ptr(c), _cabi.ptr(A), _cabi.ptr(B), _cabi.ptr(As2), _cabi.ptr(Bs),

@@ -45,7 +45,7 @@ def custom_per_token_group_fp8_quant(input, output_q, output_s, group_size, eps,
     assert input.dim() == 2 and input.stride(-1) == 1
     assert output_q.is_contiguous() and output_s.dim() == 2 and output_s.dtype == torch.float32
     m, k = input.shape
-    with torch.cuda.device(input.device):
+    with _cabi.device_guard(input):
         _cabi.check(
             _cabi.lib().fg_per_token_group_quant_fp8(
                 _cabi.ptr(input), _cabi.DTYPE_CODE[input.dtype], _cabi.ptr(output_q), _cabi.ptr(output_s),

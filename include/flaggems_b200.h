@@ -99,6 +99,16 @@ int fg_moe_align_block_size(const void* topk_ids, int ids_are_i64, int64_t numel
                             int32_t* sorted_ids, int64_t max_pad, int32_t* expert_ids,
                             int64_t n_blocks, int32_t* num_post_pad, void* stream);
 
+/* Same kernel with three extras used by the expert-parallel layer (no counterpart in the
+ * reference, which has no dispatch step): ids are read with a stride of ids_stride elements,
+ * the bucket of a slot is id / id_div (id_div = experts per rank turns expert ids into
+ * destination ranks), and expert_counts (nullable) receives the unpadded rows per bucket. */
+int fg_moe_align_block_size_ex(const void* topk_ids, int ids_are_i64, int64_t numel, int num_experts,
+                               int block_size, const int32_t* expert_map, int expert_map_len,
+                               int32_t* sorted_ids, int64_t max_pad, int32_t* expert_ids,
+                               int64_t n_blocks, int32_t* num_post_pad, int64_t ids_stride, int id_div,
+                               int32_t* expert_counts, void* stream);
+
 /* silu_and_mul_out / _silu_and_mul_kernel: src/flag_gems/fused/silu_and_mul.py:26-31,66-69,
  * src/flag_gems/fused/fused_moe.py:795-800.  out = dtype(x32/(1+exp(-x32)) * y32). */
 int fg_silu_and_mul(const void* x, const void* y, void* out, int64_t M, int64_t N, int64_t ld_x,
@@ -122,8 +132,43 @@ int fg_moe_sum_indexed(const void* in, void* out, int64_t M, int topk, int64_t K
  * (offs_token // top_k, src/flag_gems/fused/fused_moe.py:1101-1110), done ahead of the GEMM so
  * the GEMM reads contiguous tiles by TMA.  n_rows_dev (nullable): device count of rows. */
 int fg_gather_rows_fp8(const void* src_q, const float* src_s, void* dst_q, float* dst_s, int64_t rows,
-                       int64_t K, int64_t s_cols, const int32_t* row_index, int32_t index_div,
-                       int32_t index_limit, const int32_t* n_rows_dev, void* stream);
+                       int64_t K, int64_t s_cols, int64_t src_q_stride, int64_t src_s_stride,
+                       const int32_t* row_index, int32_t index_div, int32_t index_limit,
+                       const int32_t* n_rows_dev, void* stream);
+
+/* ---- expert-parallel dispatch format and one-call routed pipeline ------------------------
+ * No counterpart in the reference (its multi-GPU hook is expert_map only); the per-row
+ * arithmetic is that of fused_experts_impl, src/flag_gems/fused/fused_moe.py:1994-2183.
+ *
+ * Packed dispatch row (row_bytes, a multiple of 16, >= K + 4*K/128 + 8):
+ *   [0, K) e4m3 | [K, K + 4*K/128) fp32 group scales | int32 local expert | fp32 router weight. */
+
+/* Quantises (1x128 groups) the tokens x [T,K] into packed rows in send order: output row p is
+ * route slot order[p] (token order[p]/topk); its trailer gets topk_ids[slot] % experts_per_rank
+ * and topk_w[slot]; inv[slot] = p (nullable). */
+int fg_ep_pack_rows_fp8(const void* x, int x_dtype, int64_t T, int64_t K, int64_t ld_x,
+                        const void* topk_ids, int ids_are_i64, const void* topk_w, int topk_w_dtype,
+                        int topk, int experts_per_rank, const int32_t* order, void* packed,
+                        int64_t row_bytes, int32_t* inv, void* stream);
+
+/* Bytes of workspace the two functions below need for n_rows_in routed rows. */
+int64_t fg_moe_routed_workspace_bytes(int64_t n_rows_in, int num_experts, int64_t H, int64_t I);
+
+/* All experts local: y[T*topk, H] (route-slot order) = w2[e] . quant(silu_mul(w1[e] . quant(x)))
+ * times the router weight, for every (token, slot).  Five launches (align, quantise+gather,
+ * GEMM1+SiLU, quantise, GEMM2), no allocation: scratch is the caller's workspace (256-byte
+ * aligned, fg_moe_routed_workspace_bytes(T*topk, ...)). */
+int fg_moe_routed_block_fp8_local(void* y, const void* hidden, int hidden_dtype, const void* topk_ids,
+                                  int ids_are_i64, const void* topk_w, int topk_w_dtype, int64_t T,
+                                  int topk, const void* w1, const void* w2, const float* s1,
+                                  const float* s2, int num_experts, int64_t H, int64_t I,
+                                  void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Same for R packed rows received from other ranks: y[R, H] in arrival order. */
+int fg_moe_routed_block_fp8_packed(void* y, const void* rows, int64_t R, int64_t row_bytes,
+                                   const void* w1, const void* w2, const float* s1, const float* s2,
+                                   int num_experts, int64_t H, int64_t I, void* workspace,
+                                   int64_t workspace_bytes, int out_dtype, void* stream);
 
 /* ---- scaled FP8 matrix products (tcgen05 / TMEM / TMA) ---------------------- */
 
@@ -167,10 +212,10 @@ int fg_block_scaled_mm_fp8(void* c, const void* a, const void* b, const float* a
  * (FUSE_SILU branch :1186-1347); else c gets N columns.
  * scatter != 0: row r is written to c row sorted_ids[r] (skipped when
  * sorted_ids[r] >= numel) instead of row r; mul_weight != 0 multiplies by
- * topk_weights[sorted_ids[r]] in fp32 before the cast (:1485-1493). */
+ * topk_weights[sorted_ids[r] * topk_w_stride] in fp32 before the cast (:1485-1493). */
 int fg_moe_grouped_gemm_fp8(void* c, const void* a, const void* w, const float* a_scale,
                             const float* w_scale, const void* topk_weights, int topk_w_dtype,
-                            const int32_t* sorted_ids, const int32_t* expert_ids,
+                            int64_t topk_w_stride, const int32_t* sorted_ids, const int32_t* expert_ids,
                             const int32_t* num_post_pad, int64_t max_rows, int64_t numel,
                             int num_experts, int64_t N, int64_t K, int64_t ld_a, int64_t ld_c,
                             int block_rows, int scale_mode, int a_scale_per_row, int fuse_silu,

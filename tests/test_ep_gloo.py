@@ -18,24 +18,58 @@ FP8 = torch.float8_e4m3fn
 
 
 class OracleOps:
-    """Test double for CudaMoEOps: same methods, computed by the CPU oracle."""
+    """Test double for CudaMoEOps: same methods and the same packed row format, computed by the
+    CPU oracle."""
 
     def __init__(self, w1, w2, s1, s2, shared=None):
+        from flaggems_b200.ep import packed_row_bytes
+
         self.w1, self.w2, self.s1, self.s2, self.shared = w1, w2, s1, s2, shared
+        self.hidden = w1.shape[2]
+        self.e_loc = w1.shape[0]
+        self.row_bytes = packed_row_bytes(self.hidden)
 
-    def route_order(self, dest, world):
-        return torch.sort(dest, stable=True).indices.to(torch.int32)
-
-    def quant_gather(self, hidden, order, topk):
+    def plan_and_pack(self, hidden, topk_ids, topk_w, world):
         import oracle
 
-        return oracle.per_token_group_quant_fp8(hidden[order.long() // topk], 128)
+        t, topk = topk_ids.shape
+        numel = t * topk
+        flat = topk_ids.reshape(-1)
+        dest = flat // self.e_loc
+        order = torch.sort(dest, stable=True).indices
+        counts = torch.bincount(dest, minlength=world).to(torch.int32)
+        q, s = oracle.per_token_group_quant_fp8(hidden[order // topk], 128)
+        h = self.hidden
+        packed = torch.zeros(numel, self.row_bytes, dtype=torch.uint8)
+        packed[:, :h] = q.view(torch.uint8)
+        packed[:, h:h + 4 * (h // 128)] = s.contiguous().view(torch.uint8).reshape(numel, -1)
+        off = h + 4 * (h // 128)
+        packed[:, off:off + 4] = (flat[order] % self.e_loc).to(torch.int32).view(torch.uint8).reshape(numel, 4)
+        packed[:, off + 4:off + 8] = topk_w.reshape(-1).float()[order].view(torch.uint8).reshape(numel, 4)
+        inv = torch.empty(numel, dtype=torch.int32)
+        inv[order] = torch.arange(numel, dtype=torch.int32)
+        return packed, counts, inv
 
-    def local_routed(self, hidden, topk_ids, weight, topk):
-        xq, xs = self.quant_gather(hidden, torch.arange(topk_ids.numel()), topk)
-        return self.expert_compute(xq, xs, topk_ids.reshape(-1).int(), weight, hidden.dtype)
+    def _unpack(self, packed):
+        h = self.hidden
+        off = h + 4 * (h // 128)
+        xq = packed[:, :h].contiguous().view(FP8)
+        xs = packed[:, h:off].contiguous().view(torch.float32)
+        le = packed[:, off:off + 4].contiguous().view(torch.int32).reshape(-1)
+        wt = packed[:, off + 4:off + 8].contiguous().view(torch.float32).reshape(-1)
+        return xq, xs, le, wt
 
-    def expert_compute(self, xq, xs, le, wt, dtype):
+    def experts_packed(self, packed, dtype):
+        return self._experts(*self._unpack(packed), dtype)
+
+    def local_routed(self, hidden, topk_ids, topk_w):
+        import oracle
+
+        topk = topk_ids.shape[1]
+        xq, xs = oracle.per_token_group_quant_fp8(hidden[torch.arange(topk_ids.numel()) // topk], 128)
+        return self._experts(xq, xs, topk_ids.reshape(-1).int(), topk_w.reshape(-1).float(), hidden.dtype)
+
+    def _experts(self, xq, xs, le, wt, dtype):
         import oracle
         from oracle.moe import _silu_mul_f32
 
