@@ -333,7 +333,8 @@ def run_ours(args):
     e_loc, t_loc = EXPERTS // world, TOKENS // world
     w1, w2, s1, s2 = make_expert_weights(e_loc, rank * e_loc, dev)
     shared = make_shared_weights(dev)
-    layer = ExpertParallelMoE(w1, w2, s1, s2, EXPERTS, rank, world, shared=shared)
+    layer = ExpertParallelMoE(w1, w2, s1, s2, EXPERTS, rank, world, shared=shared,
+                              p2p_combine_rows=0 if args.a2a_combine else t_loc * TOPK)
     tw_all, ti_all = make_router(TOKENS, EXPERTS, TOPK)
     # logical expert -> physical slot (rank * E_loc + local index); identical on every rank
     from flaggems_b200.ep import balanced_expert_placement
@@ -447,6 +448,9 @@ def run_ours(args):
                 "d2h_bytes_per_step": d2h * world, "ms_per_step": round(ms_e2e, 4)},
         "gpu_launches": int(launches), "roofline": roofline, "device_status": status,
         "phase_ms_rank0": phases,
+        "combine": ("n/a (single rank)" if world == 1 else
+                    "NCCL all_to_all_single" if args.a2a_combine else
+                    "fused into GEMM2's epilogue: rows stored to the home rank over NVLink peer memory"),
         "routed_rows_per_rank": {"max": int(rows_per_rank.max()), "mean": float(rows_per_rank.float().mean())},
         "layer_tflops": round((2.0 * TOKENS * TOPK * 3 * HIDDEN * INTER + 2.0 * TOKENS * 3 * HIDDEN * INTER) / ms / 1e9, 1),
     }
@@ -494,6 +498,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-tokens", type=int, default=16, help="tokens in the bounded CPU sample")
     ap.add_argument("--no-extras", action="store_true", help="skip the dense GEMM / quant figures at N=1")
+    ap.add_argument("--a2a-combine", action="store_true",
+                    help="return expert outputs by NCCL all-to-all instead of the fused peer-memory combine")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -39,13 +39,22 @@ _SIGS = {
     "fg_moe_align_block_size_ex": (
         c_int, [_P, c_int, c_int64, c_int, c_int, _P, c_int, _P, c_int64, _P, c_int64, _P, c_int64, c_int, _P, _P]),
     "fg_ep_pack_rows_fp8": (
-        c_int, [_P, c_int, c_int64, c_int64, c_int64, _P, c_int, _P, c_int, c_int, c_int, _P, _P, c_int64, _P, _P]),
+        c_int, [_P, c_int, c_int64, c_int64, c_int64, _P, c_int, _P, c_int, c_int, c_int, c_int, _P, _P, c_int64,
+                _P, _P]),
     "fg_moe_routed_workspace_bytes": (c_int64, [c_int64, c_int, c_int64, c_int64]),
     "fg_moe_routed_block_fp8_local": (
         c_int, [_P, _P, c_int, _P, c_int, _P, c_int, c_int64, c_int, _P, _P, _P, _P, c_int, c_int64, c_int64,
                 _P, c_int64, _P]),
     "fg_moe_routed_block_fp8_packed": (
-        c_int, [_P, _P, c_int64, c_int64, _P, _P, _P, _P, c_int, c_int64, c_int64, _P, c_int64, c_int, _P]),
+        c_int, [_P, _P, c_int64, c_int64, _P, _P, _P, _P, c_int, c_int64, c_int64, _P, c_int64, c_int, _P, c_int,
+                _P]),
+    "fg_moe_grouped_gemm_fp8_peer": (
+        c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int64, _P, _P, _P, c_int64, c_int64, c_int, c_int64, c_int64,
+                c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int64, _P, c_int, _P]),
+    "fg_symm_alloc": (c_int, [c_int64, ctypes.POINTER(c_void_p), _P]),
+    "fg_symm_open": (c_int, [_P, ctypes.POINTER(c_void_p)]),
+    "fg_symm_close": (c_int, [_P]),
+    "fg_symm_free": (c_int, [_P]),
     "fg_scaled_mm_fp8": (
         c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                 c_int, c_int, c_int, c_int, _P]),

@@ -67,4 +67,40 @@ int fg_device_status(unsigned int* status) {
     return FG_OK;
 }
 
+// ---- buffers shared between the ranks of one node (CUDA IPC) -------------------------------
+int fg_symm_alloc(int64_t bytes, void** ptr, unsigned char* handle64) {
+    FG_REQUIRE(bytes > 0 && ptr && handle64, FG_ERR_INVALID_ARGUMENT, "bad arguments");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    void* p = nullptr;
+    FG_CUDA(cudaMalloc(&p, (size_t)bytes));
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        fg_set_error("cudaIpcGetMemHandle failed: %s", cudaGetErrorString(e));
+        return FG_ERR_CUDA;
+    }
+    memcpy(handle64, &h, 64);
+    *ptr = p;
+    return FG_OK;
+}
+
+int fg_symm_open(const unsigned char* handle64, void** ptr) {
+    FG_REQUIRE(handle64 && ptr, FG_ERR_INVALID_ARGUMENT, "bad arguments");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    FG_CUDA(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return FG_OK;
+}
+
+int fg_symm_close(void* ptr) {
+    FG_CUDA(cudaIpcCloseMemHandle(ptr));
+    return FG_OK;
+}
+
+int fg_symm_free(void* ptr) {
+    FG_CUDA(cudaFree(ptr));
+    return FG_OK;
+}
+
 }  // extern "C"

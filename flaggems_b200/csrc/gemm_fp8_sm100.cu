@@ -61,6 +61,12 @@ struct GemmParams {
     const void* topk_w;
     int topk_w_dtype;
     int64_t topk_w_stride;  // elements between the weights of consecutive route slots
+    // Peer scatter (expert-parallel combine fused into GEMM2's epilogue): row with arrival index
+    // sid is stored to peer_out[dest[sid*dest_stride + 1]] at row dest[sid*dest_stride].
+    const int32_t* dest;
+    int64_t dest_stride;
+    int n_peers;
+    void* peer_out[8];
     unsigned int* status;
 };
 
@@ -328,7 +334,15 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 row_ok = row < p.M;
             }
             const int esz = p.out_dtype == FG_DTYPE_F32 ? 4 : 2;
-            uint8_t* out_ptr = reinterpret_cast<uint8_t*>(p.c) + out_row * p.ld_c * esz;
+            uint8_t* out_base = reinterpret_cast<uint8_t*>(p.c);
+            if (p.n_peers > 0 && p.grouped && p.scatter && row_ok) {
+                const int32_t* d = p.dest + out_row * p.dest_stride;
+                const int32_t home = d[1];
+                out_row = d[0];
+                row_ok = home >= 0 && home < p.n_peers && out_row >= 0;
+                out_base = reinterpret_cast<uint8_t*>(p.peer_out[row_ok ? home : 0]);
+            }
+            uint8_t* out_ptr = out_base + out_row * p.ld_c * esz;
             // column of output chunk c (32 wide) handled by this thread
             const int out_col_base = n0 + (FUSE_SILU ? 64 * half : 128 * half);
             constexpr int OUT_CHUNKS = FUSE_SILU ? 2 : 4;
@@ -635,14 +649,29 @@ int fg_block_scaled_mm_fp8(void* c, const void* a, const void* b, const float* a
 
 int fg_moe_grouped_gemm_fp8(void* c, const void* a, const void* w, const float* a_scale, const float* w_scale,
                             const void* topk_weights, int topk_w_dtype, int64_t topk_w_stride,
+                            const int32_t* sorted_ids, const int32_t* expert_ids, const int32_t* num_post_pad,
+                            int64_t max_rows, int64_t numel, int num_experts, int64_t N, int64_t K, int64_t ld_a,
+                            int64_t ld_c, int block_rows, int scale_mode, int a_scale_per_row, int fuse_silu,
+                            int scatter, int mul_weight, int out_dtype, void* stream) {
+    return fg_moe_grouped_gemm_fp8_peer(c, a, w, a_scale, w_scale, topk_weights, topk_w_dtype, topk_w_stride,
+                                        sorted_ids, expert_ids, num_post_pad, max_rows, numel, num_experts, N, K,
+                                        ld_a, ld_c, block_rows, scale_mode, a_scale_per_row, fuse_silu, scatter,
+                                        mul_weight, out_dtype, nullptr, 0, nullptr, 0, stream);
+}
+
+int fg_moe_grouped_gemm_fp8_peer(void* c, const void* a, const void* w, const float* a_scale, const float* w_scale,
+                            const void* topk_weights, int topk_w_dtype, int64_t topk_w_stride,
                             const int32_t* sorted_ids,
                             const int32_t* expert_ids, const int32_t* num_post_pad, int64_t max_rows, int64_t numel,
                             int num_experts, int64_t N, int64_t K, int64_t ld_a, int64_t ld_c, int block_rows,
                             int scale_mode, int a_scale_per_row, int fuse_silu, int scatter, int mul_weight,
-                            int out_dtype, void* stream) {
+                            int out_dtype, const int32_t* dest, int64_t dest_stride, void* const* peer_out, int n_peers,
+                            void* stream) {
     FG_REQUIRE(max_rows >= 0 && N > 0 && K > 0 && num_experts > 0, FG_ERR_INVALID_ARGUMENT, "bad sizes");
-    FG_REQUIRE(c && a && w && a_scale && w_scale && sorted_ids && expert_ids && num_post_pad,
+    FG_REQUIRE((c || n_peers > 0) && a && w && a_scale && w_scale && sorted_ids && expert_ids && num_post_pad,
                FG_ERR_INVALID_ARGUMENT, "null pointer");
+    FG_REQUIRE(n_peers >= 0 && n_peers <= 8 && (n_peers == 0 || (dest && peer_out && scatter && dest_stride >= 2)),
+               FG_ERR_INVALID_ARGUMENT, "peer scatter needs 1..8 peers, scatter mode and a (slot, rank) table");
     FG_REQUIRE(dtype_ok(out_dtype), FG_ERR_INVALID_ARGUMENT, "bad out_dtype %d", out_dtype);
     FG_REQUIRE(block_rows >= 8 && block_rows <= 128 && block_rows % 8 == 0, FG_ERR_UNSUPPORTED,
                "block_rows %d must be a multiple of 8 in [8, 128]", block_rows);
@@ -670,6 +699,9 @@ int fg_moe_grouped_gemm_fp8(void* c, const void* a, const void* w, const float* 
     p.grouped = 1; p.sorted_ids = sorted_ids; p.expert_ids = expert_ids; p.num_post_pad = num_post_pad;
     p.block_rows = block_rows; p.numel = numel; p.scatter = scatter; p.mul_weight = mul_weight;
     p.topk_w = topk_weights; p.topk_w_dtype = topk_w_dtype; p.topk_w_stride = topk_w_stride > 0 ? topk_w_stride : 1;
+    p.dest = dest; p.dest_stride = dest_stride; p.n_peers = n_peers;
+    for (int i = 0; i < n_peers; ++i) p.peer_out[i] = peer_out[i];
+    if (n_peers > 0 && !c) p.c = peer_out[0];
     return launch_gemm(p, a, p.M, ld_a, w, num_experts, K, block, fuse_silu != 0, (cudaStream_t)stream);
 }
 

@@ -59,7 +59,8 @@ int check_dims(int64_t n_in, int num_experts, int64_t H, int64_t I, int out_dtyp
 // GEMM1 -> quant -> GEMM2 on rows already in sorted order in ws.a1 / ws.a1s.
 int run_gemms(void* y, const Workspace& ws, int64_t n_in, const void* w1, const void* w2, const float* s1,
               const float* s2, int num_experts, int64_t H, int64_t I, const void* weights, int w_dtype,
-              int64_t w_stride, int out_dtype, void* stream) {
+              int64_t w_stride, int out_dtype, const int32_t* dest, int64_t dest_stride, void* const* peer_out,
+              int n_peers, void* stream) {
     int rc = fg_moe_grouped_gemm_fp8(ws.act, ws.a1, w1, ws.a1s, s1, nullptr, 0, 1, ws.sorted_ids, ws.expert_ids,
                                      ws.post_pad, ws.rows, n_in, num_experts, 2 * I, H, H, I, TILE_ROWS, FG_SCALE_BLOCK,
                                      1, /*fuse_silu=*/1, /*scatter=*/0, /*mul_weight=*/0, out_dtype, stream);
@@ -67,9 +68,10 @@ int run_gemms(void* y, const Workspace& ws, int64_t n_in, const void* w1, const 
     rc = fg_per_token_group_quant_fp8_gather(ws.act, out_dtype, ws.a2, ws.a2s, ws.rows, I, 128, I, I, nullptr, 1, 0,
                                              ws.post_pad, stream);
     if (rc != FG_OK) return rc;
-    return fg_moe_grouped_gemm_fp8(y, ws.a2, w2, ws.a2s, s2, weights, w_dtype, w_stride, ws.sorted_ids, ws.expert_ids,
-                                   ws.post_pad, ws.rows, n_in, num_experts, H, I, I, H, TILE_ROWS, FG_SCALE_BLOCK, 1,
-                                   /*fuse_silu=*/0, /*scatter=*/1, /*mul_weight=*/1, out_dtype, stream);
+    return fg_moe_grouped_gemm_fp8_peer(y, ws.a2, w2, ws.a2s, s2, weights, w_dtype, w_stride, ws.sorted_ids,
+                                        ws.expert_ids, ws.post_pad, ws.rows, n_in, num_experts, H, I, I, H, TILE_ROWS,
+                                        FG_SCALE_BLOCK, 1, /*fuse_silu=*/0, /*scatter=*/1, /*mul_weight=*/1, out_dtype,
+                                        dest, dest_stride, peer_out, n_peers, stream);
 }
 
 }  // namespace
@@ -101,17 +103,20 @@ int fg_moe_routed_block_fp8_local(void* y, const void* hidden, int hidden_dtype,
     rc = fg_per_token_group_quant_fp8_gather(hidden, hidden_dtype, ws.a1, ws.a1s, ws.rows, H, 128, H, H, ws.sorted_ids,
                                              topk, (int32_t)n_in, ws.post_pad, stream);
     if (rc != FG_OK) return rc;
-    return run_gemms(y, ws, n_in, w1, w2, s1, s2, num_experts, H, I, topk_w, topk_w_dtype, 1, hidden_dtype, stream);
+    return run_gemms(y, ws, n_in, w1, w2, s1, s2, num_experts, H, I, topk_w, topk_w_dtype, 1, hidden_dtype, nullptr, 0,
+                     nullptr, 0, stream);
 }
 
 int fg_moe_routed_block_fp8_packed(void* y, const void* rows, int64_t R, int64_t row_bytes, const void* w1,
                                    const void* w2, const float* s1, const float* s2, int num_experts, int64_t H,
-                                   int64_t I, void* workspace, int64_t workspace_bytes, int out_dtype, void* stream) {
+                                   int64_t I, void* workspace, int64_t workspace_bytes, int out_dtype,
+                                   void* const* peer_out, int n_peers, void* stream) {
     int rc = check_dims(R, num_experts, H, I, out_dtype);
     if (rc != FG_OK) return rc;
     if (R == 0) return FG_OK;
-    FG_REQUIRE(y && rows && w1 && w2 && s1 && s2 && workspace, FG_ERR_INVALID_ARGUMENT, "null pointer");
-    FG_REQUIRE(row_bytes >= H + 4 * (H / 128) + 8 && row_bytes % 16 == 0 && (uintptr_t)rows % 16 == 0,
+    FG_REQUIRE((y || n_peers > 0) && rows && w1 && w2 && s1 && s2 && workspace, FG_ERR_INVALID_ARGUMENT,
+               "null pointer");
+    FG_REQUIRE(row_bytes >= H + 4 * (H / 128) + 16 && row_bytes % 16 == 0 && (uintptr_t)rows % 16 == 0,
                FG_ERR_INVALID_ARGUMENT, "bad packed row size %lld", (long long)row_bytes);
     FG_REQUIRE((uintptr_t)workspace % 256 == 0, FG_ERR_INVALID_ARGUMENT, "workspace must be 256-byte aligned");
     const Workspace ws = carve(workspace, R, num_experts, H, I, 2);
@@ -127,7 +132,9 @@ int fg_moe_routed_block_fp8_packed(void* y, const void* rows, int64_t R, int64_t
     rc = fg_gather_rows_fp8(base, reinterpret_cast<const float*>(base + H), ws.a1, ws.a1s, ws.rows, H, s_cols,
                             row_bytes, row_bytes / 4, ws.sorted_ids, 1, (int32_t)R, ws.post_pad, stream);
     if (rc != FG_OK) return rc;
-    return run_gemms(y, ws, R, w1, w2, s1, s2, num_experts, H, I, wts, FG_DTYPE_F32, row_bytes / 4, out_dtype, stream);
+    const int32_t* dest = reinterpret_cast<const int32_t*>(base + H + 4 * s_cols + 8);
+    return run_gemms(y, ws, R, w1, w2, s1, s2, num_experts, H, I, wts, FG_DTYPE_F32, row_bytes / 4, out_dtype,
+                     n_peers > 0 ? dest : nullptr, row_bytes / 4, peer_out, n_peers, stream);
 }
 
 }  // extern "C"

@@ -37,6 +37,7 @@ struct QuantArgs {
     const void* meta_w;  // route slot -> router weight
     int meta_w_dtype;
     int32_t meta_mod;  // experts per rank
+    int32_t meta_rank;  // this rank (home of the rows)
     int64_t meta_off;
     int32_t* inv;  // nullable: inv[route slot] = output row
 };
@@ -52,6 +53,8 @@ __device__ __forceinline__ void write_row_meta(const QuantArgs& a, int64_t out_r
     uint8_t* m = a.q + out_row * a.ld_q + a.meta_off;
     *reinterpret_cast<int32_t*>(m) = (int32_t)(e % a.meta_mod);
     *reinterpret_cast<float*>(m + 4) = w;
+    *reinterpret_cast<int32_t*>(m + 8) = slot;
+    *reinterpret_cast<int32_t*>(m + 12) = a.meta_rank;
     if (a.inv) a.inv[slot] = (int32_t)out_row;
 }
 
@@ -373,10 +376,11 @@ int fg_per_token_group_quant_fp8_gather(const void* x, int x_dtype, void* q, flo
 
 int fg_ep_pack_rows_fp8(const void* x, int x_dtype, int64_t T, int64_t K, int64_t ld_x, const void* topk_ids,
                         int ids_are_i64, const void* topk_w, int topk_w_dtype, int topk, int experts_per_rank,
-                        const int32_t* order, void* packed, int64_t row_bytes, int32_t* inv, void* stream) {
+                        int home_rank, const int32_t* order, void* packed, int64_t row_bytes, int32_t* inv,
+                        void* stream) {
     FG_REQUIRE(T >= 0 && K > 0 && topk > 0 && experts_per_rank > 0, FG_ERR_INVALID_ARGUMENT, "bad sizes");
     FG_REQUIRE(K % 128 == 0, FG_ERR_UNSUPPORTED, "row length %lld must be a multiple of 128", (long long)K);
-    FG_REQUIRE(row_bytes >= K + 4 * (K / 128) + 8 && row_bytes % 16 == 0, FG_ERR_INVALID_ARGUMENT,
+    FG_REQUIRE(row_bytes >= K + 4 * (K / 128) + 16 && row_bytes % 16 == 0, FG_ERR_INVALID_ARGUMENT,
                "row_bytes %lld too small or not a multiple of 16", (long long)row_bytes);
     FG_REQUIRE(T * topk < (1ll << 31), FG_ERR_UNSUPPORTED, "too many route slots");
     if (T == 0) return FG_OK;
@@ -388,7 +392,7 @@ int fg_ep_pack_rows_fp8(const void* x, int x_dtype, int64_t T, int64_t K, int64_
     a.eps = 1e-10f; a.pow2 = 0;
     a.row_index = order; a.index_div = topk; a.index_limit = (int32_t)(T * topk); a.n_rows_dev = nullptr;
     a.meta_ids = topk_ids; a.meta_ids_i64 = ids_are_i64; a.meta_w = topk_w; a.meta_w_dtype = topk_w_dtype;
-    a.meta_mod = experts_per_rank; a.meta_off = K + 4 * (K / 128); a.inv = inv;
+    a.meta_mod = experts_per_rank; a.meta_rank = home_rank; a.meta_off = K + 4 * (K / 128); a.inv = inv;
     int rc = check_common(a, x_dtype);
     if (rc != FG_OK) return rc;
     return launch_quant<QM_GROUP>(x_dtype, a, (cudaStream_t)stream);

@@ -58,9 +58,53 @@ def balanced_expert_placement(counts: torch.Tensor, world: int) -> torch.Tensor:
 
 
 def packed_row_bytes(hidden: int) -> int:
-    """Bytes of one dispatch row: FP8 payload, 1x128 group scales, int32 local expert, fp32 router
-    weight, padded to 16 bytes (so that rows can be read by TMA where they land)."""
-    return (hidden + 4 * (hidden // 128) + 8 + 15) // 16 * 16
+    """Bytes of one dispatch row: FP8 payload, 1x128 group scales, then int32 local expert, fp32
+    router weight, int32 route slot at the home rank, int32 home rank; a multiple of 16."""
+    return (hidden + 4 * (hidden // 128) + 16 + 15) // 16 * 16
+
+
+class SymmetricBuffers:
+    """``count`` device buffers of ``nbytes`` on every rank, each mapped into every other rank of
+    the node through CUDA IPC.  ``ptrs[i][r]`` is the address, valid in this process, of buffer i
+    of rank r.  Creation is collective over ``group``."""
+
+    def __init__(self, nbytes, count, rank, world, group=None):
+        import ctypes
+
+        L = _cabi.lib()
+        self.nbytes, self.count, self.rank, self.world = nbytes, count, rank, world
+        self.local, handles = [], []
+        for _ in range(count):
+            ptr = ctypes.c_void_p()
+            h = (ctypes.c_ubyte * 64)()
+            _cabi.check(L.fg_symm_alloc(nbytes, ctypes.byref(ptr), h))
+            self.local.append(ptr.value)
+            handles.append(bytes(h))
+        gathered = [None] * world
+        dist.all_gather_object(gathered, handles, group=group)
+        self.ptrs, self._opened = [], []
+        for i in range(count):
+            row = []
+            for r in range(world):
+                if r == rank:
+                    row.append(self.local[i])
+                else:
+                    ptr = ctypes.c_void_p()
+                    buf = (ctypes.c_ubyte * 64).from_buffer_copy(gathered[r][i])
+                    _cabi.check(L.fg_symm_open(buf, ctypes.byref(ptr)))
+                    row.append(ptr.value)
+                    self._opened.append(ptr.value)
+            self.ptrs.append(row)
+        self.ptr_arrays = [(ctypes.c_void_p * world)(*row) for row in self.ptrs]
+        dist.barrier(group=group)
+
+    def close(self):
+        L = _cabi.lib()
+        for p in self._opened:
+            L.fg_symm_close(p)
+        for p in self.local:
+            L.fg_symm_free(p)
+        self._opened, self.local = [], []
 
 
 class CudaMoEOps:
@@ -84,7 +128,7 @@ class CudaMoEOps:
             self._ws = torch.empty(int(need * 1.25) + 256, dtype=torch.uint8, device=device)
         return self._ws
 
-    def plan_and_pack(self, hidden, topk_ids, topk_w, world):
+    def plan_and_pack(self, hidden, topk_ids, topk_w, world, rank):
         """Orders the route slots by destination rank (stable), counts rows per destination and
         writes the packed dispatch rows in that order.  Returns (packed [numel, row_bytes] uint8,
         counts int32 [world] on the device, inv int32 [numel]: row of each route slot)."""
@@ -104,21 +148,35 @@ class CudaMoEOps:
         _cabi.check(L.fg_ep_pack_rows_fp8(
             _cabi.ptr(hidden), _cabi.DTYPE_CODE[hidden.dtype], t, self.hidden, hidden.stride(0),
             _cabi.ptr(topk_ids), ids64, _cabi.ptr(topk_w), _cabi.DTYPE_CODE[topk_w.dtype], topk,
-            self.num_local_experts, _cabi.ptr(order), _cabi.ptr(packed), self.row_bytes, _cabi.ptr(inv), st))
+            self.num_local_experts, rank, _cabi.ptr(order), _cabi.ptr(packed), self.row_bytes, _cabi.ptr(inv), st))
         return packed, meta[1:], inv
 
-    def experts_packed(self, packed, out_dtype):
-        """Routed-expert pipeline on R received packed rows; result [R, H] in arrival order."""
+    def experts_packed(self, packed, out_dtype, peer_out=None):
+        """Routed-expert pipeline on R received packed rows.  Without ``peer_out`` the result is
+        returned as [R, H] in arrival order; with it (a ctypes array of one buffer address per
+        rank) GEMM2 stores every row into its home rank's buffer and None is returned."""
         r = packed.shape[0]
-        y = torch.empty((r, self.w2.shape[1]), dtype=out_dtype, device=packed.device)
+        y = None
+        if peer_out is None:
+            y = torch.empty((r, self.w2.shape[1]), dtype=out_dtype, device=packed.device)
         if r == 0:
             return y
         ws = self._workspace(r, packed.device)
         _cabi.check(_cabi.lib().fg_moe_routed_block_fp8_packed(
             _cabi.ptr(y), _cabi.ptr(packed), r, self.row_bytes, _cabi.ptr(self.w1), _cabi.ptr(self.w2),
             _cabi.ptr(self.w1_scale), _cabi.ptr(self.w2_scale), self.num_local_experts, self.hidden, self.inter,
-            _cabi.ptr(ws), ws.numel(), _cabi.DTYPE_CODE[out_dtype], _cabi.stream_ptr(packed.device)))
+            _cabi.ptr(ws), ws.numel(), _cabi.DTYPE_CODE[out_dtype], peer_out,
+            0 if peer_out is None else len(peer_out), _cabi.stream_ptr(packed.device)))
         return y
+
+    def combine_slots(self, buf_ptr, tokens, topk, dtype, device, addend):
+        """Top-k sum over a [tokens*topk, H] buffer given by address (rows in route-slot order)."""
+        out = torch.empty((tokens, self.w2.shape[1]), dtype=dtype, device=device)
+        if tokens:
+            _cabi.check(_cabi.lib().fg_moe_sum_indexed(
+                buf_ptr, _cabi.ptr(out), tokens, topk, self.w2.shape[1], _cabi.DTYPE_CODE[dtype], None,
+                _cabi.ptr(addend), _cabi.stream_ptr(device)))
+        return out
 
     def local_routed(self, hidden, topk_ids, topk_w):
         """Single-rank form: all experts are local.  Result [T*topk, H] in route-slot order."""
@@ -173,7 +231,7 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, w1, w2, w1_scale, w2_scale, num_experts: int, rank: int = 0, world: int = 1,
-                 group=None, shared=None, ops=None):
+                 group=None, shared=None, ops=None, p2p_combine_rows: int = 0):
         assert num_experts % world == 0, "experts must divide evenly over the ranks"
         assert w1.shape[0] == num_experts // world, "w1 must hold exactly this rank's experts"
         self.num_experts, self.rank, self.world, self.group = num_experts, rank, world, group
@@ -182,6 +240,15 @@ class ExpertParallelMoE:
         self._side = None
         self.last_counts = None  # (send_counts, recv_counts) of the latest step, for reporting
         self.trace = None  # set to a list to collect (phase name, CUDA event) marks of a step
+        # Fused combine: GEMM2 writes result rows straight into the home rank's buffer over
+        # NVLink peer memory.  p2p_combine_rows = capacity in route slots (tokens * topk) per rank;
+        # 0 keeps the all-to-all combine.  Two buffers alternate between steps.
+        self._symm, self._step = None, 0
+        if p2p_combine_rows > 0 and world > 1 and ops is None:
+            hidden_size = w1.shape[2]
+            self._symm = SymmetricBuffers(p2p_combine_rows * hidden_size * 2, 2, rank, world, group)
+            self._symm_rows = p2p_combine_rows
+            self._flag = torch.zeros(1, dtype=torch.float32, device=w1.device)
 
     def _mark(self, name, device):
         if self.trace is not None and device.type == "cuda":
@@ -232,23 +299,37 @@ class ExpertParallelMoE:
             inv = None
             self._mark("experts", dev)
         else:
-            packed, counts_dev, inv = ops.plan_and_pack(hidden, topk_ids, topk_weights, self.world)
+            packed, counts_dev, inv = ops.plan_and_pack(hidden, topk_ids, topk_weights, self.world, self.rank)
             self._mark("route+pack", dev)
             send_counts, recv_counts = self._exchange_counts(counts_dev)
             self.last_counts = (send_counts, recv_counts)
             self._mark("counts", dev)
             packed_r = self._all_to_all(packed, send_counts, recv_counts)
             self._mark("dispatch", dev)
-            y_r = ops.experts_packed(packed_r, hidden.dtype)
-            self._mark("experts", dev)
-            y = self._all_to_all(y_r, recv_counts, send_counts)
-            self._mark("combine_a2a", dev)
+            use_p2p = (self._symm is not None and hidden.dtype in (torch.bfloat16, torch.float16)
+                       and tokens * topk <= self._symm_rows)
+            if use_p2p:
+                buf = self._step & 1
+                self._step += 1
+                ops.experts_packed(packed_r, hidden.dtype, self._symm.ptr_arrays[buf])
+                self._mark("experts+combine", dev)
+                # every rank's GEMM2 has finished once this stream-ordered collective completes
+                dist.all_reduce(self._flag, group=self.group)
+                self._mark("barrier", dev)
+            else:
+                y_r = ops.experts_packed(packed_r, hidden.dtype)
+                self._mark("experts", dev)
+                y = self._all_to_all(y_r, recv_counts, send_counts)
+                self._mark("combine_a2a", dev)
 
         if side is not None:
             main = torch.cuda.current_stream(hidden.device)
             main.wait_stream(side)
             shared_out.record_stream(main)
-        out = ops.combine(y, inv, tokens, topk, shared_out)
+        if self.world > 1 and use_p2p:
+            out = ops.combine_slots(self._symm.local[buf], tokens, topk, hidden.dtype, dev, shared_out)
+        else:
+            out = ops.combine(y, inv, tokens, topk, shared_out)
         self._mark("sum", dev)
         return out
 

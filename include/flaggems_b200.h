@@ -140,16 +140,17 @@ int fg_gather_rows_fp8(const void* src_q, const float* src_s, void* dst_q, float
  * No counterpart in the reference (its multi-GPU hook is expert_map only); the per-row
  * arithmetic is that of fused_experts_impl, src/flag_gems/fused/fused_moe.py:1994-2183.
  *
- * Packed dispatch row (row_bytes, a multiple of 16, >= K + 4*K/128 + 8):
- *   [0, K) e4m3 | [K, K + 4*K/128) fp32 group scales | int32 local expert | fp32 router weight. */
+ * Packed dispatch row (row_bytes, a multiple of 16, >= K + 4*K/128 + 16):
+ *   [0, K) e4m3 | [K, K + 4*K/128) fp32 group scales | int32 local expert | fp32 router weight
+ *   | int32 route slot at the home rank | int32 home rank. */
 
 /* Quantises (1x128 groups) the tokens x [T,K] into packed rows in send order: output row p is
  * route slot order[p] (token order[p]/topk); its trailer gets topk_ids[slot] % experts_per_rank
  * and topk_w[slot]; inv[slot] = p (nullable). */
 int fg_ep_pack_rows_fp8(const void* x, int x_dtype, int64_t T, int64_t K, int64_t ld_x,
                         const void* topk_ids, int ids_are_i64, const void* topk_w, int topk_w_dtype,
-                        int topk, int experts_per_rank, const int32_t* order, void* packed,
-                        int64_t row_bytes, int32_t* inv, void* stream);
+                        int topk, int experts_per_rank, int home_rank, const int32_t* order,
+                        void* packed, int64_t row_bytes, int32_t* inv, void* stream);
 
 /* Bytes of workspace the two functions below need for n_rows_in routed rows. */
 int64_t fg_moe_routed_workspace_bytes(int64_t n_rows_in, int num_experts, int64_t H, int64_t I);
@@ -164,11 +165,39 @@ int fg_moe_routed_block_fp8_local(void* y, const void* hidden, int hidden_dtype,
                                   const float* s2, int num_experts, int64_t H, int64_t I,
                                   void* workspace, int64_t workspace_bytes, void* stream);
 
-/* Same for R packed rows received from other ranks: y[R, H] in arrival order. */
+/* Same for R packed rows received from other ranks.  n_peers == 0: y[R, H] in arrival order
+ * (to be returned by an all-to-all).  n_peers > 0 (y may be NULL): the combine is fused into
+ * GEMM2's epilogue, which stores each result row straight into the home rank's buffer
+ * peer_out[home rank] at row (route slot), over NVLink peer memory; the home rank may read its
+ * buffer once every rank's call has completed (a stream-ordered barrier or collective). */
 int fg_moe_routed_block_fp8_packed(void* y, const void* rows, int64_t R, int64_t row_bytes,
                                    const void* w1, const void* w2, const float* s1, const float* s2,
                                    int num_experts, int64_t H, int64_t I, void* workspace,
-                                   int64_t workspace_bytes, int out_dtype, void* stream);
+                                   int64_t workspace_bytes, int out_dtype, void* const* peer_out,
+                                   int n_peers, void* stream);
+
+/* fg_moe_grouped_gemm_fp8 with the peer scatter described above: with scatter != 0 and
+ * n_peers > 0, row r (arrival index sid = sorted_ids[r]) goes to peer_out[dest[sid*dest_stride+1]]
+ * at row dest[sid*dest_stride]. */
+int fg_moe_grouped_gemm_fp8_peer(void* c, const void* a, const void* w, const float* a_scale,
+                                 const float* w_scale, const void* topk_weights, int topk_w_dtype,
+                                 int64_t topk_w_stride, const int32_t* sorted_ids,
+                                 const int32_t* expert_ids, const int32_t* num_post_pad,
+                                 int64_t max_rows, int64_t numel, int num_experts, int64_t N,
+                                 int64_t K, int64_t ld_a, int64_t ld_c, int block_rows,
+                                 int scale_mode, int a_scale_per_row, int fuse_silu, int scatter,
+                                 int mul_weight, int out_dtype, const int32_t* dest,
+                                 int64_t dest_stride, void* const* peer_out, int n_peers,
+                                 void* stream);
+
+/* Buffers visible to every rank of one node (set-up time only; these four are the only entry
+ * points that allocate or free device memory).  fg_symm_alloc: cudaMalloc + a 64-byte CUDA IPC
+ * handle to pass to the other processes; fg_symm_open maps a peer's buffer (peer access is
+ * enabled on first use); fg_symm_close / fg_symm_free undo them. */
+int fg_symm_alloc(int64_t bytes, void** ptr, unsigned char* handle64);
+int fg_symm_open(const unsigned char* handle64, void** ptr);
+int fg_symm_close(void* ptr);
+int fg_symm_free(void* ptr);
 
 /* ---- scaled FP8 matrix products (tcgen05 / TMEM / TMA) ---------------------- */
 

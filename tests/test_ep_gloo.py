@@ -29,7 +29,7 @@ class OracleOps:
         self.e_loc = w1.shape[0]
         self.row_bytes = packed_row_bytes(self.hidden)
 
-    def plan_and_pack(self, hidden, topk_ids, topk_w, world):
+    def plan_and_pack(self, hidden, topk_ids, topk_w, world, rank):
         import oracle
 
         t, topk = topk_ids.shape
@@ -46,6 +46,8 @@ class OracleOps:
         off = h + 4 * (h // 128)
         packed[:, off:off + 4] = (flat[order] % self.e_loc).to(torch.int32).view(torch.uint8).reshape(numel, 4)
         packed[:, off + 4:off + 8] = topk_w.reshape(-1).float()[order].view(torch.uint8).reshape(numel, 4)
+        packed[:, off + 8:off + 12] = order.to(torch.int32).view(torch.uint8).reshape(numel, 4)
+        packed[:, off + 12:off + 16] = torch.full((numel,), rank, dtype=torch.int32).view(torch.uint8).reshape(numel, 4)
         inv = torch.empty(numel, dtype=torch.int32)
         inv[order] = torch.arange(numel, dtype=torch.int32)
         return packed, counts, inv

@@ -49,13 +49,21 @@ def _worker(rank, world, port, q):
         e, t = w1.shape[0], hidden.shape[0]
         el, tl = e // world, t // world
         lo = rank * el
-        layer = ExpertParallelMoE(w1[lo:lo + el].to(dev), w2[lo:lo + el].to(dev), s1[lo:lo + el].to(dev),
-                                  s2[lo:lo + el].to(dev), e, rank, world, shared=tuple(x.to(dev) for x in shared))
         sl = slice(rank * tl, (rank + 1) * tl)
-        outs = [layer(hidden[sl].to(dev), tw[sl].to(dev), ti[sl].to(dev)) for _ in range(2)]
         single = _layer_single(case, dev)[sl]
-        q.put((rank, bool(torch.equal(outs[0], single)), bool(torch.equal(outs[0], outs[1])),
-               float((outs[0].float() - single.float()).abs().max()), _cabi.device_status()))
+        equal, repeat, err = True, True, 0.0
+        # all-to-all combine, then the combine fused into GEMM2 over peer memory (3 steps: both buffers)
+        for p2p_rows in (0, tl * ti.shape[1]):
+            layer = ExpertParallelMoE(w1[lo:lo + el].to(dev), w2[lo:lo + el].to(dev), s1[lo:lo + el].to(dev),
+                                      s2[lo:lo + el].to(dev), e, rank, world,
+                                      shared=tuple(x.to(dev) for x in shared), p2p_combine_rows=p2p_rows)
+            outs = [layer(hidden[sl].to(dev), tw[sl].to(dev), ti[sl].to(dev)) for _ in range(3)]
+            equal = equal and bool(torch.equal(outs[0], single))
+            repeat = repeat and bool(torch.equal(outs[0], outs[1])) and bool(torch.equal(outs[0], outs[2]))
+            err = max(err, float((outs[0].float() - single.float()).abs().max()))
+            torch.cuda.synchronize()
+            dist.barrier()
+        q.put((rank, equal, repeat, err, _cabi.device_status()))
     finally:
         dist.destroy_process_group()
 
