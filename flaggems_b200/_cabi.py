@@ -45,6 +45,8 @@ _SIGS = {
     "fg_moe_routed_block_fp8_local": (
         c_int, [_P, _P, c_int, _P, c_int, _P, c_int, c_int64, c_int, _P, _P, _P, _P, c_int, c_int64, c_int64,
                 _P, c_int64, _P]),
+    "fg_moe_routed_block_fp8_local_noalloc": (
+        c_int, [_P, _P, c_int, _P, c_int, _P, c_int, c_int64, c_int, _P, _P, _P, _P, c_int, c_int64, c_int64, _P]),
     "fg_moe_routed_block_fp8_packed": (
         c_int, [_P, _P, c_int64, c_int64, _P, _P, _P, _P, c_int, c_int64, c_int64, _P, c_int64, c_int, _P, c_int,
                 _P]),

@@ -3,7 +3,14 @@
 // quantisation -> grouped GEMM2 with the router weight.  Five launches issued back to back from
 // C++, so the host cost of a layer step does not grow with the number of kernels.  All scratch
 // lives in a caller-provided workspace; nothing is allocated here.
+#include <mutex>
+
 #include "common.cuh"
+
+// Built-in scratch of fg_moe_routed_block_fp8_local_noalloc: part of the library image, so every
+// GPU on which the library is loaded keeps these bytes reserved until the process exits.
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) unsigned char g_routed_scratch[FG_NOALLOC_SCRATCH_BYTES];
 
 namespace {
 
@@ -74,6 +81,23 @@ int run_gemms(void* y, const Workspace& ws, int64_t n_in, const void* w1, const 
                                         dest, dest_stride, peer_out, n_peers, stream);
 }
 
+// Device address of g_routed_scratch on the current device, looked up once per device.
+int builtin_scratch(void** out) {
+    static std::mutex mu;
+    static void* addr[64] = {nullptr};
+    int dev = -1;
+    FG_CUDA(cudaGetDevice(&dev));
+    FG_REQUIRE(dev >= 0 && dev < 64, FG_ERR_UNSUPPORTED, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (!addr[dev]) {
+        void* p = nullptr;
+        FG_CUDA(cudaGetSymbolAddress((void**)&p, g_routed_scratch));
+        addr[dev] = p;
+    }
+    *out = addr[dev];
+    return FG_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -135,6 +159,25 @@ int fg_moe_routed_block_fp8_packed(void* y, const void* rows, int64_t R, int64_t
     const int32_t* dest = reinterpret_cast<const int32_t*>(base + H + 4 * s_cols + 8);
     return run_gemms(y, ws, R, w1, w2, s1, s2, num_experts, H, I, wts, FG_DTYPE_F32, row_bytes / 4, out_dtype,
                      n_peers > 0 ? dest : nullptr, row_bytes / 4, peer_out, n_peers, stream);
+}
+
+int fg_moe_routed_block_fp8_local_noalloc(void* y, const void* hidden, int hidden_dtype, const void* topk_ids,
+                                          int ids_are_i64, const void* topk_w, int topk_w_dtype, int64_t T,
+                                          int topk, const void* w1, const void* w2, const float* s1,
+                                          const float* s2, int num_experts, int64_t H, int64_t I, void* stream) {
+    int rc = check_dims(T * topk, num_experts, H, I, hidden_dtype);
+    if (rc != FG_OK) return rc;
+    const int64_t need = carve(nullptr, T * topk, num_experts, H, I, 2).bytes;
+    FG_REQUIRE(need <= (int64_t)FG_NOALLOC_SCRATCH_BYTES, FG_ERR_UNSUPPORTED,
+               "this problem (T*topk = %lld rows, %d experts, hidden %lld, intermediate %lld) needs %lld bytes of "
+               "scratch; the built-in scratch holds %lld. Use fg_moe_routed_block_fp8_local with your own workspace.",
+               (long long)(T * topk), num_experts, (long long)H, (long long)I, (long long)need,
+               (long long)FG_NOALLOC_SCRATCH_BYTES);
+    void* scratch = nullptr;
+    rc = builtin_scratch(&scratch);
+    if (rc != FG_OK) return rc;
+    return fg_moe_routed_block_fp8_local(y, hidden, hidden_dtype, topk_ids, ids_are_i64, topk_w, topk_w_dtype, T, topk,
+                                         w1, w2, s1, s2, num_experts, H, I, scratch, FG_NOALLOC_SCRATCH_BYTES, stream);
 }
 
 }  // extern "C"

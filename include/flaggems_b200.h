@@ -165,6 +165,27 @@ int fg_moe_routed_block_fp8_local(void* y, const void* hidden, int hidden_dtype,
                                   const float* s2, int num_experts, int64_t H, int64_t I,
                                   void* workspace, int64_t workspace_bytes, void* stream);
 
+/* fg_moe_routed_block_fp8_local for callers that must not allocate device memory and have no
+ * workspace to lend.  It has no counterpart in the reference.  Think of a host that handed the
+ * whole device to its own memory planner at start-up (a later cudaMalloc fails or fragments its
+ * plan), of code that runs where an allocation would stall every stream of the device, or of a
+ * plug-in whose contract leaves all memory management to the embedding process.  The scratch is
+ * a fixed array of FG_NOALLOC_SCRATCH_BYTES inside the library image (each GPU that loads the
+ * library holds it until the process ends).  Problems whose scratch need (the value
+ * fg_moe_routed_workspace_bytes reports) exceeds it are refused with FG_ERR_UNSUPPORTED.
+ * This function never calls cudaMalloc, cudaFree or any allocating routine.  Its first call on
+ * a device looks up the array's device address (cudaGetSymbolAddress) and, like any first
+ * launch, loads kernels: make that call before starting a stream capture.  All calls share the
+ * one array and leave their intermediates in it; no part of it has to start at zero because a
+ * call writes every element before reading it, but two calls whose kernels overlap on the GPU
+ * (different streams, or graphs replayed concurrently) race on it: keep them on one stream. */
+#define FG_NOALLOC_SCRATCH_BYTES (32u << 20)
+int fg_moe_routed_block_fp8_local_noalloc(void* y, const void* hidden, int hidden_dtype,
+                                          const void* topk_ids, int ids_are_i64, const void* topk_w,
+                                          int topk_w_dtype, int64_t T, int topk, const void* w1,
+                                          const void* w2, const float* s1, const float* s2,
+                                          int num_experts, int64_t H, int64_t I, void* stream);
+
 /* Same for R packed rows received from other ranks.  n_peers == 0: y[R, H] in arrival order
  * (to be returned by an all-to-all).  n_peers > 0 (y may be NULL): the combine is fused into
  * GEMM2's epilogue, which stores each result row straight into the home rank's buffer
