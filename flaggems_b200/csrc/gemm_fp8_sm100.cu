@@ -55,7 +55,8 @@ struct GemmParams {
     const int32_t* sorted_ids;
     const int32_t* expert_ids;
     const int32_t* num_post_pad;
-    int block_rows;  // rows per m-tile (TMA box rows of A), <= 128
+    int block_rows;  // grouped: rows per m-tile (TMA box rows of A), <= 128
+    int a_box_rows;  // dense: TMA box rows of A (128, or fewer when M is small)
     int64_t numel;
     int scatter, mul_weight;
     const void* topk_w;
@@ -70,9 +71,12 @@ struct GemmParams {
     unsigned int* status;
 };
 
-template <int BN>
+template <int BN, bool SMALL_A>
 struct Cfg {
-    static constexpr int EPI_WARPS = BN / 32;
+    static_assert(BN == 32 || BN == 64 || BN == 128 || BN == 256, "unsupported tile width");
+    static_assert(!SMALL_A || BN == 32, "the narrow-A layout exists for the 32-wide tile only");
+    static constexpr int COLS = BN >= 128 ? 128 : BN;          // accumulator columns per epilogue thread
+    static constexpr int EPI_WARPS = BN >= 128 ? BN / 32 : 4;  // one warp per 32 TMEM lanes, x column halves
     static constexpr int FIRST_EPI_WARP = 4;  // warps 0-3: TMA, MMA, two spare (one warpgroup)
     static constexpr int THREADS = 32 * (FIRST_EPI_WARP + EPI_WARPS);
     // With 384 threads the launch-time register file share is 168 per thread; the epilogue
@@ -82,13 +86,22 @@ struct Cfg {
     static constexpr bool REBALANCE_REGS = BN == 256;
     static constexpr int REGS_PRODUCER = 40, REGS_EPILOGUE = 232;
     static_assert(128 * REGS_PRODUCER + 256 * REGS_EPILOGUE <= 384 * 168, "setmaxnreg.inc would wait forever");
-    static constexpr int A_BYTES = BLOCK_M * BLOCK_K;
+    // Narrow-A layout (M <= 32, weight streaming): only 32 rows of A are staged per K block.  The
+    // MMA still reads 128 rows from the stage's address; rows 32..127 are whatever follows in
+    // shared memory (later stages or the tail pad) and only feed accumulator rows nobody reads.
+    static constexpr int A_ROWS_SMEM = SMALL_A ? 32 : BLOCK_M;
+    static constexpr int A_BYTES = A_ROWS_SMEM * BLOCK_K;
     static constexpr int B_BYTES = BN * BLOCK_K;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = BN == 256 ? 4 : 6;
-    static constexpr int TMEM_COLS = 2 * BN;
-    static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
+    static constexpr int STAGES = BN == 256 ? 4 : BN == 128 ? 6 : BN == 64 ? 8 : (SMALL_A ? 22 : 9);
+    static constexpr int TAIL_PAD = SMALL_A ? BLOCK_M * BLOCK_K : 0;
+    static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+    static constexpr int BAR_BYTES = 512;  // (2*STAGES + 4) mbarriers, TMEM base slot, abort flag
+    static_assert((2 * STAGES + 4) * 8 + 16 <= BAR_BYTES, "barrier area too small");
+    static constexpr int EPI_STAGE_BYTES = 2048;  // per epilogue warp: 32 rows x 64 bytes
+    static constexpr int SMEM_BYTES =
+        STAGES * STAGE_BYTES + TAIL_PAD + BAR_BYTES + EPI_WARPS * EPI_STAGE_BYTES + 1024;
+    static_assert(SMEM_BYTES <= 232448, "over the 227 KB shared memory limit");
 };
 
 __device__ __forceinline__ float load_as_float(const void* p, int dtype, int64_t i) {
@@ -147,6 +160,46 @@ __device__ __forceinline__ void store_chunk(void* row_ptr, int col0, const float
     }
 }
 
+// Stores 32 consecutive 16-bit output values per lane (lane = row) with coalescing: the warp
+// transposes the 32 x 64-byte block through its private shared-memory staging area (16-byte
+// chunks XOR-swizzled so that neither side has bank conflicts) and then writes 64 contiguous
+// bytes per row, eight rows per instruction, instead of 16 bytes to 32 different rows.  That is
+// what makes the stores to a peer GPU's memory (fused combine) efficient on NVLink, and it halves
+// the number of partial-sector writes for local outputs.  All 32 lanes must call it.
+__device__ __forceinline__ void store_chunk_coalesced(uint8_t* stage, int lane, const float (&v)[32],
+                                                      uint8_t* my_row_ptr, bool my_row_ok, int col0, int dtype) {
+    uint32_t w[16];
+    if (dtype == FG_DTYPE_BF16) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+    }
+    const int wsw = (lane >> 1) & 3;
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+        *reinterpret_cast<uint4*>(stage + lane * 64 + ((k ^ wsw) << 4)) =
+            make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
+    __syncwarp();
+    const int c = lane & 3;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int r = (lane >> 2) + 8 * j;
+        const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 64 + ((c ^ ((r >> 1) & 3)) << 4));
+        const unsigned long long ptr = __shfl_sync(0xffffffffu, (unsigned long long)my_row_ptr, r);
+        const int ok = __shfl_sync(0xffffffffu, (int)my_row_ok, r);
+        if (ok) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(ptr) + (size_t)col0 * 2 + (c << 4)) = val;
+    }
+    __syncwarp();
+}
+
 struct TileCoord {
     int m_blk, n_blk;
 };
@@ -162,22 +215,24 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int num_m, int num_n) {
     return tc;
 }
 
-template <int BN, bool BLOCK_SCALED, bool FUSE_SILU>
-__global__ void __launch_bounds__(Cfg<BN>::THREADS, 1)
+template <int BN, bool BLOCK_SCALED, bool FUSE_SILU, bool SMALL_A>
+__global__ void __launch_bounds__(Cfg<BN, SMALL_A>::THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                 const GemmParams p) {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, SMALL_A>;
+    static_assert(!FUSE_SILU || BN >= 128, "fused SiLU needs a tile of at least 128 columns");
     constexpr int STAGES = C::STAGES;
     constexpr int OUT_TILE_N = FUSE_SILU ? BN / 2 : BN;  // output columns per tile
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * C::STAGE_BYTES);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * C::STAGE_BYTES + C::TAIL_PAD);
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* tmem_full = empty_bar + STAGES;
     uint64_t* tmem_empty = tmem_full + 2;
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
     volatile uint32_t* abort_flag = tmem_base_slot + 1;
+    uint8_t* epi_stage_base = smem + STAGES * C::STAGE_BYTES + C::TAIL_PAD + C::BAR_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -216,7 +271,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     const int num_n = (p.n_out + OUT_TILE_N - 1) / OUT_TILE_N;
     const int num_tiles = num_m * num_n;
     const int a_rows_step = p.grouped ? p.block_rows : BLOCK_M;
-    const uint32_t stage_tx = (uint32_t)(a_rows_step * BLOCK_K + C::B_BYTES);
+    const uint32_t stage_tx = (uint32_t)((p.grouped ? p.block_rows : p.a_box_rows) * BLOCK_K + C::B_BYTES);
 
     if (warp < C::FIRST_EPI_WARP) {
       if constexpr (C::REBALANCE_REGS) setmaxnreg_dec<C::REGS_PRODUCER>();
@@ -305,6 +360,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         const int half = C::EPI_WARPS == 8 ? ew / 4 : 0;
         const int r_in_tile = quad * 32 + lane;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+        uint8_t* epi_stage = epi_stage_base + ew * C::EPI_STAGE_BYTES;
         uint32_t acc_iter = 0;
         bool ok = true;
 
@@ -345,7 +401,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             uint8_t* out_ptr = out_base + out_row * p.ld_c * esz;
             // column of output chunk c (32 wide) handled by this thread
             const int out_col_base = n0 + (FUSE_SILU ? 64 * half : 128 * half);
-            constexpr int OUT_CHUNKS = FUSE_SILU ? 2 : 4;
+            constexpr int OUT_CHUNKS = FUSE_SILU ? 2 : C::COLS / 32;
 
             if (expert < 0) {
                 // Block of an expert that is not on this rank: the rows are defined to be zero.
@@ -409,17 +465,20 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                         }
                     }
                     const int nc = min(32, p.n_out - col);
-                    if (row_ok && nc > 0) store_chunk(out_ptr, col, v, nc, p.out_dtype, p.c_vec_ok);
+                    if (nc == 32 && p.c_vec_ok && esz == 2)
+                        store_chunk_coalesced(epi_stage, lane, v, out_ptr, row_ok, col, p.out_dtype);
+                    else if (row_ok && nc > 0)
+                        store_chunk(out_ptr, col, v, nc, p.out_dtype, p.c_vec_ok);
                 }
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&tmem_empty[buf]);
                 ++acc_iter;
             } else {
-                // 128 fp32 accumulators per thread, kept as 64 packed pairs for FFMA2.
-                uint64_t acc[64];
+                // COLS fp32 accumulators per thread, kept as packed pairs for FFMA2.
+                uint64_t acc[C::COLS / 2];
 #pragma unroll
-                for (int i = 0; i < 64; ++i) acc[i] = 0ull;
+                for (int i = 0; i < C::COLS / 2; ++i) acc[i] = 0ull;
                 // Block row of Bs for this thread's columns (two of them with fused SiLU).
                 const float* bs_e = p.sb + (int64_t)expert * p.bs_stride_e;
                 int nb0, nb1;
@@ -454,22 +513,32 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     if (!ok) break;
                     tc_fence_after_sync();
                     const uint32_t tbuf = lane_addr + buf * BN;
-                    // Two rounds of 64 columns: one load instruction, one wait, 32 packed FMAs each.
-                    uint32_t raw[64];
+                    auto release = [&]() {
+                        // Every column of this buffer is in registers: hand it back to the MMA warp
+                        // before the last part is folded.
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+                    };
+                    if constexpr (C::COLS >= 64) {
+                        // Rounds of 64 columns: one load instruction, one wait, 32 packed FMAs each.
+                        uint32_t raw[64];
 #pragma unroll
-                    for (int r = 0; r < 2; ++r) {
-                        tmem_ld_32x32b_x64(tbuf + chunk_col(2 * r), raw);
-                        tmem_ld_wait();
-                        if (r == 1) {
-                            // Every column of this buffer is now in registers: hand it back to the
-                            // MMA warp before the last half is folded.
-                            tc_fence_before_sync();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+                        for (int r = 0; r < C::COLS / 64; ++r) {
+                            tmem_ld_32x32b_x64(tbuf + chunk_col(2 * r), raw);
+                            tmem_ld_wait();
+                            if (r == C::COLS / 64 - 1) release();
+                            const uint64_t sc = (FUSE_SILU && r == 1) ? sc1 : sc0;
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) ffma2(acc[32 * r + i], raw[2 * i], raw[2 * i + 1], sc);
                         }
-                        const uint64_t sc = (FUSE_SILU && r == 1) ? sc1 : sc0;
+                    } else {
+                        uint32_t raw[32];
+                        tmem_ld_32x32b_x32(tbuf + chunk_col(0), raw);
+                        tmem_ld_wait();
+                        release();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) ffma2(acc[32 * r + i], raw[2 * i], raw[2 * i + 1], sc);
+                        for (int i = 0; i < 16; ++i) ffma2(acc[i], raw[2 * i], raw[2 * i + 1], sc0);
                     }
                     ++acc_iter;
                 }
@@ -491,7 +560,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                         }
                     }
                     const int nc = min(32, p.n_out - col);
-                    if (row_ok && nc > 0) store_chunk(out_ptr, col, v, nc, p.out_dtype, p.c_vec_ok);
+                    if (nc == 32 && p.c_vec_ok && esz == 2)
+                        store_chunk_coalesced(epi_stage, lane, v, out_ptr, row_ok, col, p.out_dtype);
+                    else if (row_ok && nc > 0)
+                        store_chunk(out_ptr, col, v, nc, p.out_dtype, p.c_vec_ok);
                 }
             }
         }
@@ -543,10 +615,10 @@ int make_map(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, uint64_
     return FG_OK;
 }
 
-template <int BN, bool BS, bool SILU>
+template <int BN, bool BS, bool SILU, bool SMALL_A = false>
 int launch_inst(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int max_tiles, cudaStream_t st) {
-    using C = Cfg<BN>;
-    auto kernel = gemm_fp8_kernel<BN, BS, SILU>;
+    using C = Cfg<BN, SMALL_A>;
+    auto kernel = gemm_fp8_kernel<BN, BS, SILU, SMALL_A>;
     static bool attr_done = false;
     if (!attr_done) {
         FG_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
@@ -572,37 +644,59 @@ int launch_gemm(GemmParams& p, const void* a, int64_t a_rows, int64_t ld_a, cons
     p.c_vec_ok = ((uintptr_t)p.c % 16 == 0) && ((p.ld_c * esz) % 16 == 0);
 
     const int64_t m_tiles = p.grouped ? a_rows / p.block_rows : fg_cdiv(p.M, BLOCK_M);
-    // Wide tiles when they still fill the machine, otherwise narrower ones.
-    const int out_per_256 = fuse_silu ? 128 : 256;
-    const int64_t tiles256 = m_tiles * fg_cdiv(p.n_out, out_per_256);
-    const bool wide = tiles256 >= fg_num_sms();
-    const int bn = wide ? 256 : 128;
+    const int sms = fg_num_sms();
+    // Tile width: the widest tile that still gives every SM a tile.  Narrow tiles exist for
+    // small M (weight streaming: the job is to keep all SMs pulling B from HBM).
+    int bn;
+    bool small_a = false;
+    if (fuse_silu) {
+        bn = m_tiles * fg_cdiv(p.n_out, 128) >= sms ? 256 : 128;
+    } else if (m_tiles * fg_cdiv(p.n_out, 256) >= sms) {
+        bn = 256;
+    } else if (m_tiles * fg_cdiv(p.n_out, 128) >= sms || p.grouped) {
+        bn = 128;
+    } else if (m_tiles * fg_cdiv(p.n_out, 64) >= sms) {
+        bn = 64;
+    } else {
+        bn = 32;
+        small_a = p.M <= 32;
+    }
+    p.a_box_rows = BLOCK_M;
+    if (!p.grouped && p.M < BLOCK_M) p.a_box_rows = (int)((p.M + 7) / 8 * 8);
     const int out_tile = fuse_silu ? bn / 2 : bn;
     const int64_t tiles = m_tiles * fg_cdiv(p.n_out, out_tile);
     FG_REQUIRE(tiles < (1ll << 31), FG_ERR_UNSUPPORTED, "too many tiles");
     if (tiles == 0) return FG_OK;
 
     CUtensorMap ta, tb;
-    int rc = make_map(&ta, a, (uint64_t)p.K, (uint64_t)a_rows, 1, (uint64_t)ld_a, 0, (uint32_t)(p.grouped ? p.block_rows : BLOCK_M), 2);
+    int rc = make_map(&ta, a, (uint64_t)p.K, (uint64_t)a_rows, 1, (uint64_t)ld_a, 0,
+                      (uint32_t)(p.grouped ? p.block_rows : p.a_box_rows), 2);
     if (rc != FG_OK) return rc;
     rc = make_map(&tb, b, (uint64_t)p.K, (uint64_t)p.N, (uint64_t)num_experts, (uint64_t)ld_b,
                   (uint64_t)ld_b * (uint64_t)p.N, (uint32_t)(fuse_silu ? bn / 2 : bn), 3);
     if (rc != FG_OK) return rc;
 
-#define FG_DISPATCH(BN_)                                                                       \
-    if (block_scaled) {                                                                        \
-        if (fuse_silu) return launch_inst<BN_, true, true>(ta, tb, p, (int)tiles, st);         \
-        return launch_inst<BN_, true, false>(ta, tb, p, (int)tiles, st);                       \
-    } else {                                                                                   \
-        if (fuse_silu) return launch_inst<BN_, false, true>(ta, tb, p, (int)tiles, st);        \
-        return launch_inst<BN_, false, false>(ta, tb, p, (int)tiles, st);                      \
+    const int t = (int)tiles;
+    if (bn == 256) {
+        if (block_scaled) return fuse_silu ? launch_inst<256, true, true>(ta, tb, p, t, st)
+                                           : launch_inst<256, true, false>(ta, tb, p, t, st);
+        return fuse_silu ? launch_inst<256, false, true>(ta, tb, p, t, st)
+                         : launch_inst<256, false, false>(ta, tb, p, t, st);
     }
-    if (wide) {
-        FG_DISPATCH(256)
-    } else {
-        FG_DISPATCH(128)
+    if (bn == 128) {
+        if (block_scaled) return fuse_silu ? launch_inst<128, true, true>(ta, tb, p, t, st)
+                                           : launch_inst<128, true, false>(ta, tb, p, t, st);
+        return fuse_silu ? launch_inst<128, false, true>(ta, tb, p, t, st)
+                         : launch_inst<128, false, false>(ta, tb, p, t, st);
     }
-#undef FG_DISPATCH
+    if (bn == 64)
+        return block_scaled ? launch_inst<64, true, false>(ta, tb, p, t, st)
+                            : launch_inst<64, false, false>(ta, tb, p, t, st);
+    if (small_a)
+        return block_scaled ? launch_inst<32, true, false, true>(ta, tb, p, t, st)
+                            : launch_inst<32, false, false, true>(ta, tb, p, t, st);
+    return block_scaled ? launch_inst<32, true, false>(ta, tb, p, t, st)
+                        : launch_inst<32, false, false>(ta, tb, p, t, st);
 }
 
 bool dtype_ok(int d) { return d == FG_DTYPE_BF16 || d == FG_DTYPE_F16 || d == FG_DTYPE_F32; }

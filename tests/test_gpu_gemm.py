@@ -29,7 +29,10 @@ def _llama_like(m, n, k, seed=0):
 
 @pytest.mark.parametrize("m,n,k", [(1, 256, 128), (16, 512, 4096), (128, 4096, 4096), (256, 4096, 4096),
                                    (1024, 6144, 4096), (33, 208, 496), (83, 7744, 3888), (129, 144, 144),
-                                   (512, 4096, 14336)])
+                                   (512, 4096, 14336),
+                                   # decode-sized M: the narrow tiles that keep every SM streaming weights
+                                   (1, 4096, 4096), (16, 6144, 4096), (32, 28672, 4096), (33, 4096, 4096),
+                                   (128, 4096, 14336), (8, 4096, 14336)])
 @pytest.mark.parametrize("bias", [False, True])
 def test_cutlass_scaled_mm_per_token_per_channel(m, n, k, bias):
     aq, sa, wq, sw, g = _llama_like(m, n, k)
@@ -146,7 +149,8 @@ def _block_case(m, n, k, seed=0):
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 512), (64, 128, 128), (256, 256, 256), (83, 7752, 3840),
-                                   (1, 2112, 7168), (64, 4096, 7168), (512, 2112, 7168), (300, 1536, 1024)])
+                                   (1, 2112, 7168), (64, 4096, 7168), (512, 2112, 7168), (300, 1536, 1024),
+                                   (16, 4096, 7168), (128, 2112, 7168), (1, 24576, 7168), (40, 18432, 7168)])
 def test_w8a8_block_fp8_matmul(m, n, k):
     aq, a_s, wq, w_s = _block_case(m, n, k)
     out = flag_gems.w8a8_block_fp8_matmul(aq.cuda(), wq.cuda(), a_s.cuda(), w_s.cuda(), [128, 128])
