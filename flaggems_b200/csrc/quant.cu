@@ -294,9 +294,11 @@ int launch_quant_t(const QuantArgs& a, cudaStream_t st) {
         return FG_OK;
     };
     switch (a.group) {
-        case 64: return small(group_quant_kernel<T, MODE, 8, 1>, 8);
-        case 128: return small(group_quant_kernel<T, MODE, 16, 1>, 16);
-        case 256: return small(group_quant_kernel<T, MODE, 32, 1>, 32);
+        // sixteen elements (two 16-byte loads) per lane: the shuffle reduction, the scale and the
+        // index arithmetic are paid once per 16 elements, and four loads per lane are in flight
+        case 64: return small(group_quant_kernel<T, MODE, 4, 2>, 4);
+        case 128: return small(group_quant_kernel<T, MODE, 8, 2>, 8);
+        case 256: return small(group_quant_kernel<T, MODE, 16, 2>, 16);
         case 512: return small(group_quant_kernel<T, MODE, 32, 2>, 32);
         default: break;
     }
