@@ -645,17 +645,19 @@ int launch_gemm(GemmParams& p, const void* a, int64_t a_rows, int64_t ld_a, cons
 
     const int64_t m_tiles = p.grouped ? a_rows / p.block_rows : fg_cdiv(p.M, BLOCK_M);
     const int sms = fg_num_sms();
-    // Tile width: the widest tile that still gives every SM a tile.  Narrow tiles exist for
-    // small M (weight streaming: the job is to keep all SMs pulling B from HBM).
+    // Tile width.  One K block costs a CTA about the same time whatever the width (an MMA with
+    // M = 128 streams 128 rows of A however few columns it has), so the widest tile wins as long
+    // as most SMs still get a tile; below that, narrower tiles buy CTAs.
+    const int64_t enough = (int64_t)sms * 5 / 8;
     int bn;
     bool small_a = false;
     if (fuse_silu) {
-        bn = m_tiles * fg_cdiv(p.n_out, 128) >= sms ? 256 : 128;
-    } else if (m_tiles * fg_cdiv(p.n_out, 256) >= sms) {
+        bn = m_tiles * fg_cdiv(p.n_out, 128) >= enough ? 256 : 128;
+    } else if (m_tiles * fg_cdiv(p.n_out, 256) >= enough) {
         bn = 256;
-    } else if (m_tiles * fg_cdiv(p.n_out, 128) >= sms || p.grouped) {
+    } else if (m_tiles * fg_cdiv(p.n_out, 128) >= enough || p.grouped) {
         bn = 128;
-    } else if (m_tiles * fg_cdiv(p.n_out, 64) >= sms) {
+    } else if (m_tiles * fg_cdiv(p.n_out, 64) >= enough) {
         bn = 64;
     } else {
         bn = 32;
