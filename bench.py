@@ -334,7 +334,8 @@ def run_ours(args):
     w1, w2, s1, s2 = make_expert_weights(e_loc, rank * e_loc, dev)
     shared = make_shared_weights(dev)
     layer = ExpertParallelMoE(w1, w2, s1, s2, EXPERTS, rank, world, shared=shared,
-                              p2p_combine_rows=0 if args.a2a_combine else t_loc * TOPK)
+                              p2p_combine_rows=0 if args.a2a_combine else t_loc * TOPK,
+                              p2p_dispatch_rows=0 if (args.a2a_combine or args.a2a_dispatch) else TOKENS * TOPK)
     tw_all, ti_all = make_router(TOKENS, EXPERTS, TOPK)
     # logical expert -> physical slot (rank * E_loc + local index); identical on every rank
     from flaggems_b200.ep import balanced_expert_placement
@@ -448,6 +449,10 @@ def run_ours(args):
                 "d2h_bytes_per_step": d2h * world, "ms_per_step": round(ms_e2e, 4)},
         "gpu_launches": int(launches), "roofline": roofline, "device_status": status,
         "phase_ms_rank0": phases,
+        "dispatch": ("n/a (single rank)" if world == 1 else
+                     "NCCL all_to_all_single" if (args.a2a_combine or args.a2a_dispatch) else
+                     "fused into the quantisation kernel: packed rows stored to the destination rank over NVLink "
+                     "peer memory, counts by a stream-ordered all-gather (no host wait in the step)"),
         "combine": ("n/a (single rank)" if world == 1 else
                     "NCCL all_to_all_single" if args.a2a_combine else
                     "fused into GEMM2's epilogue: rows stored to the home rank over NVLink peer memory"),
@@ -498,6 +503,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-tokens", type=int, default=16, help="tokens in the bounded CPU sample")
     ap.add_argument("--no-extras", action="store_true", help="skip the dense GEMM / quant figures at N=1")
+    ap.add_argument("--a2a-dispatch", action="store_true",
+                    help="send packed rows by NCCL all-to-all instead of storing them to peers from the pack kernel")
     ap.add_argument("--a2a-combine", action="store_true",
                     help="return expert outputs by NCCL all-to-all instead of the fused peer-memory combine")
     args = ap.parse_args()

@@ -37,7 +37,12 @@ _SIGS = {
     "fg_gather_rows_fp8": (
         c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int64, _P, c_int32, c_int32, _P, _P]),
     "fg_moe_align_block_size_ex": (
-        c_int, [_P, c_int, c_int64, c_int, c_int, _P, c_int, _P, c_int64, _P, c_int64, _P, c_int64, c_int, _P, _P]),
+        c_int, [_P, c_int, c_int64, c_int, c_int, _P, c_int, _P, c_int64, _P, c_int64, _P, c_int64, c_int, _P, _P,
+                _P]),
+    "fg_ep_pack_rows_fp8_peer": (
+        c_int, [_P, c_int, c_int64, c_int64, c_int64, _P, c_int, _P, c_int, c_int, c_int, c_int, _P, _P, c_int64,
+                _P, _P, _P, c_int, _P]),
+    "fg_ep_plan": (c_int, [_P, c_int, c_int, _P, _P]),
     "fg_ep_pack_rows_fp8": (
         c_int, [_P, c_int, c_int64, c_int64, c_int64, _P, c_int, _P, c_int, c_int, c_int, c_int, _P, _P, c_int64,
                 _P, _P]),
@@ -49,7 +54,7 @@ _SIGS = {
         c_int, [_P, _P, c_int, _P, c_int, _P, c_int, c_int64, c_int, _P, _P, _P, _P, c_int, c_int64, c_int64, _P]),
     "fg_moe_routed_block_fp8_packed": (
         c_int, [_P, _P, c_int64, c_int64, _P, _P, _P, _P, c_int, c_int64, c_int64, _P, c_int64, c_int, _P, c_int,
-                _P]),
+                _P, _P]),
     "fg_moe_grouped_gemm_fp8_peer": (
         c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int64, _P, _P, _P, c_int64, c_int64, c_int, c_int64, c_int64,
                 c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int64, _P, c_int, _P]),

@@ -37,6 +37,7 @@ struct AlignArgs {
     int64_t ids_stride;       // elements between consecutive ids (1 = dense)
     int32_t id_div;           // bucket = id / id_div
     int32_t* expert_counts;   // nullable: rows per bucket before padding
+    const int32_t* numel_dev; // nullable: device-side slot count (numel is then the capacity)
 };
 
 template <typename IdT>
@@ -60,12 +61,19 @@ __global__ void __launch_bounds__(ALIGN_THREADS, 1) moe_align_kernel(AlignArgs a
     __syncthreads();
 
     // Segment of this warp: contiguous, multiple of 32 slots, in global index order.
+    // Slots actually present: the host bound, or fewer when a device-side count is given (the
+    // padding value stays the host bound, so "index < bound" still tells real rows from padding).
+    int64_t numel = a.numel;
+    if (a.numel_dev) {
+        const int64_t v = *a.numel_dev;
+        numel = v < 0 ? 0 : (v < numel ? v : numel);
+    }
     const int64_t n_segments = (int64_t)n_ranks * ALIGN_WARPS;
-    int64_t seg_len = (a.numel + n_segments - 1) / n_segments;
+    int64_t seg_len = (numel + n_segments - 1) / n_segments;
     seg_len = (seg_len + 31) / 32 * 32;
     const int64_t seg_id = (int64_t)rank * ALIGN_WARPS + warp;
-    const int64_t seg_begin = seg_id * seg_len < a.numel ? seg_id * seg_len : a.numel;
-    const int64_t seg_end = seg_begin + seg_len < a.numel ? seg_begin + seg_len : a.numel;
+    const int64_t seg_begin = seg_id * seg_len < numel ? seg_id * seg_len : numel;
+    const int64_t seg_end = seg_begin + seg_len < numel ? seg_begin + seg_len : numel;
     const IdT* ids = reinterpret_cast<const IdT*>(a.topk_ids);
     int32_t* my_hist = warp_hist + warp * E;
 
@@ -257,6 +265,25 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint8_t* __restr
     }
 }
 
+// Send/receive geometry of one rank, from the matrix counts[src][dst] of routed rows.
+__global__ void ep_plan_kernel(const int32_t* __restrict__ counts, int world, int me, int32_t* __restrict__ plan) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int32_t run = 0;
+    for (int d = 0; d < world; ++d) {  // plan[0..world]: first send-order row for each destination
+        plan[d] = run;
+        run += counts[me * world + d];
+    }
+    plan[world] = run;
+    int32_t total = 0;
+    for (int d = 0; d < world; ++d) {  // plan[9+d]: where this rank's rows start in d's receive buffer
+        int32_t off = 0;
+        for (int r = 0; r < me; ++r) off += counts[r * world + d];
+        plan[9 + d] = off;
+    }
+    for (int r = 0; r < world; ++r) total += counts[r * world + me];
+    plan[17] = total;  // rows this rank receives
+}
+
 unsigned grid_for(int64_t work_items, int per_block) {
     int64_t b = fg_cdiv(work_items, per_block);
     const int64_t cap = (int64_t)fg_num_sms() * 16;
@@ -274,13 +301,13 @@ int fg_moe_align_block_size(const void* topk_ids, int ids_are_i64, int64_t numel
                             int32_t* expert_ids, int64_t n_blocks, int32_t* num_post_pad, void* stream) {
     return fg_moe_align_block_size_ex(topk_ids, ids_are_i64, numel, num_experts, block_size, expert_map,
                                       expert_map_len, sorted_ids, max_pad, expert_ids, n_blocks, num_post_pad, 1, 1,
-                                      nullptr, stream);
+                                      nullptr, nullptr, stream);
 }
 
 int fg_moe_align_block_size_ex(const void* topk_ids, int ids_are_i64, int64_t numel, int num_experts, int block_size,
                                const int32_t* expert_map, int expert_map_len, int32_t* sorted_ids, int64_t max_pad,
                                int32_t* expert_ids, int64_t n_blocks, int32_t* num_post_pad, int64_t ids_stride,
-                               int id_div, int32_t* expert_counts, void* stream) {
+                               int id_div, int32_t* expert_counts, const int32_t* numel_dev, void* stream) {
     FG_REQUIRE(ids_stride >= 1 && id_div >= 1, FG_ERR_INVALID_ARGUMENT, "ids_stride and id_div must be >= 1");
     FG_REQUIRE(numel >= 0 && num_experts > 0 && block_size > 0, FG_ERR_INVALID_ARGUMENT,
                "numel %lld, num_experts %d, block_size %d", (long long)numel, num_experts, block_size);
@@ -298,7 +325,7 @@ int fg_moe_align_block_size_ex(const void* topk_ids, int ids_are_i64, int64_t nu
                "expert_map has %d entries for %d experts", expert_map_len, num_experts);
 
     AlignArgs a{topk_ids, numel, num_experts, block_size, expert_map, expert_map_len,
-                sorted_ids, max_pad, expert_ids, n_blocks, num_post_pad, ids_stride, id_div, expert_counts};
+                sorted_ids, max_pad, expert_ids, n_blocks, num_post_pad, ids_stride, id_div, expert_counts, numel_dev};
     // One CTA handles 32 warps x 128 slots comfortably; grow the cluster with numel up to 8.
     int ranks = 1;
     while (ranks < 8 && (int64_t)ranks * ALIGN_THREADS * 4 < numel) ranks *= 2;
@@ -326,6 +353,15 @@ int fg_moe_align_block_size_ex(const void* topk_ids, int ids_are_i64, int64_t nu
     cfg.numAttrs = 1;
     FG_CUDA(cudaLaunchKernelEx(&cfg, kernel, a));
     fg_count_launch(1);
+    return FG_OK;
+}
+
+int fg_ep_plan(const int32_t* counts, int world, int rank, int32_t* plan, void* stream) {
+    FG_REQUIRE(counts && plan && world >= 1 && world <= 8 && rank >= 0 && rank < world, FG_ERR_INVALID_ARGUMENT,
+               "bad arguments (world must be 1..8)");
+    ep_plan_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(counts, world, rank, plan);
+    fg_count_launch(1);
+    FG_LAUNCH_CHECK();
     return FG_OK;
 }
 

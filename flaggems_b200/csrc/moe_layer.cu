@@ -134,7 +134,7 @@ int fg_moe_routed_block_fp8_local(void* y, const void* hidden, int hidden_dtype,
 int fg_moe_routed_block_fp8_packed(void* y, const void* rows, int64_t R, int64_t row_bytes, const void* w1,
                                    const void* w2, const float* s1, const float* s2, int num_experts, int64_t H,
                                    int64_t I, void* workspace, int64_t workspace_bytes, int out_dtype,
-                                   void* const* peer_out, int n_peers, void* stream) {
+                                   void* const* peer_out, int n_peers, const int32_t* n_rows_dev, void* stream) {
     int rc = check_dims(R, num_experts, H, I, out_dtype);
     if (rc != FG_OK) return rc;
     if (R == 0) return FG_OK;
@@ -151,7 +151,8 @@ int fg_moe_routed_block_fp8_packed(void* y, const void* rows, int64_t R, int64_t
     const int32_t* ids = reinterpret_cast<const int32_t*>(base + H + 4 * s_cols);
     const float* wts = reinterpret_cast<const float*>(base + H + 4 * s_cols + 4);
     rc = fg_moe_align_block_size_ex(ids, 0, R, num_experts, TILE_ROWS, nullptr, 0, ws.sorted_ids, ws.max_pad,
-                                    ws.expert_ids, ws.n_blocks, ws.post_pad, row_bytes / 4, 1, nullptr, stream);
+                                    ws.expert_ids, ws.n_blocks, ws.post_pad, row_bytes / 4, 1, nullptr, n_rows_dev,
+                                    stream);
     if (rc != FG_OK) return rc;
     rc = fg_gather_rows_fp8(base, reinterpret_cast<const float*>(base + H), ws.a1, ws.a1s, ws.rows, H, s_cols,
                             row_bytes, row_bytes / 4, ws.sorted_ids, 1, (int32_t)R, ws.post_pad, stream);

@@ -40,7 +40,22 @@ struct QuantArgs {
     int32_t meta_rank;  // this rank (home of the rows)
     int64_t meta_off;
     int32_t* inv;  // nullable: inv[route slot] = output row
+    // Direct dispatch: output row p (send order) is written into the receive buffer of its
+    // destination rank d (plan[d] <= p < plan[d+1]) at row plan[9+d] + (p - plan[d]).
+    const int32_t* plan;  // nullable
+    int world;
+    uint8_t* peer_q[8];
 };
+
+// Start of the packed row that output row `r` is written to.
+__device__ __forceinline__ uint8_t* packed_row_ptr(const QuantArgs& a, int64_t r) {
+    if (!a.plan) return a.q + r * a.ld_q;
+    int d = 0;
+#pragma unroll
+    for (int i = 1; i < 8; ++i)
+        if (i < a.world && r >= a.plan[i]) d = i;
+    return a.peer_q[d] + (int64_t)(a.plan[9 + d] + (int32_t)r - a.plan[d]) * a.ld_q;
+}
 
 __device__ __forceinline__ void write_row_meta(const QuantArgs& a, int64_t out_row) {
     const int32_t slot = a.row_index[out_row];
@@ -50,7 +65,7 @@ __device__ __forceinline__ void write_row_meta(const QuantArgs& a, int64_t out_r
     if (a.meta_w_dtype == FG_DTYPE_BF16) w = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.meta_w)[slot]);
     else if (a.meta_w_dtype == FG_DTYPE_F16) w = __half2float(reinterpret_cast<const __half*>(a.meta_w)[slot]);
     else w = reinterpret_cast<const float*>(a.meta_w)[slot];
-    uint8_t* m = a.q + out_row * a.ld_q + a.meta_off;
+    uint8_t* m = packed_row_ptr(a, out_row) + a.meta_off;
     *reinterpret_cast<int32_t*>(m) = (int32_t)(e % a.meta_mod);
     *reinterpret_cast<float*>(m + 4) = w;
     *reinterpret_cast<int32_t*>(m + 8) = slot;
@@ -204,17 +219,21 @@ __global__ void __launch_bounds__(256) group_quant_kernel(QuantArgs a) {
             const float s = make_scale<MODE>(amax, a.eps, a.pow2);
             const Divider d = make_divider<MODE>(s);
             if (row[u] < rows) {
+                uint8_t* qrow = a.meta_ids ? packed_row_ptr(a, row[u]) : a.q + (int64_t)row[u] * a.ld_q;
 #pragma unroll
                 for (int w = 0; w < VPT; ++w) {
                     float q[8];
 #pragma unroll
                     for (int i = 0; i < 8; i += 2) apply_divider2<MODE>(v[u][w][i], v[u][w][i + 1], d, q[i], q[i + 1]);
-                    *reinterpret_cast<uint2*>(a.q + (int64_t)row[u] * a.ld_q + cg[u] * GROUP +
-                                              (w * TPG + lane_in_team) * 8) = fg_pack_e4m3x8(q);
+                    *reinterpret_cast<uint2*>(qrow + cg[u] * GROUP + (w * TPG + lane_in_team) * 8) = fg_pack_e4m3x8(q);
                 }
                 if (lane_in_team == 0) {
-                    a.s[(int64_t)row[u] * a.s_row_stride + (int64_t)cg[u] * a.s_col_stride] = s;
-                    if (a.meta_ids && cg[u] == 0) write_row_meta(a, row[u]);
+                    if (a.meta_ids) {  // packed row: scales sit behind the payload of the same row
+                        reinterpret_cast<float*>(qrow + a.K)[cg[u]] = s;
+                        if (cg[u] == 0) write_row_meta(a, row[u]);
+                    } else {
+                        a.s[(int64_t)row[u] * a.s_row_stride + (int64_t)cg[u] * a.s_col_stride] = s;
+                    }
                 }
             }
             cg[u] += step_cg;
@@ -405,13 +424,24 @@ int fg_ep_pack_rows_fp8(const void* x, int x_dtype, int64_t T, int64_t K, int64_
                         int ids_are_i64, const void* topk_w, int topk_w_dtype, int topk, int experts_per_rank,
                         int home_rank, const int32_t* order, void* packed, int64_t row_bytes, int32_t* inv,
                         void* stream) {
+    return fg_ep_pack_rows_fp8_peer(x, x_dtype, T, K, ld_x, topk_ids, ids_are_i64, topk_w, topk_w_dtype, topk,
+                                    experts_per_rank, home_rank, order, packed, row_bytes, inv, nullptr, nullptr, 0,
+                                    stream);
+}
+
+int fg_ep_pack_rows_fp8_peer(const void* x, int x_dtype, int64_t T, int64_t K, int64_t ld_x, const void* topk_ids,
+                             int ids_are_i64, const void* topk_w, int topk_w_dtype, int topk, int experts_per_rank,
+                             int home_rank, const int32_t* order, void* packed, int64_t row_bytes, int32_t* inv,
+                             const int32_t* plan, void* const* peer_rows, int world, void* stream) {
     FG_REQUIRE(T >= 0 && K > 0 && topk > 0 && experts_per_rank > 0, FG_ERR_INVALID_ARGUMENT, "bad sizes");
     FG_REQUIRE(K % 128 == 0, FG_ERR_UNSUPPORTED, "row length %lld must be a multiple of 128", (long long)K);
     FG_REQUIRE(row_bytes >= K + 4 * (K / 128) + 16 && row_bytes % 16 == 0, FG_ERR_INVALID_ARGUMENT,
                "row_bytes %lld too small or not a multiple of 16", (long long)row_bytes);
     FG_REQUIRE(T * topk < (1ll << 31), FG_ERR_UNSUPPORTED, "too many route slots");
     if (T == 0) return FG_OK;
-    FG_REQUIRE(x && topk_ids && topk_w && order && packed, FG_ERR_INVALID_ARGUMENT, "null pointer");
+    FG_REQUIRE(x && topk_ids && topk_w && order && (packed || plan), FG_ERR_INVALID_ARGUMENT, "null pointer");
+    FG_REQUIRE(plan == nullptr || (peer_rows && world >= 1 && world <= 8), FG_ERR_INVALID_ARGUMENT,
+               "direct dispatch needs 1..8 peer buffers");
     QuantArgs a{};
     a.x = x; a.q = (uint8_t*)packed; a.s = reinterpret_cast<float*>((uint8_t*)packed + K);
     a.rows = T * topk; a.K = K; a.group = 128;
@@ -420,6 +450,12 @@ int fg_ep_pack_rows_fp8(const void* x, int x_dtype, int64_t T, int64_t K, int64_
     a.row_index = order; a.index_div = topk; a.index_limit = (int32_t)(T * topk); a.n_rows_dev = nullptr;
     a.meta_ids = topk_ids; a.meta_ids_i64 = ids_are_i64; a.meta_w = topk_w; a.meta_w_dtype = topk_w_dtype;
     a.meta_mod = experts_per_rank; a.meta_rank = home_rank; a.meta_off = K + 4 * (K / 128); a.inv = inv;
+    a.plan = plan; a.world = world;
+    for (int i = 0; i < 8; ++i) a.peer_q[i] = (plan && i < world) ? (uint8_t*)peer_rows[i] : nullptr;
+    if (plan) {
+        a.q = (uint8_t*)peer_rows[home_rank];
+        a.s = reinterpret_cast<float*>(a.q + K);
+    }
     int rc = check_common(a, x_dtype);
     if (rc != FG_OK) return rc;
     return launch_quant<QM_GROUP>(x_dtype, a, (cudaStream_t)stream);

@@ -144,12 +144,51 @@ class CudaMoEOps:
         ids64 = 1 if topk_ids.dtype == torch.int64 else 0
         _cabi.check(L.fg_moe_align_block_size_ex(
             _cabi.ptr(topk_ids), ids64, numel, world, 1, None, 0, _cabi.ptr(order), numel, _cabi.ptr(blocks),
-            numel + 1, _cabi.ptr(meta), 1, self.num_local_experts, meta.data_ptr() + 4, st))
+            numel + 1, _cabi.ptr(meta), 1, self.num_local_experts, meta.data_ptr() + 4, None, st))
         _cabi.check(L.fg_ep_pack_rows_fp8(
             _cabi.ptr(hidden), _cabi.DTYPE_CODE[hidden.dtype], t, self.hidden, hidden.stride(0),
             _cabi.ptr(topk_ids), ids64, _cabi.ptr(topk_w), _cabi.DTYPE_CODE[topk_w.dtype], topk,
             self.num_local_experts, rank, _cabi.ptr(order), _cabi.ptr(packed), self.row_bytes, _cabi.ptr(inv), st))
         return packed, meta[1:], inv
+
+    def route(self, topk_ids, world):
+        """Route slots ordered by destination rank (stable) and rows per destination, on the device."""
+        numel = topk_ids.numel()
+        dev = topk_ids.device
+        order = torch.empty(numel, dtype=torch.int32, device=dev)
+        blocks = torch.empty(numel + 1, dtype=torch.int32, device=dev)
+        meta = torch.empty(world + 1, dtype=torch.int32, device=dev)
+        _cabi.check(_cabi.lib().fg_moe_align_block_size_ex(
+            _cabi.ptr(topk_ids), 1 if topk_ids.dtype == torch.int64 else 0, numel, world, 1, None, 0,
+            _cabi.ptr(order), numel, _cabi.ptr(blocks), numel + 1, _cabi.ptr(meta), 1, self.num_local_experts,
+            meta.data_ptr() + 4, None, _cabi.stream_ptr(dev)))
+        return order, meta[1:]
+
+    def pack_to_peers(self, hidden, topk_ids, topk_w, order, counts_matrix, world, rank, peer_rows):
+        """Quantises the local tokens and stores every packed row directly into its destination
+        rank's receive buffer.  Returns the plan tensor; plan[17] is the number of rows this rank
+        receives (device-side)."""
+        t, topk = topk_ids.shape
+        dev = hidden.device
+        plan = torch.empty(18, dtype=torch.int32, device=dev)
+        L, st = _cabi.lib(), _cabi.stream_ptr(dev)
+        _cabi.check(L.fg_ep_plan(_cabi.ptr(counts_matrix), world, rank, _cabi.ptr(plan), st))
+        _cabi.check(L.fg_ep_pack_rows_fp8_peer(
+            _cabi.ptr(hidden), _cabi.DTYPE_CODE[hidden.dtype], t, self.hidden, hidden.stride(0),
+            _cabi.ptr(topk_ids), 1 if topk_ids.dtype == torch.int64 else 0, _cabi.ptr(topk_w),
+            _cabi.DTYPE_CODE[topk_w.dtype], topk, self.num_local_experts, rank, _cabi.ptr(order), None,
+            self.row_bytes, None, _cabi.ptr(plan), peer_rows, world, st))
+        return plan
+
+    def experts_from_buffer(self, rows_ptr, capacity, n_rows_dev_ptr, out_dtype, device, peer_out):
+        """Routed-expert pipeline on the rows that peers stored into this rank's receive buffer;
+        the row count is read on the device, results go to the home ranks' buffers."""
+        ws = self._workspace(capacity, device)
+        _cabi.check(_cabi.lib().fg_moe_routed_block_fp8_packed(
+            None, rows_ptr, capacity, self.row_bytes, _cabi.ptr(self.w1), _cabi.ptr(self.w2),
+            _cabi.ptr(self.w1_scale), _cabi.ptr(self.w2_scale), self.num_local_experts, self.hidden, self.inter,
+            _cabi.ptr(ws), ws.numel(), _cabi.DTYPE_CODE[out_dtype], peer_out, len(peer_out), n_rows_dev_ptr,
+            _cabi.stream_ptr(device)))
 
     def experts_packed(self, packed, out_dtype, peer_out=None):
         """Routed-expert pipeline on R received packed rows.  Without ``peer_out`` the result is
@@ -166,7 +205,7 @@ class CudaMoEOps:
             _cabi.ptr(y), _cabi.ptr(packed), r, self.row_bytes, _cabi.ptr(self.w1), _cabi.ptr(self.w2),
             _cabi.ptr(self.w1_scale), _cabi.ptr(self.w2_scale), self.num_local_experts, self.hidden, self.inter,
             _cabi.ptr(ws), ws.numel(), _cabi.DTYPE_CODE[out_dtype], peer_out,
-            0 if peer_out is None else len(peer_out), _cabi.stream_ptr(packed.device)))
+            0 if peer_out is None else len(peer_out), None, _cabi.stream_ptr(packed.device)))
         return y
 
     def combine_slots(self, buf_ptr, tokens, topk, dtype, device, addend):
@@ -231,7 +270,7 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, w1, w2, w1_scale, w2_scale, num_experts: int, rank: int = 0, world: int = 1,
-                 group=None, shared=None, ops=None, p2p_combine_rows: int = 0):
+                 group=None, shared=None, ops=None, p2p_combine_rows: int = 0, p2p_dispatch_rows: int = 0):
         assert num_experts % world == 0, "experts must divide evenly over the ranks"
         assert w1.shape[0] == num_experts // world, "w1 must hold exactly this rank's experts"
         self.num_experts, self.rank, self.world, self.group = num_experts, rank, world, group
@@ -249,6 +288,15 @@ class ExpertParallelMoE:
             self._symm = SymmetricBuffers(p2p_combine_rows * hidden_size * 2, 2, rank, world, group)
             self._symm_rows = p2p_combine_rows
             self._flag = torch.zeros(1, dtype=torch.float32, device=w1.device)
+        # Fused dispatch: the quantisation kernel stores packed rows straight into the destination
+        # rank's receive buffer; counts travel by an all-gather that stays on the stream, so a step
+        # has no host round trip at all.  p2p_dispatch_rows = receive capacity in rows per rank
+        # (the safe value is world * tokens * topk: every route of every rank landing on one rank).
+        self._recv = None
+        if p2p_dispatch_rows > 0 and self._symm is not None:
+            self._recv = SymmetricBuffers(p2p_dispatch_rows * self.ops.row_bytes, 2, rank, world, group)
+            self._recv_rows = p2p_dispatch_rows
+            self._counts_matrix = torch.zeros(world * world, dtype=torch.int32, device=w1.device)
 
     def _mark(self, name, device):
         if self.trace is not None and device.type == "cuda":
@@ -299,6 +347,31 @@ class ExpertParallelMoE:
             inv = None
             self._mark("experts", dev)
         else:
+            use_p2p = (self._symm is not None and hidden.dtype in (torch.bfloat16, torch.float16)
+                       and tokens * topk <= self._symm_rows)
+            if use_p2p and self._recv is not None and self.world * tokens * topk <= self._recv_rows:
+                # Device-driven step: no host wait, no NCCL payload traffic.
+                buf = self._step & 1
+                self._step += 1
+                order, counts_dev = ops.route(topk_ids, self.world)
+                dist.all_gather_into_tensor(self._counts_matrix, counts_dev.contiguous(), group=self.group)
+                self._mark("route+counts", dev)
+                plan = ops.pack_to_peers(hidden, topk_ids, topk_weights, order, self._counts_matrix, self.world,
+                                         self.rank, self._recv.ptr_arrays[buf])
+                dist.all_reduce(self._flag, group=self.group)  # every rank's rows have landed
+                self._mark("pack+dispatch", dev)
+                ops.experts_from_buffer(self._recv.local[buf], self._recv_rows, plan.data_ptr() + 17 * 4,
+                                        hidden.dtype, dev, self._symm.ptr_arrays[buf])
+                self._mark("experts+combine", dev)
+                dist.all_reduce(self._flag, group=self.group)  # every rank's GEMM2 has finished
+                self._mark("barrier", dev)
+                if side is not None:
+                    main = torch.cuda.current_stream(dev)
+                    main.wait_stream(side)
+                    shared_out.record_stream(main)
+                out = ops.combine_slots(self._symm.local[buf], tokens, topk, hidden.dtype, dev, shared_out)
+                self._mark("sum", dev)
+                return out
             packed, counts_dev, inv = ops.plan_and_pack(hidden, topk_ids, topk_weights, self.world, self.rank)
             self._mark("route+pack", dev)
             send_counts, recv_counts = self._exchange_counts(counts_dev)
@@ -306,8 +379,6 @@ class ExpertParallelMoE:
             self._mark("counts", dev)
             packed_r = self._all_to_all(packed, send_counts, recv_counts)
             self._mark("dispatch", dev)
-            use_p2p = (self._symm is not None and hidden.dtype in (torch.bfloat16, torch.float16)
-                       and tokens * topk <= self._symm_rows)
             if use_p2p:
                 buf = self._step & 1
                 self._step += 1

@@ -102,12 +102,14 @@ int fg_moe_align_block_size(const void* topk_ids, int ids_are_i64, int64_t numel
 /* Same kernel with three extras used by the expert-parallel layer (no counterpart in the
  * reference, which has no dispatch step): ids are read with a stride of ids_stride elements,
  * the bucket of a slot is id / id_div (id_div = experts per rank turns expert ids into
- * destination ranks), and expert_counts (nullable) receives the unpadded rows per bucket. */
+ * destination ranks), expert_counts (nullable) receives the unpadded rows per bucket, and
+ * numel_dev (nullable) is a device-side slot count: numel is then only the capacity (and the
+ * padding value), so a step needs no host round trip to learn how many rows arrived. */
 int fg_moe_align_block_size_ex(const void* topk_ids, int ids_are_i64, int64_t numel, int num_experts,
                                int block_size, const int32_t* expert_map, int expert_map_len,
                                int32_t* sorted_ids, int64_t max_pad, int32_t* expert_ids,
                                int64_t n_blocks, int32_t* num_post_pad, int64_t ids_stride, int id_div,
-                               int32_t* expert_counts, void* stream);
+                               int32_t* expert_counts, const int32_t* numel_dev, void* stream);
 
 /* silu_and_mul_out / _silu_and_mul_kernel: src/flag_gems/fused/silu_and_mul.py:26-31,66-69,
  * src/flag_gems/fused/fused_moe.py:795-800.  out = dtype(x32/(1+exp(-x32)) * y32). */
@@ -152,6 +154,20 @@ int fg_ep_pack_rows_fp8(const void* x, int x_dtype, int64_t T, int64_t K, int64_
                         int topk, int experts_per_rank, int home_rank, const int32_t* order,
                         void* packed, int64_t row_bytes, int32_t* inv, void* stream);
 
+/* Same, writing each packed row straight into the receive buffer of its destination rank over
+ * NVLink peer memory (dispatch fused into the quantisation kernel): peer_rows[d] is rank d's
+ * receive buffer, plan the geometry computed by fg_ep_plan.  plan == NULL: as above. */
+int fg_ep_pack_rows_fp8_peer(const void* x, int x_dtype, int64_t T, int64_t K, int64_t ld_x,
+                             const void* topk_ids, int ids_are_i64, const void* topk_w,
+                             int topk_w_dtype, int topk, int experts_per_rank, int home_rank,
+                             const int32_t* order, void* packed, int64_t row_bytes, int32_t* inv,
+                             const int32_t* plan, void* const* peer_rows, int world, void* stream);
+
+/* From counts[src*world + dst] (rows rank src sends to rank dst, gathered from all ranks) writes
+ * this rank's plan (18 int32): [0..world] first send-order row per destination, [9+d] first row
+ * of this rank's block in d's receive buffer, [17] rows this rank receives. */
+int fg_ep_plan(const int32_t* counts, int world, int rank, int32_t* plan, void* stream);
+
 /* Bytes of workspace the two functions below need for n_rows_in routed rows. */
 int64_t fg_moe_routed_workspace_bytes(int64_t n_rows_in, int num_experts, int64_t H, int64_t I);
 
@@ -190,12 +206,13 @@ int fg_moe_routed_block_fp8_local_noalloc(void* y, const void* hidden, int hidde
  * (to be returned by an all-to-all).  n_peers > 0 (y may be NULL): the combine is fused into
  * GEMM2's epilogue, which stores each result row straight into the home rank's buffer
  * peer_out[home rank] at row (route slot), over NVLink peer memory; the home rank may read its
- * buffer once every rank's call has completed (a stream-ordered barrier or collective). */
+ * buffer once every rank's call has completed (a stream-ordered barrier or collective).
+ * n_rows_dev (nullable): device-side row count; R is then the capacity of `rows`. */
 int fg_moe_routed_block_fp8_packed(void* y, const void* rows, int64_t R, int64_t row_bytes,
                                    const void* w1, const void* w2, const float* s1, const float* s2,
                                    int num_experts, int64_t H, int64_t I, void* workspace,
                                    int64_t workspace_bytes, int out_dtype, void* const* peer_out,
-                                   int n_peers, void* stream);
+                                   int n_peers, const int32_t* n_rows_dev, void* stream);
 
 /* fg_moe_grouped_gemm_fp8 with the peer scatter described above: with scatter != 0 and
  * n_peers > 0, row r (arrival index sid = sorted_ids[r]) goes to peer_out[dest[sid*dest_stride+1]]

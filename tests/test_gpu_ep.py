@@ -52,11 +52,14 @@ def _worker(rank, world, port, q):
         sl = slice(rank * tl, (rank + 1) * tl)
         single = _layer_single(case, dev)[sl]
         equal, repeat, err = True, True, 0.0
-        # all-to-all combine, then the combine fused into GEMM2 over peer memory (3 steps: both buffers)
-        for p2p_rows in (0, tl * ti.shape[1]):
+        # all-to-all both ways; combine fused into GEMM2 over peer memory; dispatch fused as well
+        # (3 steps each, so both halves of the double buffers are used)
+        n_slots = tl * ti.shape[1]
+        for p2p_rows, recv_rows in ((0, 0), (n_slots, 0), (n_slots, world * n_slots)):
             layer = ExpertParallelMoE(w1[lo:lo + el].to(dev), w2[lo:lo + el].to(dev), s1[lo:lo + el].to(dev),
                                       s2[lo:lo + el].to(dev), e, rank, world,
-                                      shared=tuple(x.to(dev) for x in shared), p2p_combine_rows=p2p_rows)
+                                      shared=tuple(x.to(dev) for x in shared), p2p_combine_rows=p2p_rows,
+                                      p2p_dispatch_rows=recv_rows)
             outs = [layer(hidden[sl].to(dev), tw[sl].to(dev), ti[sl].to(dev)) for _ in range(3)]
             equal = equal and bool(torch.equal(outs[0], single))
             repeat = repeat and bool(torch.equal(outs[0], outs[1])) and bool(torch.equal(outs[0], outs[2]))
