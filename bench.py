@@ -108,7 +108,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -381,15 +381,22 @@ def run_ours(args):
             ms = float(t.item())
         return ms
 
-    for _ in range(max(args.warmup, 3)):
-        step_resident()
-    launches0 = _cabi.launch_count()
+    # Clocks are sampled from the first warm-up step to the last end-to-end step: the same
+    # workload throughout, and long enough for nvidia-smi to report even when the timed region
+    # itself lasts only tens of milliseconds.
     with ClockSampler(local_rank) as clocks:
+        for _ in range(max(args.warmup, 3)):
+            step_resident()
+        launches0 = _cabi.launch_count()
         ms = timed(step_resident, args.steps)
-    launches = _cabi.launch_count() - launches0
-    for _ in range(2):
-        step_e2e()
-    ms_e2e = timed(step_e2e, args.steps)
+        launches = _cabi.launch_count() - launches0
+        for _ in range(2):
+            step_e2e()
+        ms_e2e = timed(step_e2e, args.steps)
+        t_end = time.time() + 0.3
+        while clocks.rows.__len__() < 3 and time.time() < t_end:  # let a few samples land under load
+            step_resident()
+        torch.cuda.synchronize()
     status = _cabi.device_status()
 
     # dominant kernel: the grouped GEMM1 (block-scaled, fused SiLU) on this rank's routed rows,

@@ -67,7 +67,7 @@ _SIGS = {
                 c_int, c_int, c_int, c_int, _P]),
     "fg_block_scaled_mm_fp8": (
         c_int, [_P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
-                c_int64, c_int64, c_int, _P]),
+                c_int64, c_int64, c_int64, c_int, _P]),
     "fg_moe_grouped_gemm_fp8": (
         c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int64, _P, _P, _P, c_int64, c_int64, c_int, c_int64, c_int64,
                 c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P]),

@@ -48,7 +48,7 @@ struct GemmParams {
     const void* bias;
     int sa_mode, sb_mode;  // FG_SCALE_SCALAR / FG_SCALE_VECTOR (ignored in block mode)
     int bias_after_round;
-    int64_t ld_as;                                  // block mode: row stride of As
+    int64_t ld_as, as_stride_k;                     // block mode: row / K-block strides of As
     int64_t bs_stride_n, bs_stride_k, bs_stride_e;  // block mode: strides of Bs
     int64_t sb_stride_e;                            // vector mode: per-expert stride of sb
     int grouped;
@@ -503,7 +503,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     const float sc0f = as_next * b0_next;
                     const float sc1f = FUSE_SILU ? as_next * b1_next : sc0f;
                     if (kb + 1 < num_k_blocks) {  // next block's scales travel while this block is folded in
-                        as_next = as_row[kb + 1];
+                        as_next = as_row[(int64_t)(kb + 1) * p.as_stride_k];
                         b0_next = __ldg(bs0 + (int64_t)(kb + 1) * p.bs_stride_k);
                         if constexpr (FUSE_SILU) b1_next = __ldg(bs1 + (int64_t)(kb + 1) * p.bs_stride_k);
                     }
@@ -729,7 +729,8 @@ int fg_scaled_mm_fp8(void* c, const void* a, const void* b, const float* sa, con
 
 int fg_block_scaled_mm_fp8(void* c, const void* a, const void* b, const float* a_s, const float* b_s, int64_t M,
                            int64_t N, int64_t K, int64_t ld_a, int64_t ld_b, int64_t ld_c, int64_t ld_as,
-                           int64_t bs_stride_n, int64_t bs_stride_k, int out_dtype, void* stream) {
+                           int64_t as_stride_k, int64_t bs_stride_n, int64_t bs_stride_k, int out_dtype,
+                           void* stream) {
     FG_REQUIRE(M >= 0 && N >= 0 && K >= 0, FG_ERR_INVALID_ARGUMENT, "negative size");
     if (M == 0 || N == 0) return FG_OK;
     FG_REQUIRE(c && a && b && a_s && b_s, FG_ERR_INVALID_ARGUMENT, "null pointer");
@@ -738,7 +739,8 @@ int fg_block_scaled_mm_fp8(void* c, const void* a, const void* b, const float* a
     GemmParams p{};
     p.M = M; p.N = (int)N; p.K = (int)K; p.n_out = (int)N;
     p.c = c; p.ld_c = ld_c; p.out_dtype = out_dtype;
-    p.sa = a_s; p.sb = b_s; p.ld_as = ld_as; p.bs_stride_n = bs_stride_n; p.bs_stride_k = bs_stride_k;
+    p.sa = a_s; p.sb = b_s; p.ld_as = ld_as; p.as_stride_k = as_stride_k;
+    p.bs_stride_n = bs_stride_n; p.bs_stride_k = bs_stride_k;
     p.block_rows = BLOCK_M;
     return launch_gemm(p, a, M, ld_a, b, 1, ld_b, true, false, (cudaStream_t)stream);
 }
@@ -786,7 +788,7 @@ int fg_moe_grouped_gemm_fp8_peer(void* c, const void* a, const void* w, const fl
     p.sa = a_scale; p.sb = w_scale;
     if (block) {
         const int64_t kb = fg_cdiv(K, 128), nb = fg_cdiv(N, 128);
-        p.ld_as = kb; p.bs_stride_k = 1; p.bs_stride_n = kb; p.bs_stride_e = kb * nb;
+        p.ld_as = kb; p.as_stride_k = 1; p.bs_stride_k = 1; p.bs_stride_n = kb; p.bs_stride_e = kb * nb;
     } else {
         p.sa_mode = (scale_mode == FG_SCALE_VECTOR || a_scale_per_row) ? FG_SCALE_VECTOR : FG_SCALE_SCALAR;
         p.sb_mode = scale_mode == FG_SCALE_VECTOR ? FG_SCALE_VECTOR : FG_SCALE_SCALAR;

@@ -90,12 +90,11 @@ def cutlass_scaled_mm(
                 f"b_scale.shape[1]={b_scale.size(1)}"
             )
             assert bias is None, "Bias not yet supported for blockwise scaled_mm"
-            assert a_scale.stride(1) == 1, "a_scale rows must be contiguous"
             # b_scale is [K/128, N/128] here: block (n, k) sits at k*stride(0) + n*stride(1)
             _cabi.check(
                 L.fg_block_scaled_mm_fp8(
                     _cabi.ptr(c), _cabi.ptr(a), _cabi.ptr(b), _cabi.ptr(a_scale), _cabi.ptr(b_scale),
-                    m, n, k, a.stride(0), b.stride(1), c.stride(0), a_scale.stride(0),
+                    m, n, k, a.stride(0), b.stride(1), c.stride(0), a_scale.stride(0), a_scale.stride(1),
                     b_scale.stride(1), b_scale.stride(0), _cabi.DTYPE_CODE[c.dtype], stream,
                 )
             )

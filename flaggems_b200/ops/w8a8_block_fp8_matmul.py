@@ -48,16 +48,16 @@ def w8a8_block_fp8_matmul(
         return c
     if B.stride(1) != 1 or B.stride(0) % 16 != 0:
         B = B.contiguous()
-    As2 = As.reshape(m, As.shape[-1])
-    if As2.dtype != torch.float32 or As2.stride(1) != 1:
-        As2 = As2.float().contiguous()
+    As2 = As.reshape(m, As.shape[-1])  # any strides: row-major or the column-major scale layout
+    if As2.dtype != torch.float32:
+        As2 = As2.float()
     if Bs.dtype != torch.float32:
         Bs = Bs.float()
     with _cabi.device_guard(A):
         _cabi.check(
             _cabi.lib().fg_block_scaled_mm_fp8(
                 _cabi.ptr(c), _cabi.ptr(A), _cabi.ptr(B), _cabi.ptr(As2), _cabi.ptr(Bs),
-                m, n, k, k, B.stride(0), n, As2.stride(0), Bs.stride(0), Bs.stride(1),
+                m, n, k, k, B.stride(0), n, As2.stride(0), As2.stride(1), Bs.stride(0), Bs.stride(1),
                 _cabi.DTYPE_CODE[output_dtype], _cabi.stream_ptr(A.device),
             )
         )

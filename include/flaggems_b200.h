@@ -256,13 +256,14 @@ int fg_scaled_mm_fp8(void* c, const void* a, const void* b, const float* sa, con
  * src/flag_gems/ops/w8a8_block_fp8_matmul.py:173-232 (kernel :51-122),
  * src/flag_gems/ops/fp8_matmul.py:137-205,
  * src/flag_gems/fused/cutlass_scaled_mm.py:153-194.
- * a e4m3 [M,K], b e4m3 [N,K]; a_s fp32 [M, ceil(K/128)] (row stride ld_as);
+ * a e4m3 [M,K], b e4m3 [N,K]; a_s[m*ld_as + kb*as_stride_k] fp32 (row-major [M, K/128] or the
+ * column-major layout of column_major_scales, which the kernel reads coalesced);
  * b_s[nb*bs_stride_n + kb*bs_stride_k] fp32; block sizes fixed at 128x128.
  * C[m,n] = out(sum_kb (A_kb . B_kb) * a_s[m,kb] * b_s[n/128,kb]). */
 int fg_block_scaled_mm_fp8(void* c, const void* a, const void* b, const float* a_s,
                            const float* b_s, int64_t M, int64_t N, int64_t K, int64_t ld_a,
-                           int64_t ld_b, int64_t ld_c, int64_t ld_as, int64_t bs_stride_n,
-                           int64_t bs_stride_k, int out_dtype, void* stream);
+                           int64_t ld_b, int64_t ld_c, int64_t ld_as, int64_t as_stride_k,
+                           int64_t bs_stride_n, int64_t bs_stride_k, int out_dtype, void* stream);
 
 /* Grouped expert GEMM of the fused MoE layer: fused_moe_kernel /
  * invoke_fused_moe_triton_kernel / dispatch_fused_moe_kernel,

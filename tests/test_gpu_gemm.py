@@ -150,7 +150,9 @@ def _block_case(m, n, k, seed=0):
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 512), (64, 128, 128), (256, 256, 256), (83, 7752, 3840),
                                    (1, 2112, 7168), (64, 4096, 7168), (512, 2112, 7168), (300, 1536, 1024),
-                                   (16, 4096, 7168), (128, 2112, 7168), (1, 24576, 7168), (40, 18432, 7168)])
+                                   (16, 4096, 7168), (128, 2112, 7168), (1, 24576, 7168), (40, 18432, 7168),
+                                   # wide enough for the 192-column tile (scale blocks straddle its halves)
+                                   (2048, 2112, 1024), (1100, 4096, 512), (1536, 1408, 384)])
 def test_w8a8_block_fp8_matmul(m, n, k):
     aq, a_s, wq, w_s = _block_case(m, n, k)
     out = flag_gems.w8a8_block_fp8_matmul(aq.cuda(), wq.cuda(), a_s.cuda(), w_s.cuda(), [128, 128])
