@@ -27,6 +27,9 @@ _SIGS = {
         c_int, [_P, c_int, _P, _P, c_int64, c_int64, c_int, c_int64, c_int64, c_int64, c_int64, c_float, c_int, _P]),
     "fg_per_token_quant_fp8": (
         c_int, [_P, c_int, _P, _P, c_int64, c_int64, c_int64, c_int64, _P, c_int32, c_int32, _P, _P]),
+    "fg_per_tensor_quant_fp8": (
+        c_int, [_P, c_int, _P, _P, c_int, _P, c_int64, c_int64, c_int64, c_int64, _P, c_int32, c_int32, _P, _P]),
+    "fg_abs_max": (c_int, [_P, c_int, c_int64, c_int64, c_int64, _P, _P, _P]),
     "fg_per_token_group_quant_fp8_gather": (
         c_int, [_P, c_int, _P, _P, c_int64, c_int64, c_int, c_int64, c_int64, _P, c_int32, c_int32, _P, _P]),
     "fg_moe_align_block_size": (

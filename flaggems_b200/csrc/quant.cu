@@ -4,6 +4,8 @@
 //   QM_ACT    act_quant          s = max(amax,1e-4) * fp32(1/448), y = x * (1/s)
 //   QM_GROUP  per-token-group    s = max(amax,eps) / 448,          q = x / s
 //   QM_TOKEN  per-token (MoE)    s = max(max(amax,1e-10)/448, 1/(448*512)), q = x / s
+//   QM_TENSOR_STATIC / _DYNAMIC  one scale for the whole tensor: given (q = x / s) or derived from a
+//             precomputed global amax (s = max(amax,1e-10)/448, q = x * (1/s))
 // The results are bit-exact with IEEE fp32 evaluation of those formulas: products use
 // __fmul_rn, the quotient x / s is a correctly rounded division built from one correctly
 // rounded reciprocal per group and two FMAs per element (Markstein's correction), with a
@@ -13,7 +15,7 @@
 
 namespace {
 
-enum { QM_ACT = 0, QM_GROUP = 1, QM_TOKEN = 2 };
+enum { QM_ACT = 0, QM_GROUP = 1, QM_TOKEN = 2, QM_TENSOR_STATIC = 3, QM_TENSOR_DYNAMIC = 4 };
 
 struct QuantArgs {
     const void* x;
@@ -40,6 +42,8 @@ struct QuantArgs {
     int32_t meta_rank;  // this rank (home of the rows)
     int64_t meta_off;
     int32_t* inv;  // nullable: inv[route slot] = output row
+    const float* tensor_scale;  // per-tensor modes: the given scale, or the global amax
+    float* tensor_scale_out;    // dynamic per-tensor mode: where the derived scale is written
     // Direct dispatch: output row p (send order) is written into the receive buffer of its
     // destination rank d (plan[d] <= p < plan[d+1]) at row plan[9+d] + (p - plan[d]).
     const int32_t* plan;  // nullable
@@ -292,9 +296,19 @@ __global__ void __launch_bounds__(256) row_quant_kernel(QuantArgs a) {
 #pragma unroll
     for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
 
-    const float s = make_scale<MODE>(amax, a.eps, a.pow2);
-    const Divider d = make_divider<MODE>(s);
-    if (threadIdx.x == 0) a.s[row * a.s_row_stride + cg * a.s_col_stride] = s;
+    float s;
+    if constexpr (MODE == QM_TENSOR_STATIC) {
+        s = a.tensor_scale[0];
+    } else if constexpr (MODE == QM_TENSOR_DYNAMIC) {
+        s = __fdiv_rn(fmaxf(a.tensor_scale[0], __uint_as_float(0x2edbe6ffu)), 448.0f);
+        if (threadIdx.x == 0 && g == 0) a.tensor_scale_out[0] = s;
+    } else {
+        s = make_scale<MODE>(amax, a.eps, a.pow2);
+        if (threadIdx.x == 0) a.s[row * a.s_row_stride + cg * a.s_col_stride] = s;
+    }
+    // dynamic per-tensor quantisation multiplies by the reciprocal, like act_quant
+    constexpr int DMODE = MODE == QM_TENSOR_DYNAMIC ? QM_ACT : (MODE == QM_TENSOR_STATIC ? QM_GROUP : MODE);
+    const Divider d = make_divider<DMODE>(s);
 
     if (src < 0) {
         for (int iv = threadIdx.x; iv < nvec; iv += 256) *reinterpret_cast<uint2*>(q + (int64_t)iv * 8) = make_uint2(0u, 0u);
@@ -307,7 +321,7 @@ __global__ void __launch_bounds__(256) row_quant_kernel(QuantArgs a) {
             if (iv < nvec) {
                 float o[8];
 #pragma unroll
-                for (int i = 0; i < 8; i += 2) apply_divider2<MODE>(v[j][i], v[j][i + 1], d, o[i], o[i + 1]);
+                for (int i = 0; i < 8; i += 2) apply_divider2<DMODE>(v[j][i], v[j][i + 1], d, o[i], o[i + 1]);
                 *reinterpret_cast<uint2*>(q + (int64_t)iv * 8) = fg_pack_e4m3x8(o);
             }
         }
@@ -316,9 +330,39 @@ __global__ void __launch_bounds__(256) row_quant_kernel(QuantArgs a) {
             float t[8], o[8];
             fg_load8(x + (int64_t)iv * 8, t);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) o[i] = apply_divider<MODE>(t[i], d);
+            for (int i = 0; i < 8; ++i) o[i] = apply_divider<DMODE>(t[i], d);
             *reinterpret_cast<uint2*>(q + (int64_t)iv * 8) = fg_pack_e4m3x8(o);
         }
+    }
+}
+
+// Global max|x| over rows [0, rows) into amax[0] (which must start at zero): block reduction, then
+// one atomicMax per block on the bit pattern (non-negative floats order like unsigned integers).
+template <typename T>
+__global__ void __launch_bounds__(256) abs_max_kernel(const T* __restrict__ x, int64_t rows, int64_t K, int64_t ld_x,
+                                                      const int32_t* __restrict__ n_rows_dev,
+                                                      unsigned int* __restrict__ amax) {
+    if (n_rows_dev) {
+        const int64_t v = *n_rows_dev;
+        rows = v < rows ? v : rows;
+    }
+    const int64_t vec_per_row = K / 8, total = rows * vec_per_row;
+    float m = 0.0f;
+    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += (int64_t)gridDim.x * blockDim.x) {
+        float f[8];
+        fg_load8(x + (v / vec_per_row) * ld_x + (v % vec_per_row) * 8, f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(f[i]));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    __shared__ float red[8];
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int w = 1; w < 8; ++w) m = fmaxf(m, red[w]);
+        atomicMax(amax, __float_as_uint(m));
     }
 }
 
@@ -459,6 +503,60 @@ int fg_ep_pack_rows_fp8_peer(const void* x, int x_dtype, int64_t T, int64_t K, i
     int rc = check_common(a, x_dtype);
     if (rc != FG_OK) return rc;
     return launch_quant<QM_GROUP>(x_dtype, a, (cudaStream_t)stream);
+}
+
+int fg_abs_max(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ld_x, const int32_t* n_rows_dev,
+               float* amax, void* stream) {
+    FG_REQUIRE(M >= 0 && K >= 0 && amax, FG_ERR_INVALID_ARGUMENT, "bad arguments");
+    if (M == 0 || K == 0) return FG_OK;
+    const int esz = x_dtype == FG_DTYPE_F32 ? 4 : 2;
+    FG_REQUIRE(K % 8 == 0 && (uintptr_t)x % 16 == 0 && (ld_x * esz) % 16 == 0, FG_ERR_UNSUPPORTED,
+               "abs_max needs K %% 8 == 0 and 16-byte aligned rows");
+    int64_t blocks = fg_cdiv(M * (K / 8), 256 * 4);
+    const int64_t cap = (int64_t)fg_num_sms() * 8;
+    if (blocks > cap) blocks = cap;
+    cudaStream_t st = (cudaStream_t)stream;
+    unsigned int* out = reinterpret_cast<unsigned int*>(amax);
+    switch (x_dtype) {
+        case FG_DTYPE_BF16: abs_max_kernel<<<(unsigned)blocks, 256, 0, st>>>((const __nv_bfloat16*)x, M, K, ld_x, n_rows_dev, out); break;
+        case FG_DTYPE_F16: abs_max_kernel<<<(unsigned)blocks, 256, 0, st>>>((const __half*)x, M, K, ld_x, n_rows_dev, out); break;
+        case FG_DTYPE_F32: abs_max_kernel<<<(unsigned)blocks, 256, 0, st>>>((const float*)x, M, K, ld_x, n_rows_dev, out); break;
+        default: fg_set_error("unsupported input dtype code %d", x_dtype); return FG_ERR_INVALID_ARGUMENT;
+    }
+    fg_count_launch(1);
+    FG_LAUNCH_CHECK();
+    return FG_OK;
+}
+
+int fg_per_tensor_quant_fp8(const void* x, int x_dtype, void* q, const float* scale_or_amax, int dynamic,
+                            float* scale_out, int64_t M, int64_t K, int64_t ld_x, int64_t ld_q,
+                            const int32_t* row_index, int32_t index_div, int32_t index_limit,
+                            const int32_t* n_rows_dev, void* stream) {
+    QuantArgs a{};
+    a.x = x; a.q = (uint8_t*)q; a.s = const_cast<float*>(scale_or_amax); a.rows = M; a.K = K; a.group = (int)K;
+    a.ld_x = ld_x; a.ld_q = ld_q; a.s_row_stride = 0; a.s_col_stride = 0;
+    a.row_index = row_index; a.index_div = index_div; a.index_limit = index_limit; a.n_rows_dev = n_rows_dev;
+    a.tensor_scale = scale_or_amax; a.tensor_scale_out = scale_out;
+    FG_REQUIRE(scale_or_amax && (!dynamic || scale_out), FG_ERR_INVALID_ARGUMENT, "scale pointers missing");
+    FG_REQUIRE(K < (1ll << 31) && M < (1ll << 31), FG_ERR_UNSUPPORTED, "size too large");
+    FG_REQUIRE(row_index == nullptr || index_div > 0, FG_ERR_INVALID_ARGUMENT, "index_div must be positive");
+    if (K == 0 || M == 0) return FG_OK;
+    int rc = check_common(a, x_dtype);
+    if (rc != FG_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+#define FG_ROW_LAUNCH(T_)                                                                       \
+    if (dynamic) row_quant_kernel<T_, QM_TENSOR_DYNAMIC><<<(unsigned)M, 256, 0, st>>>(a);        \
+    else row_quant_kernel<T_, QM_TENSOR_STATIC><<<(unsigned)M, 256, 0, st>>>(a);
+    switch (x_dtype) {
+        case FG_DTYPE_BF16: FG_ROW_LAUNCH(__nv_bfloat16) break;
+        case FG_DTYPE_F16: FG_ROW_LAUNCH(__half) break;
+        case FG_DTYPE_F32: FG_ROW_LAUNCH(float) break;
+        default: fg_set_error("unsupported input dtype code %d", x_dtype); return FG_ERR_INVALID_ARGUMENT;
+    }
+#undef FG_ROW_LAUNCH
+    fg_count_launch(1);
+    FG_LAUNCH_CHECK();
+    return FG_OK;
 }
 
 int fg_per_token_quant_fp8(const void* x, int x_dtype, void* q, float* s, int64_t M, int64_t K, int64_t ld_x,

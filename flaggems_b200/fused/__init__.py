@@ -2,6 +2,8 @@ from .act_quant import act_quant_triton  # noqa: F401
 from .cutlass_scaled_mm import cutlass_scaled_mm  # noqa: F401
 from .fused_moe import (  # noqa: F401
     MoEActivation,
+    dispatch_fused_moe_kernel,
+    invoke_fused_moe_triton_kernel,
     fused_experts_impl,
     inplace_fused_experts,
     moe_kernel_quantize_input,

@@ -19,7 +19,7 @@ from typing import Optional
 import torch
 
 from .. import _cabi
-from .moe_align_block_size import moe_align_block_size
+from .moe_align_block_size import ceil_div, moe_align_block_size
 from .moe_sum import moe_sum
 from .silu_and_mul import silu_and_mul_out
 
@@ -96,9 +96,35 @@ def _group_quant(x, group, row_index=None, index_div=1, index_limit=0, n_rows_de
     return q, s
 
 
+def _per_tensor_quant(x, scale=None, row_index=None, index_div=1, index_limit=0, n_rows_dev=None, out_rows=None,
+                      amax_rows_dev=None):
+    """Per-tensor FP8 quantisation (reference: fused_moe.py:686-698): with a given ``scale``
+    q = x / scale; without, scale = max(max|x|, 1e-10) / 448 over the whole tensor and
+    q = x * (1 / scale).  Returns (q, scale[1])."""
+    k = x.shape[-1]
+    x2 = x.reshape(-1, k)
+    rows = x2.shape[0] if out_rows is None else out_rows
+    q = torch.empty((rows, k), dtype=torch.float8_e4m3fn, device=x.device)
+    L, st = _cabi.lib(), _cabi.stream_ptr(x.device)
+    if scale is not None:
+        s_in = scale.float().reshape(-1)[:1].contiguous()
+        s_out, dynamic = s_in, 0
+    else:
+        s_in = torch.zeros(1, dtype=torch.float32, device=x.device)
+        s_out, dynamic = torch.empty(1, dtype=torch.float32, device=x.device), 1
+        if x2.shape[0] and k:
+            _cabi.check(L.fg_abs_max(_cabi.ptr(x2), _cabi.DTYPE_CODE[x.dtype], x2.shape[0], k, x2.stride(0),
+                                     _cabi.ptr(amax_rows_dev), _cabi.ptr(s_in), st))
+    if rows and k:
+        _cabi.check(L.fg_per_tensor_quant_fp8(
+            _cabi.ptr(x2), _cabi.DTYPE_CODE[x.dtype], _cabi.ptr(q), _cabi.ptr(s_in), dynamic, _cabi.ptr(s_out),
+            rows, k, x2.stride(0), k, _cabi.ptr(row_index), index_div, index_limit, _cabi.ptr(n_rows_dev), st))
+    return q, s_out
+
+
 def _fp8_quantize(A, A_scale, per_act_token, block_shape=None):
-    """FP8 e4m3 quantisation of MoE activations: block-wise or per-token
-    (reference: fused_moe.py:629-698).  The per-tensor branches are not implemented."""
+    """FP8 e4m3 quantisation of MoE activations: block-wise, per-token, or per-tensor with a
+    given or a dynamic scale (reference: fused_moe.py:629-698)."""
     _cabi.require_cuda(A)
     with _cabi.device_guard(A):
         if block_shape is not None:
@@ -111,7 +137,8 @@ def _fp8_quantize(A, A_scale, per_act_token, block_shape=None):
         if per_act_token:
             q, s = _per_token_quant(A)
             return q.reshape(A.shape), s.reshape(A.shape[:-1] + (1,))
-    raise NotImplementedError("per-tensor FP8 activation quantisation is not implemented")
+        q, s = _per_tensor_quant(A, A_scale)
+        return q.reshape(A.shape), (A_scale if A_scale is not None else s)
 
 
 def moe_kernel_quantize_input(A, A_scale, quant_dtype, per_act_token_quant, block_shape=None, ocp_mx_scheme=None):
@@ -126,7 +153,7 @@ def moe_kernel_quantize_input(A, A_scale, quant_dtype, per_act_token_quant, bloc
 
 
 def _grouped_gemm(c, a, w, a_scale, w_scale, topk_weights, sorted_ids, expert_ids, num_post_pad, numel,
-                  scale_mode, fuse_silu, scatter, mul_weight):
+                  scale_mode, fuse_silu, scatter, mul_weight, block_rows=_TILE_ROWS, a_scale_per_row=None):
     e, n, k = w.shape
     c = c.view(-1, c.shape[-1])
     _cabi.check(
@@ -135,7 +162,8 @@ def _grouped_gemm(c, a, w, a_scale, w_scale, topk_weights, sorted_ids, expert_id
             _cabi.ptr(topk_weights), _cabi.DTYPE_CODE.get(topk_weights.dtype, -1) if topk_weights is not None else 0,
             1,
             _cabi.ptr(sorted_ids), _cabi.ptr(expert_ids), _cabi.ptr(num_post_pad),
-            a.shape[0], numel, e, n, k, a.stride(0), c.stride(0), _TILE_ROWS, scale_mode, 1,
+            a.shape[0], numel, e, n, k, a.stride(0), c.stride(0), block_rows, scale_mode,
+            (0 if scale_mode == _cabi.SCALE_SCALAR else 1) if a_scale_per_row is None else int(a_scale_per_row),
             1 if fuse_silu else 0, 1 if scatter else 0, 1 if mul_weight else 0,
             _cabi.DTYPE_CODE[c.dtype], _cabi.stream_ptr(a.device),
         )
@@ -180,10 +208,8 @@ def fused_experts_impl(
         raise NotImplementedError("zero points and expert biases are not implemented")
     if apply_router_weight_on_input:
         raise NotImplementedError("apply_router_weight_on_input is not implemented")
-    if block_shape is None and not per_channel_quant:
-        raise NotImplementedError("per-tensor FP8 scales are not implemented; use per_channel_quant or block_shape")
-    if a1_scale is not None or a2_scale is not None:
-        raise NotImplementedError("static activation scales are not implemented (dynamic quantisation only)")
+    if (a1_scale is not None or a2_scale is not None) and (block_shape is not None or per_channel_quant):
+        raise NotImplementedError("static activation scales are implemented for the per-tensor mode only")
 
     assert hidden_states.size(1) == w1.size(2), f"Hidden size mismatch {hidden_states.size(1)} != {w1.size(2)}"
     assert topk_weights.size() == topk_ids.size(), "topk shape mismatch"
@@ -218,11 +244,16 @@ def fused_experts_impl(
         w2s = w2_scale.float().contiguous()
         assert w1s.shape == (e, (n + 127) // 128, hidden // 128), f"w1_scale shape {tuple(w1s.shape)}"
         assert w2s.shape == (e, (k_out + 127) // 128, inter // 128), f"w2_scale shape {tuple(w2s.shape)}"
-    else:
+    elif per_channel_quant:
         scale_mode = _cabi.SCALE_VECTOR
         w1s = w1_scale.float().reshape(e, -1).contiguous()
         w2s = w2_scale.float().reshape(e, -1).contiguous()
         assert w1s.shape == (e, n) and w2s.shape == (e, k_out), "per-channel scales must be [E, N]"
+    else:
+        scale_mode = _cabi.SCALE_SCALAR  # one scale per expert, one per activation tensor
+        w1s = w1_scale.float().reshape(-1).contiguous()
+        w2s = w2_scale.float().reshape(-1).contiguous()
+        assert w1s.numel() == e and w2s.numel() == e, "per-tensor weight scales must hold one value per expert"
 
     out = hidden_states if inplace else torch.empty_like(hidden_states)
     if num_tokens == 0:
@@ -244,20 +275,110 @@ def fused_experts_impl(
 
             if scale_mode == _cabi.SCALE_BLOCK:
                 a1, a1s = _group_quant(h, 128, sorted_ids, top_k, numel, post_pad, rows)
-            else:
+            elif scale_mode == _cabi.SCALE_VECTOR:
                 a1, a1s = _per_token_quant(h, sorted_ids, top_k, numel, post_pad, rows)
+            else:
+                a1, a1s = _per_tensor_quant(h, a1_scale, sorted_ids, top_k, numel, post_pad, rows)
             act = torch.empty((rows, inter), dtype=dtype, device=h.device)
             _grouped_gemm(act, a1, w1, a1s, w1s, None, sorted_ids, expert_ids, post_pad, numel,
                           scale_mode, fuse_silu=True, scatter=False, mul_weight=False)
             if scale_mode == _cabi.SCALE_BLOCK:
                 a2, a2s = _group_quant(act, 128, None, 1, 0, post_pad, rows)
-            else:
+            elif scale_mode == _cabi.SCALE_VECTOR:
                 a2, a2s = _per_token_quant(act, None, 1, 0, post_pad, rows)
+            else:
+                a2, a2s = _per_tensor_quant(act, a2_scale, None, 1, 0, post_pad, rows, amax_rows_dev=post_pad)
             routed = torch.empty((t, top_k, k_out), dtype=dtype, device=h.device)
             _grouped_gemm(routed, a2, w2, a2s, w2s, w, sorted_ids, expert_ids, post_pad, numel,
                           scale_mode, fuse_silu=False, scatter=True, mul_weight=True)
             moe_sum(routed, out[begin:end])
     return out
+
+
+def _dtype_of(compute_type):
+    if isinstance(compute_type, torch.dtype):
+        return compute_type
+    name = str(compute_type)
+    for key, dt in (("bfloat16", torch.bfloat16), ("bf16", torch.bfloat16), ("float16", torch.float16),
+                    ("fp16", torch.float16), ("float32", torch.float32), ("fp32", torch.float32)):
+        if name.endswith(key):
+            return dt
+    raise ValueError(f"unsupported compute_type {compute_type!r}")
+
+
+def invoke_fused_moe_triton_kernel(A, B, C, A_scale, B_scale, topk_weights, sorted_token_ids, expert_ids,
+                                   num_tokens_post_padded, mul_routed_weight, top_k, config, compute_type,
+                                   use_fp8_w8a8=False, use_int8_w8a8=False, use_int8_w8a16=False, use_int4_w4a16=False,
+                                   per_channel_quant=False, block_shape=None, B_bias=None, FUSE_SILU=False,
+                                   direct_sum=False, out_top_k=1) -> None:
+    """One grouped expert GEMM over rows already sorted by ``moe_align_block_size``
+    (reference: fused_moe.py:1602-1727; the name is kept, the kernel is the tcgen05 grouped GEMM).
+
+    A [M, K] FP8 with A_scale (block [M, K/128], per-token [M, 1] or per-tensor [1]); B [E, N, K];
+    row ``s`` of ``sorted_token_ids`` reads A[s // top_k] and writes C.view(-1, N_out)[s];
+    ``config["BLOCK_SIZE_M"]`` is the block size the ids were aligned with.
+    """
+    assert topk_weights is not None or not mul_routed_weight
+    assert topk_weights is None or topk_weights.stride(1) == 1
+    assert sorted_token_ids is None or sorted_token_ids.stride(0) == 1
+    if not use_fp8_w8a8 or use_int8_w8a8 or use_int8_w8a16 or use_int4_w4a16:
+        raise NotImplementedError("only use_fp8_w8a8 is implemented")
+    if B_bias is not None or direct_sum:
+        raise NotImplementedError("expert bias and direct_sum are not implemented")
+    assert B_scale is not None and A_scale is not None
+    _cabi.require_cuda(A, B, C, A_scale, B_scale, sorted_token_ids, expert_ids, num_tokens_post_padded)
+    block_rows = int(config["BLOCK_SIZE_M"])
+    e, n, k = B.shape
+    m = A.shape[0]
+    numel = m * top_k
+    out_dtype = _dtype_of(compute_type)
+    assert C.dtype == out_dtype, "C must have the compute dtype"
+    n_out = n // 2 if FUSE_SILU else n
+    c2 = C.view(-1, n_out)
+    rows = sorted_token_ids.numel() // block_rows * block_rows
+    if block_shape is not None:
+        assert list(block_shape) == [128, 128], "only 128x128 blocks are implemented"
+        assert ceil_div(n, 128) == B_scale.size(-2) and ceil_div(k, 128) == B_scale.size(-1)
+        scale_mode, per_row, s_cols = _cabi.SCALE_BLOCK, 1, k // 128
+        w_s = B_scale.float().contiguous()
+    elif per_channel_quant:
+        scale_mode, per_row, s_cols = _cabi.SCALE_VECTOR, 1, 1
+        w_s = B_scale.float().reshape(e, -1).contiguous()
+    else:
+        per_row = 1 if A_scale.numel() == m and m > 1 else 0
+        scale_mode, s_cols = _cabi.SCALE_SCALAR, (1 if per_row else 0)
+        w_s = B_scale.float().reshape(-1).contiguous()
+    with _cabi.device_guard(A):
+        a_sorted = torch.empty((rows, k), dtype=torch.float8_e4m3fn, device=A.device)
+        if s_cols:
+            a_s = A_scale.float().reshape(m, s_cols).contiguous()
+            a_s_sorted = torch.empty((rows, s_cols), dtype=torch.float32, device=A.device)
+        else:
+            a_s, a_s_sorted = None, A_scale.float().reshape(-1)[:1].contiguous()
+        _cabi.check(_cabi.lib().fg_gather_rows_fp8(
+            _cabi.ptr(A), _cabi.ptr(a_s), _cabi.ptr(a_sorted), _cabi.ptr(a_s_sorted if s_cols else None), rows, k,
+            s_cols, A.stride(0), max(s_cols, 1), _cabi.ptr(sorted_token_ids), top_k, numel,
+            _cabi.ptr(num_tokens_post_padded), _cabi.stream_ptr(A.device)))
+        tw = None
+        if mul_routed_weight:
+            tw = topk_weights if topk_weights.dtype in _cabi.DTYPE_CODE else topk_weights.float()
+            tw = tw.contiguous().reshape(-1)
+        _grouped_gemm(c2, a_sorted, B, a_s_sorted, w_s, tw, sorted_token_ids, expert_ids, num_tokens_post_padded,
+                      numel, scale_mode, fuse_silu=FUSE_SILU, scatter=True, mul_weight=mul_routed_weight,
+                      block_rows=block_rows, a_scale_per_row=per_row)
+
+
+def dispatch_fused_moe_kernel(A, B, C, A_scale, B_scale, B_zp, topk_weights, sorted_token_ids, expert_ids,
+                              num_tokens_post_padded, mul_routed_weight, top_k, config, compute_type, use_fp8_w8a8,
+                              use_int8_w8a8, use_int8_w8a16, use_int4_w4a16, per_channel_quant, block_shape=None,
+                              B_bias=None, FUSE_SILU=False, direct_sum=False, out_top_k=1) -> None:
+    """Reference: fused_moe.py:1730-1818.  The weight-only (wna16) branch is not implemented."""
+    if B_zp is not None:
+        raise NotImplementedError("zero points (weight-only quantisation) are not implemented")
+    invoke_fused_moe_triton_kernel(A, B, C, A_scale, B_scale, topk_weights, sorted_token_ids, expert_ids,
+                                   num_tokens_post_padded, mul_routed_weight, top_k, config, compute_type,
+                                   use_fp8_w8a8, use_int8_w8a8, use_int8_w8a16, use_int4_w4a16, per_channel_quant,
+                                   block_shape, B_bias, FUSE_SILU=FUSE_SILU, direct_sum=direct_sum, out_top_k=out_top_k)
 
 
 def inplace_fused_experts(hidden_states, w1, w2, topk_weights, topk_ids, **kwargs) -> None:

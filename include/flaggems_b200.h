@@ -75,6 +75,20 @@ int fg_per_token_quant_fp8(const void* x, int x_dtype, void* q, float* s, int64_
                            int64_t ld_x, int64_t ld_q, const int32_t* row_index, int32_t index_div,
                            int32_t index_limit, const int32_t* n_rows_dev, void* stream);
 
+/* Per-tensor branches of _fp8_quantize: src/flag_gems/fused/fused_moe.py:686-698.
+ * dynamic == 0 (static scale given): q = x / scale_or_amax[0].
+ * dynamic != 0: scale_or_amax[0] holds max|x| over the tensor (fg_abs_max); s = max(amax,1e-10)/448,
+ * q = x * (1/s), and s is written to scale_out[0].  Row gather options as above. */
+int fg_per_tensor_quant_fp8(const void* x, int x_dtype, void* q, const float* scale_or_amax, int dynamic,
+                            float* scale_out, int64_t M, int64_t K, int64_t ld_x, int64_t ld_q,
+                            const int32_t* row_index, int32_t index_div, int32_t index_limit,
+                            const int32_t* n_rows_dev, void* stream);
+
+/* max|x| over x[0:M, 0:K] into amax[0], which the caller has set to zero (the `A.abs().amax()` of
+ * the same reference lines).  n_rows_dev (nullable): device-side row count. */
+int fg_abs_max(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ld_x, const int32_t* n_rows_dev,
+               float* amax, void* stream);
+
 /* Same gather options for the per-group form (used by the block-FP8 MoE path;
  * src/flag_gems/fused/fused_moe.py:647-659 feeding :2016-2023). Scales are written
  * row-major [M, K/group]. */

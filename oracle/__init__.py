@@ -21,6 +21,7 @@ from .quant import (  # noqa: F401
     act_quant,
     per_token_group_quant_fp8,
     per_token_quant_fp8,
+    per_tensor_quant_fp8,
     quantize_weight_per_channel,
     quantize_weight_block,
 )
@@ -31,5 +32,6 @@ from .moe import (  # noqa: F401
     moe_sum,
     fused_moe_block_fp8,
     fused_moe_per_channel_fp8,
+    fused_moe_per_tensor_fp8,
     dense_block_fp8_mlp,
 )

@@ -4,7 +4,7 @@ from typing import Optional, Tuple
 import torch
 
 from .gemm import block_scaled_mm
-from .quant import per_token_group_quant_fp8, per_token_quant_fp8
+from .quant import per_tensor_quant_fp8, per_token_group_quant_fp8, per_token_quant_fp8
 
 
 def moe_align_block_size(
@@ -164,6 +164,50 @@ def fused_moe_per_channel_fp8(
         act = _silu_mul_f32(z, fuse_silu, hidden.dtype)
         aq, asc = per_token_quant_fp8(act)
         r = torch.mm(aq.float(), w2[e].float().t()) * asc * s2
+        r = (r * topk_weights[tok, slot].float().unsqueeze(1)).to(hidden.dtype)
+        out[tok, slot] = r.float()
+    return moe_sum(out).to(hidden.dtype)
+
+
+def fused_moe_per_tensor_fp8(
+    hidden: torch.Tensor,
+    w1: torch.Tensor,
+    w2: torch.Tensor,
+    w1_scale: torch.Tensor,
+    w2_scale: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    a1_scale: Optional[torch.Tensor] = None,
+    a2_scale: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Per-tensor FP8 MoE layer: one scale per expert weight, one per activation tensor.
+
+    Restated from the kernel path of src/flag_gems/fused/fused_moe.py: per-tensor quantisation of
+    the hidden states (:686-698, dynamic unless a1_scale is given), ``acc * a_scale * b_scale``
+    (:1478-1479), fused SiLU in fp32 (:1344), per-tensor quantisation of the whole intermediate
+    [T*topk, I], router weight in fp32 then cast (:1485-1493), fp32 top-k sum.  The reference's own
+    test of this mode (tests/test_fused_experts_impl.py:375-461) compares against a per-row
+    fake-quantised formulation with rtol 0.5; this restatement follows the device path instead.
+    """
+    t, h = hidden.shape
+    topk = topk_ids.shape[1]
+    inter = w2.shape[2]
+    hq, hs = per_tensor_quant_fp8(hidden, a1_scale)
+    act = torch.zeros(t, topk, inter, dtype=hidden.dtype)
+    for e in range(w1.shape[0]):
+        tok, slot = torch.nonzero(topk_ids == e, as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        z = torch.mm(hq[tok].float(), w1[e].float().t()) * hs * w1_scale.reshape(-1)[e].float()
+        act[tok, slot] = _silu_mul_f32(z, True, hidden.dtype)
+    aq, a_s = per_tensor_quant_fp8(act.reshape(t * topk, inter), a2_scale)
+    aq = aq.reshape(t, topk, inter)
+    out = torch.zeros(t, topk, w2.shape[1], dtype=torch.float32)
+    for e in range(w1.shape[0]):
+        tok, slot = torch.nonzero(topk_ids == e, as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        r = torch.mm(aq[tok, slot].float(), w2[e].float().t()) * a_s * w2_scale.reshape(-1)[e].float()
         r = (r * topk_weights[tok, slot].float().unsqueeze(1)).to(hidden.dtype)
         out[tok, slot] = r.float()
     return moe_sum(out).to(hidden.dtype)

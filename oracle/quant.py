@@ -101,6 +101,22 @@ def per_token_quant_fp8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return q, s.reshape(x.shape[:-1] + (1,))
 
 
+def per_tensor_quant_fp8(x: torch.Tensor, scale: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-tensor quantisation, static or dynamic.
+
+    Follows src/flag_gems/fused/fused_moe.py:686-698: with a given scale ``q = clamp(x.float() / scale)``;
+    otherwise ``scale = max(max|x|, 1e-10) / 448`` and ``q = clamp(x.float() * (1 / scale))``.
+    """
+    if scale is not None:
+        s = scale.float().reshape(-1)[:1]
+        q = (x.float() / s).clamp(FP8_MIN, FP8_MAX).to(FP8)
+        return q, s
+    amax = x.abs().amax().clamp(min=1e-10).to(torch.float32)
+    s = amax / FP8_MAX
+    q = (x.float() * (1.0 / s)).clamp(FP8_MIN, FP8_MAX).to(FP8)
+    return q, s.reshape(1)
+
+
 def quantize_weight_per_channel(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """Synthetic-weight helper: per-output-channel scales for W[..., N, K] fp32.
 

@@ -124,6 +124,14 @@ def main():
     q, s = fq(x, None, False, [128, 128])
     save("fp8_quantize_block3d", dict(x=x, q=q.view(torch.uint8), s=s))
 
+    # per-tensor branches (:686-698): dynamic scale, then a given scale
+    x = torch.randn(33, 512, generator=g).bfloat16()
+    q_dyn, s_dyn = fq(x, None, False, None)
+    given = torch.tensor([0.0123])
+    q_st, _ = fq(x, given, False, None)
+    save("fp8_quantize_per_tensor", dict(x=x, q_dynamic=q_dyn.view(torch.uint8), s_dynamic=s_dyn,
+                                         scale_static=given, q_static=q_st.view(torch.uint8)))
+
     # ---- moe_align_block_size: tests/test_moe_align_block_size.py:28-123
     fa = lift("tests/test_moe_align_block_size.py", ["torch_moe_align_block_size"])[
         "torch_moe_align_block_size"

@@ -59,6 +59,73 @@ def test_fused_moe_block_fp8(t, h, i, e, topk):
     _close(out, ref)
 
 
+@pytest.mark.parametrize("static", [False, True])
+def test_fused_moe_per_tensor(static):
+    g = torch.Generator().manual_seed(3)
+    t, h, i, e, topk = 100, 512, 256, 8, 2
+    hidden = torch.randn(t, h, generator=g).bfloat16()
+    w1 = (torch.randn(e, 2 * i, h, generator=g) * 20).clamp(-448, 448).to(FP8)
+    w2 = (torch.randn(e, h, i, generator=g) * 20).clamp(-448, 448).to(FP8)
+    s1 = torch.rand(e, generator=g) * 1e-3 + 5e-4
+    s2 = torch.rand(e, generator=g) * 1e-3 + 5e-4
+    tw, ti = _router(t, e, topk, g)
+    a1 = torch.tensor([0.011]) if static else None
+    a2 = torch.tensor([0.004]) if static else None
+    out = flag_gems.fused_experts_impl(hidden.cuda(), w1.cuda(), w2.cuda(), tw.cuda(), ti.cuda(), use_fp8_w8a8=True,
+                                       w1_scale=s1.cuda(), w2_scale=s2.cuda(),
+                                       a1_scale=None if a1 is None else a1.cuda(),
+                                       a2_scale=None if a2 is None else a2.cuda())
+    ref = oracle.fused_moe_per_tensor_fp8(hidden, w1, w2, s1, s2, tw, ti, a1, a2)
+    # a value that sits on an FP8 rounding boundary of the shared intermediate scale may flip:
+    # allow 2 % of the output range on top of rtol 1e-2
+    got, ref = out.cpu().float(), ref.float()
+    torch.testing.assert_close(got, ref, rtol=1e-2, atol=max(1e-2, 2e-2 * float(ref.abs().max())))
+
+
+@pytest.mark.parametrize("block_m", [16, 64, 128])
+@pytest.mark.parametrize("mode", ["block", "channel", "tensor"])
+def test_dispatch_fused_moe_kernel(block_m, mode):
+    """One grouped GEMM through the reference's launch-level API, ids aligned with several block sizes."""
+    g = torch.Generator().manual_seed(4)
+    t, k, n, e, topk = 77, 512, 384, 8, 2
+    a = torch.randn(t, k, generator=g).bfloat16()
+    w = torch.randn(e, n, k, generator=g) * 0.05
+    tw, ti = _router(t, e, topk, g)
+    if mode == "block":
+        aq, a_s = oracle.per_token_group_quant_fp8(a, 128)
+        wq = torch.empty(e, n, k, dtype=FP8)
+        ws = torch.empty(e, n // 128, k // 128)
+        for x in range(e):
+            wq[x], ws[x] = oracle.quantize_weight_block(w[x])
+    elif mode == "channel":
+        aq, a_s = oracle.per_token_quant_fp8(a)
+        wq, ws = oracle.quantize_weight_per_channel(w)
+    else:
+        aq, a_s = oracle.per_tensor_quant_fp8(a)
+        wq = (w / 0.001).clamp(-448, 448).to(FP8)
+        ws = torch.full((e,), 0.001)
+    sorted_ids, expert_ids, post_pad = flag_gems.moe_align_block_size(ti.cuda(), block_m, e)
+    c = torch.full((t, topk, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    flag_gems.dispatch_fused_moe_kernel(
+        aq.cuda(), wq.cuda(), c, a_s.cuda(), ws.cuda(), None, tw.cuda(), sorted_ids, expert_ids, post_pad,
+        True, topk, {"BLOCK_SIZE_M": block_m}, torch.bfloat16, True, False, False, False, mode == "channel",
+        block_shape=[128, 128] if mode == "block" else None)
+    ref = torch.zeros(t, topk, n)
+    for x in range(e):
+        tok, slot = torch.nonzero(ti == x, as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        if mode == "block":
+            r = oracle.block_scaled_mm(aq[tok], wq[x], a_s[tok], ws[x], out_dtype=torch.float32)
+        elif mode == "channel":
+            r = torch.mm(aq[tok].float(), wq[x].float().t()) * a_s[tok] * ws[x].reshape(1, -1)
+        else:
+            r = torch.mm(aq[tok].float(), wq[x].float().t()) * a_s * ws[x]
+        ref[tok, slot] = (r * tw[tok, slot].float().unsqueeze(1)).bfloat16().float()
+    assert not torch.isnan(c.float()).any()
+    _close(c, ref)
+
+
 def test_fused_moe_block_fp8_golden(golden_dir):
     """Against the output of the reference's own golden (tests/test_fused_experts_impl.py:604-662),
     with that test's tolerance."""

@@ -173,6 +173,22 @@ def test_per_token_quant_golden(golden_dir):
         _assert_bytes_equal(q, c["q"])
 
 
+def test_per_tensor_quant(golden_dir):
+    c = torch.load(os.path.join(golden_dir, "fp8_quantize_per_tensor.pt"))
+    fq = flag_gems.fused.fused_moe._fp8_quantize
+    q, s = fq(c["x"].cuda(), None, False, None)
+    assert torch.equal(s.cpu(), c["s_dynamic"])
+    _assert_bytes_equal(q, c["q_dynamic"])
+    q, s = fq(c["x"].cuda(), c["scale_static"].cuda(), False, None)
+    _assert_bytes_equal(q, c["q_static"])
+    torch.manual_seed(6)
+    x = (torch.randn(777, 2048) * 5).bfloat16()
+    q, s = fq(x.cuda(), None, False, None)
+    qr, sr = oracle.per_tensor_quant_fp8(x)
+    assert torch.equal(_bits(s.cpu()), _bits(sr))
+    _assert_bytes_equal(q, qr)
+
+
 def test_vllm_op_writes_in_place():
     flag_gems.patch_empty_vllm()
     torch.manual_seed(5)

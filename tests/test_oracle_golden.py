@@ -66,6 +66,14 @@ def test_per_token_quant_bit_exact(golden_dir):
         assert torch.equal(s.view(torch.int32), c["s"].view(torch.int32))
 
 
+def test_per_tensor_quant_bit_exact(golden_dir):
+    c = load(golden_dir, "fp8_quantize_per_tensor")
+    q, s = oracle.per_tensor_quant_fp8(c["x"])
+    assert torch.equal(q.view(torch.uint8), c["q_dynamic"]) and torch.equal(s, c["s_dynamic"])
+    q, _ = oracle.per_tensor_quant_fp8(c["x"], c["scale_static"])
+    assert torch.equal(q.view(torch.uint8), c["q_static"])
+
+
 def test_moe_align_exact(golden_dir):
     for c in load(golden_dir, "moe_align"):
         so, eo, no = oracle.moe_align_block_size(c["topk_ids"], c["block_size"], c["num_experts"])
