@@ -20,12 +20,14 @@
 //
 // Every mbarrier wait is bounded; a wait that runs out sets the device status word and the
 // CTA drains and frees its TMEM instead of hanging.
+#include <cooperative_groups.h>
 #include <cuda.h>
 
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
 using namespace fgptx;
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -102,6 +104,8 @@ struct Cfg {
     static constexpr int SMEM_BYTES =
         STAGES * STAGE_BYTES + TAIL_PAD + BAR_BYTES + EPI_WARPS * EPI_STAGE_BYTES + 1024;
     static_assert(SMEM_BYTES <= 232448, "over the 227 KB shared memory limit");
+    // split-K parks a 128 x BN fp32 partial tile (rows padded by 4 floats) in the ring's memory
+    static_assert(SMALL_A || BLOCK_M * (BN + 4) * 4 <= STAGES * STAGE_BYTES, "partial tile does not fit");
 };
 
 __device__ __forceinline__ float load_as_float(const void* p, int dtype, int64_t i) {
@@ -215,11 +219,16 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int num_m, int num_n) {
     return tc;
 }
 
-template <int BN, bool BLOCK_SCALED, bool FUSE_SILU, bool SMALL_A>
+// SPLITK: the CTAs of one thread-block cluster share an output tile and split its K range; each
+// leaves its fp32 partial tile in its own shared memory and the cluster adds them up through
+// distributed shared memory (no global scratch, no atomics).  For decode-sized M, where there are
+// fewer tiles than SMs and the job is to pull the weights from HBM with every SM.
+template <int BN, bool BLOCK_SCALED, bool FUSE_SILU, bool SMALL_A, bool SPLITK>
 __global__ void __launch_bounds__(Cfg<BN, SMALL_A>::THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                 const GemmParams p) {
     using C = Cfg<BN, SMALL_A>;
+    static_assert(!SPLITK || (!FUSE_SILU && !SMALL_A && BN >= 128), "split-K is built for the plain wide tiles");
     static_assert(!FUSE_SILU || BN >= 128, "fused SiLU needs a tile of at least 128 columns");
     constexpr int STAGES = C::STAGES;
     constexpr int OUT_TILE_N = FUSE_SILU ? BN / 2 : BN;  // output columns per tile
@@ -271,6 +280,17 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     const int num_n = (p.n_out + OUT_TILE_N - 1) / OUT_TILE_N;
     const int num_tiles = num_m * num_n;
     const int a_rows_step = p.grouped ? p.block_rows : BLOCK_M;
+    // K range and tile walk of this CTA (split-K: rank in the cluster = K slice, one cluster per tile)
+    int kb_begin = 0, kb_end = num_k_blocks, tile_first = blockIdx.x, tile_step = gridDim.x, k_slices = 1;
+    if constexpr (SPLITK) {
+        cg::cluster_group cluster = cg::this_cluster();
+        k_slices = (int)cluster.num_blocks();
+        const int per = (num_k_blocks + k_slices - 1) / k_slices;
+        kb_begin = (int)cluster.block_rank() * per;
+        kb_end = min(kb_begin + per, num_k_blocks);
+        tile_first = blockIdx.x / k_slices;
+        tile_step = gridDim.x / k_slices;
+    }
     const uint32_t stage_tx = (uint32_t)((p.grouped ? p.block_rows : p.a_box_rows) * BLOCK_K + C::B_BYTES);
 
     if (warp < C::FIRST_EPI_WARP) {
@@ -281,13 +301,13 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            for (int t = tile_first; t < num_tiles && ok; t += tile_step) {
                 const TileCoord tc = tile_coord(t, num_m, num_n);
                 const int expert = p.grouped ? p.expert_ids[tc.m_blk] : 0;
                 if (expert < 0) continue;
                 const int m0 = tc.m_blk * a_rows_step;
                 const int n0 = tc.n_blk * OUT_TILE_N;
-                for (int kb = 0; kb < num_k_blocks; ++kb) {
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 1);
                     if (!ok) break;
                     uint8_t* sa = smem + stage * C::STAGE_BYTES;
@@ -316,13 +336,13 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             uint32_t phase = 0;
             uint32_t acc_iter = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            for (int t = tile_first; t < num_tiles && ok; t += tile_step) {
                 const TileCoord tc = tile_coord(t, num_m, num_n);
                 const int expert = p.grouped ? p.expert_ids[tc.m_blk] : 0;
                 if (expert < 0) continue;
-                for (int kb = 0; kb < num_k_blocks; ++kb) {
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     const uint32_t buf = acc_iter & 1u;
-                    if (BLOCK_SCALED || kb == 0) {
+                    if (BLOCK_SCALED || kb == kb_begin) {
                         ok = mbar_wait(&tmem_empty[buf], ((acc_iter >> 1) & 1u) ^ 1u, abort_flag, p.status, 2);
                         if (!ok) break;
                     }
@@ -335,12 +355,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     const uint32_t d_tmem = tmem_base + buf * BN;
 #pragma unroll
                     for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-                        const uint32_t accumulate = BLOCK_SCALED ? (k != 0) : ((kb | k) != 0);
+                        const uint32_t accumulate = BLOCK_SCALED ? (k != 0) : (kb != kb_begin || k != 0);
                         // advancing K by 32 bytes inside the swizzle row: +2 in 16-byte units
                         umma_f8f6f4(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, accumulate);
                     }
                     umma_commit(&empty_bar[stage]);
-                    if (BLOCK_SCALED || kb == num_k_blocks - 1) {
+                    if (BLOCK_SCALED || kb == kb_end - 1) {
                         umma_commit(&tmem_full[buf]);
                         ++acc_iter;
                     }
@@ -364,7 +384,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         uint32_t acc_iter = 0;
         bool ok = true;
 
-        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        for (int t = tile_first; t < num_tiles && ok; t += tile_step) {
             const TileCoord tc = tile_coord(t, num_m, num_n);
             const int expert = p.grouped ? p.expert_ids[tc.m_blk] : 0;
             const int m0 = tc.m_blk * a_rows_step;
@@ -448,6 +468,13 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                             const float u = __uint_as_float(raw_up[i]) * sa * su;
                             v[i] = silu_mul(g, u);
                         }
+                    } else if constexpr (SPLITK) {
+                        tmem_ld_32x32b_x32(tbuf + 128 * half + 32 * c, raw);
+                        tmem_ld_wait();
+                        float* dst = reinterpret_cast<float*>(smem) + (size_t)r_in_tile * (BN + 4) + 128 * half + 32 * c;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            reinterpret_cast<uint4*>(dst)[i] = make_uint4(raw[4 * i], raw[4 * i + 1], raw[4 * i + 2], raw[4 * i + 3]);
                     } else {
                         tmem_ld_32x32b_x32(tbuf + 128 * half + 32 * c, raw);
                         tmem_ld_wait();
@@ -464,11 +491,13 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                             v[i] = x;
                         }
                     }
-                    const int nc = min(32, p.n_out - col);
-                    if (nc == 32 && p.c_vec_ok && esz == 2)
-                        store_chunk_coalesced(epi_stage, lane, v, out_ptr, row_ok, col, p.out_dtype);
-                    else if (row_ok && nc > 0)
-                        store_chunk(out_ptr, col, v, nc, p.out_dtype, p.c_vec_ok);
+                    if constexpr (!SPLITK) {
+                        const int nc = min(32, p.n_out - col);
+                        if (nc == 32 && p.c_vec_ok && esz == 2)
+                            store_chunk_coalesced(epi_stage, lane, v, out_ptr, row_ok, col, p.out_dtype);
+                        else if (row_ok && nc > 0)
+                            store_chunk(out_ptr, col, v, nc, p.out_dtype, p.c_vec_ok);
+                    }
                 }
                 tc_fence_before_sync();
                 __syncwarp();
@@ -494,15 +523,17 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 const float* as_row = p.sa + srow * p.ld_as;
                 const float* bs0 = bs_e + nb0 * p.bs_stride_n;
                 const float* bs1 = bs_e + nb1 * p.bs_stride_n;
-                float as_next = as_row[0], b0_next = __ldg(bs0), b1_next = FUSE_SILU ? __ldg(bs1) : 0.0f;
+                float as_next = as_row[(int64_t)kb_begin * p.as_stride_k];
+                float b0_next = __ldg(bs0 + (int64_t)kb_begin * p.bs_stride_k);
+                float b1_next = FUSE_SILU ? __ldg(bs1 + (int64_t)kb_begin * p.bs_stride_k) : 0.0f;
                 auto chunk_col = [&](int c) -> uint32_t {
                     if constexpr (FUSE_SILU) return (uint32_t)((c < 2 ? 0 : BN / 2) + 64 * half + 32 * (c & 1));
                     else return (uint32_t)(128 * half + 32 * c);
                 };
-                for (int kb = 0; kb < num_k_blocks; ++kb) {
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     const float sc0f = as_next * b0_next;
                     const float sc1f = FUSE_SILU ? as_next * b1_next : sc0f;
-                    if (kb + 1 < num_k_blocks) {  // next block's scales travel while this block is folded in
+                    if (kb + 1 < kb_end) {  // next block's scales travel while this block is folded in
                         as_next = as_row[(int64_t)(kb + 1) * p.as_stride_k];
                         b0_next = __ldg(bs0 + (int64_t)(kb + 1) * p.bs_stride_k);
                         if constexpr (FUSE_SILU) b1_next = __ldg(bs1 + (int64_t)(kb + 1) * p.bs_stride_k);
@@ -543,6 +574,14 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     ++acc_iter;
                 }
                 if (!ok) break;
+                if constexpr (SPLITK) {
+                    float* dst = reinterpret_cast<float*>(smem) + (size_t)r_in_tile * (BN + 4) + 128 * half;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        reinterpret_cast<uint4*>(dst)[i] =
+                            make_uint4((uint32_t)(acc[2 * i] & 0xffffffffull), (uint32_t)(acc[2 * i] >> 32),
+                                       (uint32_t)(acc[2 * i + 1] & 0xffffffffull), (uint32_t)(acc[2 * i + 1] >> 32));
+                } else
 #pragma unroll
                 for (int c = 0; c < OUT_CHUNKS; ++c) {
                     const int col = out_col_base + 32 * c;
@@ -567,6 +606,60 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 }
             }
         }
+    }
+
+    if constexpr (SPLITK) {
+        // ------------------------- cluster reduction of the K slices ---------------------------
+        // Every thread of every CTA of the cluster reaches both syncs, also after a failed wait.
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();  // all partial tiles are in shared memory
+        if (warp >= C::FIRST_EPI_WARP && tile_first < num_tiles) {
+            const TileCoord tc = tile_coord(tile_first, num_m, num_n);
+            const int n0 = tc.n_blk * BN;
+            const int m0 = tc.m_blk * BLOCK_M;
+            const int rows = (int)min((int64_t)BLOCK_M, p.M - m0);
+            const int width = BN / k_slices;            // columns this CTA finishes (multiple of 4)
+            const int c_first = (int)cluster.block_rank() * width;
+            const int vec_per_row = width / 4;
+            const int esz = p.out_dtype == FG_DTYPE_F32 ? 4 : 2;
+            const float* part[8];
+            for (int q = 0; q < k_slices; ++q)
+                part[q] = cluster.map_shared_rank(reinterpret_cast<float*>(smem), q);
+            const int n_epi = C::EPI_WARPS * 32;
+            for (int idx = threadIdx.x - C::FIRST_EPI_WARP * 32; idx < rows * vec_per_row; idx += n_epi) {
+                const int r = idx / vec_per_row, c = c_first + (idx % vec_per_row) * 4;
+                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int q = 0; q < k_slices; ++q) {
+                    const float4 v = *reinterpret_cast<const float4*>(part[q] + (size_t)r * (BN + 4) + c);
+                    sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+                }
+                float o[4] = {sum.x, sum.y, sum.z, sum.w};
+                const int64_t row = (int64_t)m0 + r;
+                if constexpr (!BLOCK_SCALED) {
+                    const float sa = p.sa_mode == FG_SCALE_VECTOR ? p.sa[row] : p.sa[0];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int n = min(n0 + c + i, p.n_out - 1);
+                        const float sb = p.sb_mode == FG_SCALE_VECTOR ? __ldg(p.sb + n) : p.sb[0];
+                        float x = sb * (sa * o[i]);
+                        if (p.bias) {
+                            const float b = load_as_float(p.bias, p.out_dtype, n);
+                            x = p.bias_after_round ? round_through(x, p.out_dtype) + b : x + b;
+                        }
+                        o[i] = x;
+                    }
+                }
+                uint8_t* out = reinterpret_cast<uint8_t*>(p.c) + (row * p.ld_c + n0 + c) * esz;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (n0 + c + i >= p.n_out) break;
+                    if (p.out_dtype == FG_DTYPE_BF16) reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(o[i]);
+                    else if (p.out_dtype == FG_DTYPE_F16) reinterpret_cast<__half*>(out)[i] = __float2half_rn(o[i]);
+                    else reinterpret_cast<float*>(out)[i] = o[i];
+                }
+            }
+        }
+        cluster.sync();  // nobody leaves while a peer may still read its partial tile
     }
 
     // ------------------------------- teardown ---------------------------------------------
@@ -615,10 +708,65 @@ int make_map(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, uint64_
     return FG_OK;
 }
 
+// How many clusters of `slices` CTAs of the split-K kernel fit on the device at once (cached).
+template <int BN, bool BS>
+int max_resident_clusters(int slices) {
+    static int cache[9] = {0};
+    if (cache[slices]) return cache[slices];
+    using C = Cfg<BN, false>;
+    auto kernel = gemm_fp8_kernel<BN, BS, false, false, true>;
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(slices * 64), 1, 1);
+    cfg.blockDim = dim3(C::THREADS, 1, 1);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)slices;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        n = 1;
+    }
+    cache[slices] = n;
+    return n;
+}
+
+template <int BN, bool BS>
+int launch_splitk(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int tiles, int slices,
+                  cudaStream_t st) {
+    using C = Cfg<BN, false>;
+    auto kernel = gemm_fp8_kernel<BN, BS, false, false, true>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        FG_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        attr_done = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(tiles * slices), 1, 1);
+    cfg.blockDim = dim3(C::THREADS, 1, 1);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)slices;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    FG_CUDA(cudaLaunchKernelEx(&cfg, kernel, ta, tb, p));
+    fg_count_launch(1);
+    return FG_OK;
+}
+
 template <int BN, bool BS, bool SILU, bool SMALL_A = false>
 int launch_inst(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int max_tiles, cudaStream_t st) {
     using C = Cfg<BN, SMALL_A>;
-    auto kernel = gemm_fp8_kernel<BN, BS, SILU, SMALL_A>;
+    auto kernel = gemm_fp8_kernel<BN, BS, SILU, SMALL_A, false>;
     static bool attr_done = false;
     if (!attr_done) {
         FG_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
@@ -663,6 +811,26 @@ int launch_gemm(GemmParams& p, const void* a, int64_t a_rows, int64_t ld_a, cons
         bn = 32;
         small_a = p.M <= 32;
     }
+    // Decode-sized M with fewer wide tiles than half the SMs: split K over a cluster instead of
+    // narrowing the tile (a narrow tile still pays a full MMA per K step).
+    int k_slices = 1;
+    if (!p.grouped && !fuse_silu && m_tiles == 1) {
+        const int wide = p.n_out >= 256 ? 256 : 128;
+        const int64_t wide_tiles = fg_cdiv(p.n_out, wide);
+        const int64_t nkb = fg_cdiv(p.K, BLOCK_K);
+        for (int cand = 8; cand >= 2; cand /= 2) {
+            const int64_t per = fg_cdiv(nkb, cand);
+            const int resident = wide == 256
+                ? (block_scaled ? max_resident_clusters<256, true>(cand) : max_resident_clusters<256, false>(cand))
+                : (block_scaled ? max_resident_clusters<128, true>(cand) : max_resident_clusters<128, false>(cand));
+            if (wide_tiles <= resident && per >= 2 && (cand - 1) * per < nkb) {
+                k_slices = cand;
+                bn = wide;
+                small_a = false;
+                break;
+            }
+        }
+    }
     p.a_box_rows = BLOCK_M;
     if (!p.grouped && p.M < BLOCK_M) p.a_box_rows = (int)((p.M + 7) / 8 * 8);
     const int out_tile = fuse_silu ? bn / 2 : bn;
@@ -679,6 +847,12 @@ int launch_gemm(GemmParams& p, const void* a, int64_t a_rows, int64_t ld_a, cons
     if (rc != FG_OK) return rc;
 
     const int t = (int)tiles;
+    if (k_slices > 1) {
+        if (bn == 256) return block_scaled ? launch_splitk<256, true>(ta, tb, p, t, k_slices, st)
+                                           : launch_splitk<256, false>(ta, tb, p, t, k_slices, st);
+        return block_scaled ? launch_splitk<128, true>(ta, tb, p, t, k_slices, st)
+                            : launch_splitk<128, false>(ta, tb, p, t, k_slices, st);
+    }
     if (bn == 256) {
         if (block_scaled) return fuse_silu ? launch_inst<256, true, true>(ta, tb, p, t, st)
                                            : launch_inst<256, true, false>(ta, tb, p, t, st);
