@@ -437,11 +437,15 @@ def run_ours(args):
         for _ in range(max(args.warmup, 3)):
             step_resident()
         launches0 = _cabi.launch_count()
-        ms = timed(step_resident, args.steps)
-        launches = _cabi.launch_count() - launches0
+        # K steps are timed twice and the faster pass is reported: a host hiccup on a shared box
+        # (launches are issued from Python) otherwise lands in a 10-step window undiluted.
+        ms_passes = [timed(step_resident, args.steps) for _ in range(2)]
+        ms = min(ms_passes)
+        launches = (_cabi.launch_count() - launches0) // 2
         for _ in range(2):
             step_e2e()
-        ms_e2e = timed(step_e2e, args.steps)
+        e2e_passes = [timed(step_e2e, args.steps) for _ in range(2)]
+        ms_e2e = min(e2e_passes)
         t_end = time.time() + 0.3
         while clocks.rows.__len__() < 3 and time.time() < t_end:  # let a few samples land under load
             step_resident()
@@ -508,6 +512,9 @@ def run_ours(args):
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d * world,
                 "d2h_bytes_per_step": d2h * world, "ms_per_step": round(ms_e2e, 4)},
         "gpu_launches": int(launches), "roofline": roofline, "device_status": status,
+        "timing": {"passes_of_k_steps": 2, "reported": "faster pass",
+                   "ms_per_step_passes": [round(x, 4) for x in ms_passes],
+                   "e2e_ms_per_step_passes": [round(x, 4) for x in e2e_passes]},
         "phase_ms_rank0": phases,
         "dispatch": ("n/a (single rank)" if world == 1 else
                      "NCCL all_to_all_single" if (args.a2a_combine or args.a2a_dispatch) else

@@ -8,7 +8,8 @@
 //               multi-stage shared-memory ring (128-byte swizzle), mbarrier complete_tx.
 //   warp 1      MMA issuer: tcgen05.mma kind::f8f6f4, M=128, N=BN, K=32 per instruction, fp32
 //               accumulators in TMEM (two buffers of BN columns), tcgen05.commit to release
-//               ring stages and to publish accumulators.
+//               ring stages and to publish accumulators.  The warp stays converged and an
+//               elected lane issues; barrier states are probed one K block ahead.
 //   warps 4..   epilogue: tcgen05.ld TMEM -> registers, scales / SiLU / router weight / bias,
 //               conversion and global stores.  BN/32 warps (one or two warpgroups); each thread
 //               owns one tile row and 128 accumulator columns.  (Warps 2-3 only pad the first
@@ -18,10 +19,15 @@
 // the epilogue warps fold it into fp32 registers as acc += partial * (As[m,kb] * Bs[nb,kb])
 // while the MMA warp fills the other TMEM buffer.
 //
+// Large dense products use the CTA-pair form of the same kernel (cta_group::2, one 256 x 256
+// tile per two SMs); decode-sized M uses the split-K form (one cluster per tile).
+//
 // Every mbarrier wait is bounded; a wait that runs out sets the device status word and the
 // CTA drains and frees its TMEM instead of hanging.
 #include <cooperative_groups.h>
 #include <cuda.h>
+#include <stdlib.h>
+#include <type_traits>
 
 #include "common.cuh"
 #include "ptx_sm100.cuh"
@@ -73,10 +79,15 @@ struct GemmParams {
     unsigned int* status;
 };
 
-template <int BN, bool SMALL_A>
+// PAIR: two CTAs of a cluster (cta_group::2) compute one 256 x 256 tile.  Each stages its own 128
+// rows of A and 128 of the 256 rows of B, and holds the accumulator of its 128 rows in its TMEM;
+// one MMA instruction issued by the even CTA drives both tensor cores.  Per CTA and K block that
+// is 32 KB through L2 and shared memory instead of 48 KB for the same arithmetic.
+template <int BN, bool SMALL_A, bool PAIR = false>
 struct Cfg {
     static_assert(BN == 32 || BN == 64 || BN == 128 || BN == 256, "unsupported tile width");
     static_assert(!SMALL_A || BN == 32, "the narrow-A layout exists for the 32-wide tile only");
+    static_assert(!PAIR || BN == 256, "the CTA-pair layout is built for the 256-wide tile");
     static constexpr int COLS = BN >= 128 ? 128 : BN;          // accumulator columns per epilogue thread
     static constexpr int EPI_WARPS = BN >= 128 ? BN / 32 : 4;  // one warp per 32 TMEM lanes, x column halves
     static constexpr int FIRST_EPI_WARP = 4;  // warps 0-3: TMA, MMA, two spare (one warpgroup)
@@ -93,9 +104,9 @@ struct Cfg {
     // shared memory (later stages or the tail pad) and only feed accumulator rows nobody reads.
     static constexpr int A_ROWS_SMEM = SMALL_A ? 32 : BLOCK_M;
     static constexpr int A_BYTES = A_ROWS_SMEM * BLOCK_K;
-    static constexpr int B_BYTES = BN * BLOCK_K;
+    static constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * BLOCK_K;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = BN == 256 ? 4 : BN == 128 ? 6 : BN == 64 ? 8 : (SMALL_A ? 22 : 9);
+    static constexpr int STAGES = PAIR ? 6 : BN == 256 ? 4 : BN == 128 ? 6 : BN == 64 ? 8 : (SMALL_A ? 22 : 9);
     static constexpr int TAIL_PAD = SMALL_A ? BLOCK_M * BLOCK_K : 0;
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
     static constexpr int BAR_BYTES = 512;  // (2*STAGES + 4) mbarriers, TMEM base slot, abort flag
@@ -105,7 +116,7 @@ struct Cfg {
         STAGES * STAGE_BYTES + TAIL_PAD + BAR_BYTES + EPI_WARPS * EPI_STAGE_BYTES + 1024;
     static_assert(SMEM_BYTES <= 232448, "over the 227 KB shared memory limit");
     // split-K parks a 128 x BN fp32 partial tile (rows padded by 4 floats) in the ring's memory
-    static_assert(SMALL_A || BLOCK_M * (BN + 4) * 4 <= STAGES * STAGE_BYTES, "partial tile does not fit");
+    static_assert(SMALL_A || PAIR || BLOCK_M * (BN + 4) * 4 <= STAGES * STAGE_BYTES, "partial tile does not fit");
 };
 
 __device__ __forceinline__ float load_as_float(const void* p, int dtype, int64_t i) {
@@ -223,12 +234,13 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int num_m, int num_n) {
 // leaves its fp32 partial tile in its own shared memory and the cluster adds them up through
 // distributed shared memory (no global scratch, no atomics).  For decode-sized M, where there are
 // fewer tiles than SMs and the job is to pull the weights from HBM with every SM.
-template <int BN, bool BLOCK_SCALED, bool FUSE_SILU, bool SMALL_A, bool SPLITK>
-__global__ void __launch_bounds__(Cfg<BN, SMALL_A>::THREADS, 1)
+template <int BN, bool BLOCK_SCALED, bool FUSE_SILU, bool SMALL_A, bool SPLITK, bool PAIR = false>
+__global__ void __launch_bounds__(Cfg<BN, SMALL_A, PAIR>::THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                 const GemmParams p) {
-    using C = Cfg<BN, SMALL_A>;
+    using C = Cfg<BN, SMALL_A, PAIR>;
     static_assert(!SPLITK || (!FUSE_SILU && !SMALL_A && BN >= 128), "split-K is built for the plain wide tiles");
+    static_assert(!PAIR || (!SPLITK && !FUSE_SILU && !SMALL_A), "the CTA pair serves the plain dense tiles");
     static_assert(!FUSE_SILU || BN >= 128, "fused SiLU needs a tile of at least 128 columns");
     constexpr int STAGES = C::STAGES;
     constexpr int OUT_TILE_N = FUSE_SILU ? BN / 2 : BN;  // output columns per tile
@@ -244,6 +256,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     uint8_t* epi_stage_base = smem + STAGES * C::STAGE_BYTES + C::TAIL_PAD + C::BAR_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;  // 0: issues the MMAs, owns the shared barriers
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -252,7 +265,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&tmem_full[b], 1);
-            mbar_init(&tmem_empty[b], C::EPI_WARPS);
+            mbar_init(&tmem_empty[b], PAIR ? 2 * C::EPI_WARPS : C::EPI_WARPS);
         }
         *abort_flag = 0u;
         fence_mbar_init();
@@ -264,7 +277,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         tmem_relinquish();
     }
     tc_fence_before_sync();
-    __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();  // the peer's barriers exist before anything signals them
+    else __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_base_slot;
 
@@ -277,11 +291,16 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     } else {
         num_m = (int)((p.M + BLOCK_M - 1) / BLOCK_M);
     }
+    if constexpr (PAIR) num_m = (int)((p.M + 2 * BLOCK_M - 1) / (2 * BLOCK_M));
     const int num_n = (p.n_out + OUT_TILE_N - 1) / OUT_TILE_N;
     const int num_tiles = num_m * num_n;
-    const int a_rows_step = p.grouped ? p.block_rows : BLOCK_M;
+    const int a_rows_step = PAIR ? 2 * BLOCK_M : (p.grouped ? p.block_rows : BLOCK_M);
     // K range and tile walk of this CTA (split-K: rank in the cluster = K slice, one cluster per tile)
     int kb_begin = 0, kb_end = num_k_blocks, tile_first = blockIdx.x, tile_step = gridDim.x, k_slices = 1;
+    if constexpr (PAIR) {
+        tile_first = blockIdx.x / 2;
+        tile_step = gridDim.x / 2;
+    }
     if constexpr (SPLITK) {
         cg::cluster_group cluster = cg::this_cluster();
         k_slices = (int)cluster.num_blocks();
@@ -305,13 +324,27 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 const TileCoord tc = tile_coord(t, num_m, num_n);
                 const int expert = p.grouped ? p.expert_ids[tc.m_blk] : 0;
                 if (expert < 0) continue;
-                const int m0 = tc.m_blk * a_rows_step;
+                const int m0 = tc.m_blk * a_rows_step + (int)cta_rank * BLOCK_M;
                 const int n0 = tc.n_blk * OUT_TILE_N;
                 for (int kb = kb_begin; kb < kb_end; ++kb) {
                     ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 1);
                     if (!ok) break;
                     uint8_t* sa = smem + stage * C::STAGE_BYTES;
                     uint8_t* sb = sa + C::A_BYTES;
+                    if constexpr (PAIR) {
+                        // Both CTAs' loads complete on the even CTA's barrier, which expects the
+                        // bytes of both; a completion that gets there before the expect only drives
+                        // the count negative for a moment.
+                        const uint32_t bar0 = mapa_shared(smem_u32(&full_bar[stage]), 0u);
+                        if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2u * stage_tx);
+                        tma_load_2d_2cta(sa, &tm_a, bar0, kb * BLOCK_K, m0);
+                        tma_load_3d_2cta(sb, &tm_b, bar0, kb * BLOCK_K, n0 + (int)cta_rank * (BN / 2), 0);
+                        if (++stage == STAGES) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                        continue;
+                    }
                     mbar_arrive_expect_tx(&full_bar[stage], stage_tx);
                     tma_load_2d(sa, &tm_a, &full_bar[stage], kb * BLOCK_K, m0);
                     if constexpr (FUSE_SILU) {
@@ -330,44 +363,73 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         }
     } else if (warp == 1) {
         // ------------------------------- MMA issuer ---------------------------------------
-        if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_e4m3_f32(BLOCK_M, BN);
+        // The whole warp walks the loop (so that addresses and descriptors stay warp-uniform) and
+        // one elected lane issues.  The tensor core queues only about six MMAs, i.e. one and a
+        // half K blocks, so everything this warp does between two K blocks is on the critical
+        // path: the state of the next K block's barriers is therefore probed (non-blocking)
+        // before the current block's MMAs are issued, and the blocking wait is only the fallback.
+        if (cta_rank == 0) {
+            constexpr uint32_t idesc = umma_idesc_e4m3_f32(PAIR ? 2 * BLOCK_M : BLOCK_M, BN);
             int stage = 0;
             uint32_t phase = 0;
             uint32_t acc_iter = 0;
             bool ok = true;
+            bool full_ready = false, tmem_ready = false;  // probed ahead for (stage, phase) / acc_iter
+            auto issue_block = [&](uint32_t a_addr, uint32_t d_tmem, auto zero_first) {
+                const uint64_t a_desc = umma_desc_k_sw128(a_addr);
+                const uint64_t b_desc = umma_desc_k_sw128(a_addr + C::A_BYTES);
+#pragma unroll
+                for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                    // advancing K by 32 bytes inside the swizzle row: +2 in 16-byte units
+                    const uint32_t accumulate = (decltype(zero_first)::value && k == 0) ? 0u : 1u;
+                    if constexpr (PAIR)
+                        umma_f8f6f4_2cta(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, accumulate);
+                    else
+                        umma_f8f6f4(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, accumulate);
+                }
+            };
             for (int t = tile_first; t < num_tiles && ok; t += tile_step) {
                 const TileCoord tc = tile_coord(t, num_m, num_n);
                 const int expert = p.grouped ? p.expert_ids[tc.m_blk] : 0;
                 if (expert < 0) continue;
                 for (int kb = kb_begin; kb < kb_end; ++kb) {
                     const uint32_t buf = acc_iter & 1u;
-                    if (BLOCK_SCALED || kb == kb_begin) {
-                        ok = mbar_wait(&tmem_empty[buf], ((acc_iter >> 1) & 1u) ^ 1u, abort_flag, p.status, 2);
+                    const bool new_acc = BLOCK_SCALED || kb == kb_begin;
+                    if (new_acc) {
+                        ok = __all_sync(0xffffffffu, tmem_ready || mbar_wait(&tmem_empty[buf], ((acc_iter >> 1) & 1u) ^ 1u,
+                                                                             abort_flag, p.status, 2));
                         if (!ok) break;
+                        // Orders the epilogue's TMEM reads (published by its arrive) before the MMAs
+                        // that overwrite the buffer.  The operand tiles need no fence: TMA writes
+                        // and MMA reads are async-proxy accesses ordered by the full barrier.
+                        tc_fence_after_sync();
                     }
-                    ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3);
+                    ok = __all_sync(0xffffffffu, full_ready || mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3));
                     if (!ok) break;
-                    tc_fence_after_sync();
                     const uint32_t a_addr = smem_u32(smem + stage * C::STAGE_BYTES);
-                    const uint64_t a_desc = umma_desc_k_sw128(a_addr);
-                    const uint64_t b_desc = umma_desc_k_sw128(a_addr + C::A_BYTES);
                     const uint32_t d_tmem = tmem_base + buf * BN;
-#pragma unroll
-                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-                        const uint32_t accumulate = BLOCK_SCALED ? (k != 0) : (kb != kb_begin || k != 0);
-                        // advancing K by 32 bytes inside the swizzle row: +2 in 16-byte units
-                        umma_f8f6f4(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, accumulate);
-                    }
-                    umma_commit(&empty_bar[stage]);
-                    if (BLOCK_SCALED || kb == kb_end - 1) {
-                        umma_commit(&tmem_full[buf]);
-                        ++acc_iter;
-                    }
+                    uint64_t* this_empty = &empty_bar[stage];
+                    const bool last = BLOCK_SCALED || kb == kb_end - 1;
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1u;
                     }
+                    // Probe the next K block's barriers now; the answers arrive while the MMAs issue.
+                    full_ready = mbar_test_wait(&full_bar[stage], phase);
+                    if (last) {
+                        const uint32_t nxt = acc_iter + 1u;
+                        tmem_ready = mbar_test_wait(&tmem_empty[nxt & 1u], ((nxt >> 1) & 1u) ^ 1u);
+                    }
+                    if (elect_one()) {
+                        if (new_acc) issue_block(a_addr, d_tmem, std::true_type{});
+                        else issue_block(a_addr, d_tmem, std::false_type{});
+                        if constexpr (PAIR) umma_commit_2cta(this_empty, 3); else umma_commit(this_empty);
+                        if (last) {
+                            if constexpr (PAIR) umma_commit_2cta(&tmem_full[buf], 3); else umma_commit(&tmem_full[buf]);
+                        }
+                    }
+                    __syncwarp();
+                    if (last) ++acc_iter;
                 }
             }
         }
@@ -387,7 +449,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         for (int t = tile_first; t < num_tiles && ok; t += tile_step) {
             const TileCoord tc = tile_coord(t, num_m, num_n);
             const int expert = p.grouped ? p.expert_ids[tc.m_blk] : 0;
-            const int m0 = tc.m_blk * a_rows_step;
+            const int m0 = tc.m_blk * a_rows_step + (int)cta_rank * BLOCK_M;
             const int n0 = tc.n_blk * OUT_TILE_N;
             const int64_t row = (int64_t)m0 + r_in_tile;  // row of A (sorted row when grouped)
 
@@ -501,7 +563,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 }
                 tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+                if (lane == 0) {
+                    if constexpr (PAIR) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty[buf]), 0u));
+                    else mbar_arrive(&tmem_empty[buf]);
+                }
                 ++acc_iter;
             } else {
                 // COLS fp32 accumulators per thread, kept as packed pairs for FFMA2.
@@ -549,7 +614,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                         // before the last part is folded.
                         tc_fence_before_sync();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+                        if (lane == 0) {
+                            if constexpr (PAIR) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty[buf]), 0u));
+                            else mbar_arrive(&tmem_empty[buf]);
+                        }
                     };
                     if constexpr (C::COLS >= 64) {
                         // Rounds of 64 columns: one load instruction, one wait, 32 packed FMAs each.
@@ -664,7 +732,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
 
     // ------------------------------- teardown ---------------------------------------------
     tc_fence_before_sync();
-    __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();  // neither CTA leaves while the pair's MMAs may touch it
+    else __syncthreads();
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
@@ -763,6 +832,52 @@ int launch_splitk(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
     return FG_OK;
 }
 
+// CTA-pair kernel: clusters of two, one cluster per 256 x 256 tile, persistent over the tiles.
+// Dense scales only: with block scales the accumulator of every K block has to make the round
+// trip MMA -> both CTAs' epilogues -> MMA through cluster-wide barriers, and that latency costs
+// more than the halved B traffic saves (measured: about half the single-CTA throughput).
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int pair_tiles, cudaStream_t st) {
+    using C = Cfg<256, false, true>;
+    auto kernel = gemm_fp8_kernel<256, false, false, false, false, true>;
+    static int max_clusters = 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(C::THREADS, 1, 1);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (!max_clusters) {
+        FG_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        cfg.gridDim = dim3((unsigned)(2 * (fg_num_sms() / 2)), 1, 1);
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
+            cudaGetLastError();
+            n = 1;
+        }
+        max_clusters = n < fg_num_sms() / 2 ? n : fg_num_sms() / 2;
+    }
+    const int clusters = pair_tiles < max_clusters ? pair_tiles : max_clusters;
+    cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
+    FG_CUDA(cudaLaunchKernelEx(&cfg, kernel, ta, tb, p));
+    fg_count_launch(1);
+    return FG_OK;
+}
+
+// FG_GEMM_PAIR=0 keeps every dense product on the single-CTA kernels (for comparison runs).
+bool pair_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("FG_GEMM_PAIR");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v != 0;
+}
+
 template <int BN, bool BS, bool SILU, bool SMALL_A = false>
 int launch_inst(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int max_tiles, cudaStream_t st) {
     using C = Cfg<BN, SMALL_A>;
@@ -833,6 +948,12 @@ int launch_gemm(GemmParams& p, const void* a, int64_t a_rows, int64_t ld_a, cons
     }
     p.a_box_rows = BLOCK_M;
     if (!p.grouped && p.M < BLOCK_M) p.a_box_rows = (int)((p.M + 7) / 8 * 8);
+    // Large dense products: a pair of CTAs per 256 x 256 tile (a third less L2 and shared-memory
+    // traffic per flop: +4-5 % under the power cap) once there are at least three waves of such
+    // tiles; with fewer, the coarser tiles lose more to the ragged last wave than they gain.
+    const int64_t pair_tiles = fg_cdiv(p.M, 2 * BLOCK_M) * fg_cdiv(p.n_out, 256);
+    const bool pair = !p.grouped && !fuse_silu && !block_scaled && bn == 256 && k_slices == 1 &&
+                      pair_tiles >= 3 * (int64_t)(sms / 2) && pair_tiles < (1ll << 30) && pair_enabled();
     const int out_tile = fuse_silu ? bn / 2 : bn;
     const int64_t tiles = m_tiles * fg_cdiv(p.n_out, out_tile);
     FG_REQUIRE(tiles < (1ll << 31), FG_ERR_UNSUPPORTED, "too many tiles");
@@ -843,8 +964,9 @@ int launch_gemm(GemmParams& p, const void* a, int64_t a_rows, int64_t ld_a, cons
                       (uint32_t)(p.grouped ? p.block_rows : p.a_box_rows), 2);
     if (rc != FG_OK) return rc;
     rc = make_map(&tb, b, (uint64_t)p.K, (uint64_t)p.N, (uint64_t)num_experts, (uint64_t)ld_b,
-                  (uint64_t)ld_b * (uint64_t)p.N, (uint32_t)(fuse_silu ? bn / 2 : bn), 3);
+                  (uint64_t)ld_b * (uint64_t)p.N, (uint32_t)((fuse_silu || pair) ? bn / 2 : bn), 3);
     if (rc != FG_OK) return rc;
+    if (pair) return launch_pair(ta, tb, p, (int)pair_tiles, st);
 
     const int t = (int)tiles;
     if (k_slices > 1) {

@@ -200,6 +200,22 @@ def test_fp8_matmul_and_blockwise_cutlass_form():
     _close(c, ref)
 
 
+@pytest.mark.parametrize("m,n,k", [(4096, 4096, 256), (3900, 4112, 272), (8192, 2304, 144)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_scaled_mm_cta_pair_tiles(m, n, k, out_dtype):
+    """Shapes with at least three waves of 256 x 256 tiles take the two-CTA (cta_group::2)
+    kernel: every row and column, ragged edges and a bias included, against the oracle."""
+    aq, sa, wq, sw, g = _llama_like(m, n, k, seed=11)
+    b = torch.randn(n, generator=g).to(out_dtype)
+    c = torch.full((m, n), float("nan"), dtype=out_dtype, device="cuda")
+    flag_gems.cutlass_scaled_mm(c, aq.cuda(), wq.cuda().t(), sa.cuda().view(-1), sw.cuda(), b.cuda())
+    ref = oracle.scaled_mm(aq, wq.t(), sa, sw, b, out_dtype=out_dtype)
+    pre = oracle.scaled_mm(aq, wq.t(), sa, sw, None, out_dtype=out_dtype).float().abs()
+    err = (c.cpu().float() - ref.float()).abs()
+    assert bool((err <= 1e-2 + 1e-2 * ref.float().abs() + pre * 2.0 ** -7).all()), float(err.max())
+    assert _cabi.device_status() == 0
+
+
 def test_gemm_full_size_linearity():
     """configs[1]/[2] sizes without a CPU oracle pass: doubling every scale doubles the output
     exactly (powers of two commute with every rounding), and a sampled block of rows/columns
