@@ -232,6 +232,20 @@ def dense_extras(peaks):
     ms = time_graph(lambda: flag_gems.moe_align_block_size(ids4, 64, 8), iters=20)
     out["moe_align_us"]["T4096_top2_E8_bs64"] = round(ms * 1e3, 1)
 
+    # router kernels in front of the layer (DeepSeek-V3 routing shape): device time and HBM fraction
+    logits = torch.randn(TOKENS, EXPERTS, device="cuda", generator=g)
+    rbias = torch.randn(EXPERTS, device="cuda", generator=g) * 0.1
+    rw = torch.empty(TOKENS, TOPK, device="cuda")
+    ri = torch.empty(TOKENS, TOPK, dtype=torch.int32, device="cuda")
+    rs = torch.empty(TOKENS, TOPK, dtype=torch.int32, device="cuda")
+    router_bytes = TOKENS * EXPERTS * 4 + TOKENS * TOPK * 12
+    ms = time_graph(lambda: flag_gems.topk_softmax(rw, ri, rs, logits, True), iters=20)
+    out["router_us"] = {"topk_softmax_T8192_E256_top8": round(ms * 1e3, 1),
+                        "topk_softmax_gbs": round(router_bytes / ms / 1e6, 1)}
+    ms = time_graph(lambda: flag_gems.grouped_topk(logits, 8, 4, TOPK, True, 2.5, rbias, 1), iters=20)
+    out["router_us"]["grouped_topk_T8192_E256_g8_tg4_top8_sigmoid"] = round(ms * 1e3, 1)
+    out["router_us"]["grouped_topk_gbs"] = round((router_bytes - TOKENS * TOPK * 4) / ms / 1e6, 1)
+
     # BASELINE configs[3]: Mixtral-8x7B-shaped layer, per-token x per-channel FP8, through fused_experts_impl
     t4, h4, i4, e4 = 4096, 4096, 14336, 8
     w1 = torch.empty(e4, 2 * i4, h4, dtype=FP8, device="cuda")

@@ -71,6 +71,11 @@ _SIGS = {
     "fg_block_scaled_mm_fp8": (
         c_int, [_P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                 c_int64, c_int64, c_int64, c_int, _P]),
+    "fg_topk_softmax": (
+        c_int, [_P, _P, c_int, _P, _P, c_int, c_int64, c_int, c_int, c_int, _P, _P]),
+    "fg_grouped_topk": (
+        c_int, [_P, _P, _P, _P, c_int, c_int64, c_int, c_int64, c_int, c_int, c_int, c_int, ctypes.c_float, c_int,
+                _P, _P]),
     "fg_moe_grouped_gemm_fp8": (
         c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int64, _P, _P, _P, c_int64, c_int64, c_int, c_int64, c_int64,
                 c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P]),

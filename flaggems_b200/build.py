@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libflaggems_b200.so")
-SOURCES = ["api.cu", "quant.cu", "moe_glue.cu", "moe_layer.cu", "gemm_fp8_sm100.cu"]
+SOURCES = ["api.cu", "quant.cu", "moe_glue.cu", "moe_layer.cu", "router.cu", "gemm_fp8_sm100.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -20,6 +20,12 @@ _VLLM_OPS_SIGNATURES = {
         "int block_size, Tensor(a!) sorted_token_ids, Tensor(b!) experts_ids, "
         "Tensor(c!) num_tokens_post_pad) -> ()",
         "moe_sum": "(Tensor input, Tensor(a!) output) -> ()",
+        "topk_softmax": "(Tensor(a!) topk_weights, Tensor(b!) topk_indices, "
+        "Tensor(c!) token_expert_indices, Tensor gating_output, bool renormalize=False, "
+        "Tensor? e_score_correction_bias=None) -> ()",
+        "grouped_topk": "(Tensor gating_output, int n_group, int topk_group, "
+        "int topk, bool renormalize, float routed_scaling_factor, Tensor? bias, "
+        "int scoring_func=0) -> (Tensor, Tensor)",
     },
 }
 
@@ -75,6 +81,26 @@ def custom_moe_sum(input, output):
     moe_sum(input, output)
 
 
+def custom_topk_softmax(topk_weights, topk_indices, token_expert_indices, gating_output, renormalize=False,
+                        e_score_correction_bias=None):
+    from ..fused.topk_softmax import topk_softmax
+
+    if e_score_correction_bias is not None:
+        # newer vLLM schemas carry this argument; the reference's topk_softmax has no such input
+        raise NotImplementedError("topk_softmax with e_score_correction_bias is not implemented")
+
+    topk_softmax(topk_weights, topk_indices, token_expert_indices, gating_output, renormalize)
+
+
+def custom_moe_grouped_topk(gating_output, n_group, topk_group, topk, renormalize, routed_scaling_factor, bias,
+                            scoring_func=0):
+    from ..fused.grouped_topk import grouped_topk
+
+    return grouped_topk(scores=gating_output, n_group=n_group, topk_group=topk_group, topk=topk,
+                        renormalize=renormalize, routed_scaling_factor=routed_scaling_factor, bias=bias,
+                        scoring_func=scoring_func)
+
+
 _VLLM_OPS_IMPLS = {
     "_C": {
         "cutlass_scaled_mm": custom_cutlass_scaled_mm,
@@ -83,6 +109,8 @@ _VLLM_OPS_IMPLS = {
     "_moe_C": {
         "moe_align_block_size": custom_moe_align_block_size,
         "moe_sum": custom_moe_sum,
+        "topk_softmax": custom_topk_softmax,
+        "grouped_topk": custom_moe_grouped_topk,
     },
 }
 

@@ -130,6 +130,31 @@ int fg_moe_align_block_size_ex(const void* topk_ids, int ids_are_i64, int64_t nu
 int fg_silu_and_mul(const void* x, const void* y, void* out, int64_t M, int64_t N, int64_t ld_x,
                     int64_t ld_y, int64_t ld_out, int dtype, void* stream);
 
+/* topk_softmax: src/flag_gems/fused/topk_softmax.py:84-137 (kernel :24-81); vLLM op
+ * _moe_C::topk_softmax.  gating_output [T, E] (bf16/fp16/fp32, contiguous), softmax in fp32 with
+ * 1e-8 added to the denominator, then topk rounds of arg-max (ties to the lower expert index).
+ * topk_weights fp32 [T, topk]; topk_indices [T, topk] with index_kind 0 int32, 1 uint32, 2 int64;
+ * token_expert_indices[t, k] = k * T + t.  renormalize divides by (sum of the topk + 1e-8).
+ * topk <= 32 (assert of :94), E <= 1024 (block size cap of :107).  expert_counts: NULL, or
+ * int32 [E] to which the number of route slots per expert is added (not in the reference: the
+ * histogram an expert-parallel dispatch starts from). */
+int fg_topk_softmax(float* topk_weights, void* topk_indices, int index_kind, int32_t* token_expert_indices,
+                    const void* gating_output, int gating_dtype, int64_t num_tokens, int num_experts, int topk,
+                    int renormalize, int32_t* expert_counts, void* stream);
+
+/* grouped_topk: src/flag_gems/fused/grouped_topk.py:245-355 (kernels :24-243); vLLM op
+ * _moe_C::grouped_topk.  scores [T, E] with row stride scores_stride, bias [E], both `dtype`.
+ * scoring_func 1 applies sigmoid in fp32 and rounds to dtype (:291-294); group score = sum of
+ * the two largest (score + bias) of the group (:24-76); the topk_group best groups, then topk
+ * rounds of arg-max over (score + bias) inside them, ties to the lower index; weights are the
+ * scores without bias times routed_scaling_factor, divided by (their sum + 1e-20) when
+ * renormalize.  n_group <= 32, topk <= 32 (:262-265).  topk_values fp32, topk_indices int32,
+ * both [T, topk].  expert_counts as in fg_topk_softmax. */
+int fg_grouped_topk(float* topk_values, int32_t* topk_indices, const void* scores, const void* bias, int dtype,
+                    int64_t num_tokens, int num_experts, int64_t scores_stride, int n_group, int topk_group, int topk,
+                    int renormalize, float routed_scaling_factor, int scoring_func, int32_t* expert_counts,
+                    void* stream);
+
 /* moe_sum: src/flag_gems/fused/moe_sum.py:70-90 (kernel :24-67).
  * in [M, topk, K] contiguous, out [M, K]; fp32 sum in slot order. */
 int fg_moe_sum(const void* in, void* out, int64_t M, int topk, int64_t K, int dtype, void* stream);

@@ -15,7 +15,9 @@ functions (loaded from the reference's test files, see
 Parity status: pinned for act_quant, per_token_group_quant_fp8,
 moe_align_block_size, the block-scaled matmul and the block-fp8 fused MoE.  The
 per-token x per-channel FP8 fused MoE has no test in the reference at all
-("parity unpinned"): its oracle is restated from the kernel source only.
+("parity unpinned"): its oracle is restated from the kernel source only.  The router functions
+(topk_softmax, grouped_topk) are likewise unpinned by goldens: the reference tests them only against
+vLLM's CUDA ops at run time, which the GPU tests here repeat when those ops load.
 """
 from .quant import (  # noqa: F401
     act_quant,
@@ -26,6 +28,7 @@ from .quant import (  # noqa: F401
     quantize_weight_block,
 )
 from .gemm import scaled_mm, block_scaled_mm  # noqa: F401
+from .router import topk_softmax, grouped_topk  # noqa: F401
 from .moe import (  # noqa: F401
     moe_align_block_size,
     silu_and_mul,
