@@ -317,7 +317,8 @@ class ExpertParallelMoE:
         return both[0].tolist(), both[1].tolist()
 
     # -- forward ---------------------------------------------------------------------------
-    def forward(self, hidden: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
+    def forward(self, hidden: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
+                _buf: Optional[int] = None) -> torch.Tensor:
         assert hidden.dim() == 2 and hidden.is_contiguous()
         assert topk_weights.shape == topk_ids.shape and topk_ids.shape[0] == hidden.shape[0]
         tokens, topk = topk_ids.shape
@@ -351,8 +352,11 @@ class ExpertParallelMoE:
                        and tokens * topk <= self._symm_rows)
             if use_p2p and self._recv is not None and self.world * tokens * topk <= self._recv_rows:
                 # Device-driven step: no host wait, no NCCL payload traffic.
-                buf = self._step & 1
-                self._step += 1
+                if _buf is None:
+                    buf = self._step & 1
+                    self._step += 1
+                else:
+                    buf = _buf
                 order, counts_dev = ops.route(topk_ids, self.world)
                 dist.all_gather_into_tensor(self._counts_matrix, counts_dev.contiguous(), group=self.group)
                 self._mark("route+counts", dev)
@@ -405,3 +409,60 @@ class ExpertParallelMoE:
         return out
 
     __call__ = forward
+
+    # -- CUDA-graph replay -------------------------------------------------------------------
+    def capture(self, hidden: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> None:
+        """Record the whole step (every kernel of this rank, the side-stream fork for the shared
+        expert and, with several ranks, the stream-ordered count exchange and barriers) into CUDA
+        graphs, so that a step costs the host one launch whatever the host is busy with.
+
+        The three tensors become the step's static inputs: write new values into them (``copy_``)
+        and call :meth:`replay`.  With several ranks two graphs are recorded, one per half of the
+        double-buffered peer buffers, and replayed alternately; every rank must call ``capture``
+        and ``replay`` the same number of times, and :meth:`release_graphs` before the process
+        group is destroyed.  Only the device-driven step can be recorded (the
+        all-to-all variant waits on the host for its counts)."""
+        assert hidden.is_cuda, "graphs are a CUDA feature"
+        dev = hidden.device
+        if self.world > 1:
+            tokens, topk = topk_ids.shape
+            assert (self._symm is not None and self._recv is not None and tokens * topk <= self._symm_rows
+                    and self.world * tokens * topk <= self._recv_rows), \
+                "only the peer-memory (device-driven) step can be recorded"
+        n_graphs = 2 if self.world > 1 else 1
+        self.trace = None
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):  # warm up off the default stream: lazy initialisation, allocator pools
+            for i in range(2 * n_graphs):
+                self.forward(hidden, topk_weights, topk_ids, _buf=i % n_graphs)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        self._graphs, self._graph_out = [], []
+        launches0 = _cabi.launch_count()
+        for i in range(n_graphs):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                out = self.forward(hidden, topk_weights, topk_ids, _buf=i)
+            self._graphs.append(g)
+            self._graph_out.append(out)
+        self.kernels_per_replay = (_cabi.launch_count() - launches0) // n_graphs
+        self._graph_inputs = (hidden, topk_weights, topk_ids)
+        self._replays = 0
+
+    def release_graphs(self) -> None:
+        """Destroy the recorded graphs.  With several ranks this must happen before the process
+        group is destroyed: the graphs hold NCCL kernels, and NCCL does not let go of a communicator
+        while a graph that uses it exists (seen as both ranks sitting in ``destroy_process_group``)."""
+        if getattr(self, "_graphs", None):
+            torch.cuda.synchronize()
+            self._graphs, self._graph_out, self._graph_inputs = [], [], None
+            torch.cuda.synchronize()
+
+    def replay(self) -> torch.Tensor:
+        """One step from the recorded graph; returns the graph's static output tensor (overwritten by
+        the next replay of the same graph)."""
+        i = self._replays % len(self._graphs)
+        self._replays += 1
+        self._graphs[i].replay()
+        return self._graph_out[i]

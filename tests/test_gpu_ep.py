@@ -34,6 +34,32 @@ def test_single_gpu_layer_matches_oracle():
     torch.testing.assert_close(out.cpu().float(), ref, rtol=1e-2, atol=max(1e-2, 1e-2 * float(ref.abs().max())))
 
 
+def test_single_gpu_graph_replay_equals_eager():
+    """The step recorded into a CUDA graph gives the eager step's bits, also after new inputs have
+    been written into the static input tensors."""
+    from flaggems_b200 import _cabi
+    from flaggems_b200.ep import ExpertParallelMoE
+
+    dev = torch.device("cuda", 0)
+    case = make_case(seed=7, t=96, h=512, i=256, e=16, topk=4)
+    hidden, w1, w2, s1, s2, tw, ti, shared = case
+    layer = ExpertParallelMoE(w1.to(dev), w2.to(dev), s1.to(dev), s2.to(dev), w1.shape[0],
+                              shared=tuple(t.to(dev) for t in shared))
+    h, w, i = hidden.to(dev), tw.to(dev), ti.to(dev)
+    eager = layer(h, w, i).clone()
+    layer.capture(h, w, i)
+    assert layer.kernels_per_replay > 0
+    assert torch.equal(layer.replay(), eager)
+    assert torch.equal(layer.replay(), eager)
+    case2 = make_case(seed=8, t=96, h=512, i=256, e=16, topk=4)
+    h.copy_(case2[0].to(dev))
+    w.copy_(case2[5].to(dev))
+    i.copy_(case2[6].to(dev))
+    replayed = layer.replay().clone()
+    assert torch.equal(replayed, layer(h, w, i))
+    assert _cabi.device_status() == 0
+
+
 def _worker(rank, world, port, q):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
