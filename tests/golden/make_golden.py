@@ -1,9 +1,9 @@
 """Regenerate tests/golden/*.pt from the reference's own golden functions.
 
-Run in a container that has the reference checkout (default /root/reference,
-override with FLAGGEMS_REFERENCE):
+Run where a checkout of the reference (FlagGems) is at hand and point
+FLAGGEMS_REFERENCE at its root:
 
-    python tests/golden/make_golden.py
+    FLAGGEMS_REFERENCE=<path to the FlagGems checkout> python tests/golden/make_golden.py
 
 The reference package cannot be imported without an accelerator, so the pure
 torch golden functions are lifted out of the reference's files by name (their
@@ -20,7 +20,9 @@ from typing import Optional, Tuple  # noqa: F401  (names used by lifted code)
 
 import torch
 
-REF = os.environ.get("FLAGGEMS_REFERENCE", "/root/reference")
+REF = os.environ.get("FLAGGEMS_REFERENCE")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("set FLAGGEMS_REFERENCE to the root of a FlagGems checkout")
 OUT = os.path.dirname(os.path.abspath(__file__))
 
 

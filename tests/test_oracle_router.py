@@ -79,3 +79,34 @@ def test_grouped_topk_oracle_edge_cases():
         oracle.grouped_topk(torch.zeros(1, 8), 2, 1, 1, False, 1.0, torch.zeros(4))
     with pytest.raises(ValueError, match="scoring_func"):
         oracle.grouped_topk(torch.zeros(1, 8), 2, 1, 1, False, 1.0, torch.zeros(8), 2)
+
+
+def test_router_host_api_checks_arguments_before_touching_a_device():
+    """The host wrappers keep the reference's argument checks and error classes, and refuse CPU
+    tensors instead of falling back."""
+    import flag_gems
+
+    with pytest.raises(ValueError, match="2D"):
+        flag_gems.grouped_topk(torch.zeros(8), 2, 1, 1, False, 1.0, torch.zeros(8))
+    with pytest.raises(ValueError, match="divisible"):
+        flag_gems.grouped_topk(torch.zeros(1, 9), 2, 1, 1, False, 1.0, torch.zeros(9))
+    with pytest.raises(ValueError, match="n_group"):
+        flag_gems.grouped_topk(torch.zeros(1, 64), 64, 1, 1, False, 1.0, torch.zeros(64))
+    with pytest.raises(ValueError, match="topk should be"):
+        flag_gems.grouped_topk(torch.zeros(1, 64), 2, 1, 33, False, 1.0, torch.zeros(64))
+    with pytest.raises(ValueError, match="scoring_func"):
+        flag_gems.grouped_topk(torch.zeros(1, 8), 2, 1, 1, False, 1.0, torch.zeros(8), 3)
+    with pytest.raises(ValueError, match="bias length"):
+        flag_gems.grouped_topk(torch.zeros(1, 8), 2, 1, 1, False, 1.0, torch.zeros(4))
+    with pytest.raises(ValueError, match="Unsupported dtype"):
+        flag_gems.grouped_topk(torch.zeros(1, 8, dtype=torch.float64), 2, 1, 1, False, 1.0, torch.zeros(8))
+    with pytest.raises(Exception, match="(?i)cuda"):
+        flag_gems.grouped_topk(torch.zeros(1, 8), 2, 1, 1, False, 1.0, torch.zeros(8))
+    w, i, s = torch.empty(2, 2), torch.empty(2, 2, dtype=torch.int16), torch.empty(2, 2, dtype=torch.int32)
+    with pytest.raises(TypeError):
+        flag_gems.topk_softmax(w, i, s, torch.zeros(2, 8))
+    with pytest.raises(AssertionError):
+        flag_gems.topk_softmax(torch.empty(2, 33), torch.empty(2, 33, dtype=torch.int32),
+                               torch.empty(2, 33, dtype=torch.int32), torch.zeros(2, 64))
+    with pytest.raises(Exception, match="(?i)cuda"):
+        flag_gems.topk_softmax(w, i.int(), s, torch.zeros(2, 8))
