@@ -148,8 +148,10 @@ int fg_topk_softmax(float* topk_weights, void* topk_indices, int index_kind, int
  * the two largest (score + bias) of the group (:24-76); the topk_group best groups, then topk
  * rounds of arg-max over (score + bias) inside them, ties to the lower index; weights are the
  * scores without bias times routed_scaling_factor, divided by (their sum + 1e-20) when
- * renormalize.  n_group <= 32, topk <= 32 (:262-265).  topk_values fp32, topk_indices int32,
- * both [T, topk].  expert_counts as in fg_topk_softmax. */
+ * renormalize.  n_group <= 32, topk <= 32 (:262-265); num_experts <= 2048 (one row of scores per warp
+ * in shared memory).  A token whose groups all score -inf gets weights 1/topk and experts 0..topk-1
+ * (:221-227).  topk_values fp32, topk_indices int32, both [T, topk].  expert_counts as in
+ * fg_topk_softmax. */
 int fg_grouped_topk(float* topk_values, int32_t* topk_indices, const void* scores, const void* bias, int dtype,
                     int64_t num_tokens, int num_experts, int64_t scores_stride, int n_group, int topk_group, int topk,
                     int renormalize, float routed_scaling_factor, int scoring_func, int32_t* expert_counts,
