@@ -18,8 +18,15 @@ result inside the timed region.  Inputs are synthetic (seeded), weights random-i
 quantised as the configuration describes.  Weights (1.4-11.3 GB per rank) exceed the 126 MB
 L2, so no explicit L2 flush is needed between iterations.
 
+Every rank runs the same number of steps and collectives: the schedule (warm-up, passes of K
+timed steps, end-to-end passes, a fixed tail of steps for the clock sampler) is a function of the
+command line only (`step_schedule`), never of what a rank measures.  The reported time is the
+median of the passes; every pass is in the JSON line.
+
 --impl reference times the CPU restatement of the reference's algorithm (oracle/) on the host
-cores for the same metric on a bounded sample of the same workload.
+cores for the same metric on a bounded sample of the same workload: a few experts with ALL the
+rows the T=8192 router sends them (so that dequantising an expert's weights is amortised over its
+rows as in the full step), scaled to tokens by the rows processed.
 """
 import argparse
 import json
@@ -202,29 +209,33 @@ def dense_extras(peaks):
         sw = w.abs().amax(1).clamp_min(1e-10) / 448.0
         wq = (w / sw[:, None]).clamp(-448, 448).to(FP8)
         del w
-        for m in (128, 1024, 4096, 8192):
+        for m in (1, 16, 128, 1024, 4096, 8192):
             a = torch.randn(m, k, device="cuda", generator=g).bfloat16()
             aq, sa = flag_gems.fused.fused_moe._fp8_quantize(a, None, True, None)
             c = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
             ms = time_graph(lambda: flag_gems.cutlass_scaled_mm(c, aq, wq.t(), sa.view(-1), sw))
             tf = 2.0 * m * n * k / ms / 1e9
+            by = m * k + n * k + 2 * m * n + 4 * (m + n)
             out["scaled_mm_tflops"][f"{name}_M{m}_N{n}_K{k}"] = {
                 "tflops": round(tf, 1), "us": round(ms * 1e3, 1), "frac_of_2x_measured_bf16": round(tf / fp8_peak, 3),
-                "frac_of_nominal_4500": round(tf / 4500.0, 3)}
+                "frac_of_nominal_4500": round(tf / 4500.0, 3),
+                "frac_of_measured_hbm": round(by / ms / 1e6 / peaks["hbm_gbs"], 3)}
     k = 7168
     for n in (2112, 4096, 18432, 24576):
         w = torch.randn((n + 127) // 128 * 128, k, device="cuda", generator=g) * 0.02
         wq, ws = block_quant_weight_gpu(w)
         wq = wq[:n].contiguous()
         del w
-        for m in (512, 4096, 16384):
+        for m in (1, 64, 512, 4096, 16384):
             a = torch.randn(m, k, device="cuda", generator=g).bfloat16()
             aq, a_s = flag_gems.per_token_group_quant_fp8(a, 128)
             ms = time_graph(lambda: flag_gems.w8a8_block_fp8_matmul(aq, wq, a_s, ws, [128, 128]), iters=5)
             tf = 2.0 * m * n * k / ms / 1e9
+            by = m * k + n * k + 2 * m * n + 4 * m * (k // 128) + 4 * ((n + 127) // 128) * (k // 128)
             out["block_scaled_mm_tflops"][f"M{m}_N{n}_K{k}"] = {
                 "tflops": round(tf, 1), "us": round(ms * 1e3, 1), "frac_of_2x_measured_bf16": round(tf / fp8_peak, 3),
-                "frac_of_nominal_4500": round(tf / 4500.0, 3)}
+                "frac_of_nominal_4500": round(tf / 4500.0, 3),
+                "frac_of_measured_hbm": round(by / ms / 1e6 / peaks["hbm_gbs"], 3)}
     ids = make_router(TOKENS, EXPERTS, TOPK)[1].cuda()
     ms = time_graph(lambda: flag_gems.moe_align_block_size(ids, 64, EXPERTS), iters=20)
     out["moe_align_us"] = {"T8192_top8_E256_bs64": round(ms * 1e3, 1)}
@@ -296,25 +307,44 @@ def dense_extras(peaks):
 # ---------------------------------------------------------------------------------------------
 # CPU arm (oracle)
 # ---------------------------------------------------------------------------------------------
-def cpu_layer_sample(hidden, tw, ti, fetch_expert, shared):
-    """The oracle's layer on a few tokens.  fetch_expert(e) -> (w1, w2, s1, s2) CPU tensors."""
+def cpu_expert_sample(experts, rows_of, fetch_expert, shared, hidden_of):
+    """The oracle's layer restricted to `experts`, each with ALL the rows routed to it, plus the
+    shared expert on as many tokens as those rows amount to (rows / top-k).
+    rows_of(e) -> (token indices, router weights); fetch_expert(e) -> (w1, w2, s1, s2) CPU tensors;
+    hidden_of(tokens) -> [n, H] bf16.  Returns ({e: rows' results}, seconds, rows processed)."""
     import oracle
 
-    experts = sorted(set(ti.reshape(-1).tolist()))
-    remap = {e: i for i, e in enumerate(experts)}
-    ws = [fetch_expert(e) for e in experts]
-    w1 = torch.stack([w[0] for w in ws])
-    w2 = torch.stack([w[1] for w in ws])
-    s1 = torch.stack([w[2] for w in ws])
-    s2 = torch.stack([w[3] for w in ws])
-    ti2 = ti.clone().apply_(lambda e: remap[e])
+    results, n_rows, dt = {}, 0, 0.0
+    for e in experts:
+        tok, wts = rows_of(e)
+        if tok.numel() == 0:
+            continue
+        w = fetch_expert(e)
+        x = hidden_of(tok)
+        t0 = time.perf_counter()
+        results[e] = oracle.expert_rows_block_fp8(x, *w, wts)
+        dt += time.perf_counter() - t0
+        n_rows += tok.numel()
+    n_tok = max(1, n_rows // TOPK)
+    x = hidden_of(torch.arange(n_tok))
     t0 = time.perf_counter()
-    add = oracle.dense_block_fp8_mlp(hidden, *shared)
-    out = oracle.fused_moe_block_fp8(hidden, w1, w2, s1, s2, tw, ti2, addend=add)
-    return out, time.perf_counter() - t0
+    oracle.dense_block_fp8_mlp(x, *shared)
+    dt += time.perf_counter() - t0
+    return results, dt, n_rows
 
 
-def cpu_weight_pool(pool=8, seed=0):
+def sample_experts(ti, n=4):
+    """A fixed, routing-derived choice of experts for the CPU legs: the busiest expert, the one with
+    the fewest (non-zero) rows, and n - 2 around the median, by routed-row count."""
+    counts = torch.bincount(ti.reshape(-1), minlength=EXPERTS)
+    order = torch.argsort(counts, descending=True, stable=True).tolist()
+    order = [e for e in order if counts[e] > 0]
+    mid = len(order) // 2
+    picks = [order[0], order[-1]] + order[mid:mid + max(0, n - 2)]
+    return sorted(set(picks)), counts
+
+
+def cpu_weight_pool(pool=4, seed=0):
     import oracle
 
     g = torch.Generator().manual_seed(seed)
@@ -327,27 +357,40 @@ def cpu_weight_pool(pool=8, seed=0):
 
 
 def run_reference(args):
-    """CPU arm: oracle on all host threads, one bounded sample of tokens per step."""
+    """CPU arm: the oracle on all host threads; each step = two experts with all their routed rows."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     torch.set_num_threads(os.cpu_count() or 1)
-    sample = args.cpu_tokens
     pool = cpu_weight_pool()
     shared = pool[0]
     tw, ti = make_router(TOKENS, EXPERTS, TOPK)
+    counts = torch.bincount(ti.reshape(-1), minlength=EXPERTS)
+    order = torch.argsort(counts, descending=True, stable=True).tolist()
+    mid = len(order) // 2  # experts around the median load: ~T*topk/E rows each
     g = torch.Generator().manual_seed(1)
-    times = []
+    hidden = torch.randn(TOKENS, HIDDEN, generator=g).bfloat16()
+
+    def rows_of(e):
+        tok, slot = torch.nonzero(ti == e, as_tuple=True)
+        return tok, tw[tok, slot]
+
+    times, rows_done = [], []
     for step in range(args.warmup + args.steps):
-        lo = (step * sample) % (TOKENS - sample)
-        hidden = torch.randn(sample, HIDDEN, generator=g).bfloat16()
-        _, dt = cpu_layer_sample(hidden, tw[lo:lo + sample], ti[lo:lo + sample], lambda e: pool[e % len(pool)], shared)
+        experts = [order[(mid + 2 * step) % len(order)], order[(mid + 2 * step + 1) % len(order)]]
+        _, dt, n_rows = cpu_expert_sample(experts, rows_of, lambda e: pool[e % len(pool)], shared,
+                                          lambda tok: hidden[tok])
         if step >= args.warmup:
             times.append(dt)
-    ms = 1e3 * sum(times) / len(times)
-    value = sample / (ms / 1e3)
-    desc = (f"{sample} tokens per step of the T={TOKENS} workload (router, shapes and top-{TOPK} as configured; "
-            f"expert weights drawn from a pool of {len(pool)} generated weight sets), oracle/ torch-CPU fp32")
+            rows_done.append(n_rows)
+    tokens_equiv = sum(rows_done) / TOPK
+    total = sum(times)
+    value = tokens_equiv / total
+    ms = 1e3 * total / len(times)
+    desc = (f"per step two experts of median load with ALL rows the T={TOKENS} router sends them "
+            f"({sum(rows_done) / len(rows_done):.0f} rows per step on average) plus the shared expert on rows/top-{TOPK} "
+            f"tokens; tokens = rows / {TOPK}; expert weights from a pool of {len(pool)} generated sets; "
+            f"oracle/ torch-CPU fp32")
     line = {
         "impl": "reference", "metric": "fused_moe_tokens_per_s", "value": round(value, 3), "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 3),
@@ -372,12 +415,30 @@ def workload_config(n):
 # ---------------------------------------------------------------------------------------------
 # main arm
 # ---------------------------------------------------------------------------------------------
+CLOCK_TAIL_STEPS = 200  # resident steps after the timed passes, so the clock sampler sees load
+
+
+def step_schedule(args):
+    """What every rank runs, in order, as (phase, number of steps).  A function of the command
+    line only: ranks must issue identical sequences of collectives, so nothing a rank observes
+    (time, clock samples, its own load) may change how many steps it runs."""
+    warm = max(args.warmup, 3)
+    sched = [("warmup", warm)]
+    sched += [("timed", args.steps)] * args.passes
+    sched += [("e2e_warmup", 2)]
+    sched += [("e2e", args.steps)] * args.passes
+    sched += [("clock_tail", CLOCK_TAIL_STEPS), ("phase_trace", 1)]
+    return sched
+
+
 def run_ours(args):
+    import datetime
+
     import torch.distributed as dist
 
     import flag_gems  # noqa: F401
     from flaggems_b200 import _cabi
-    from flaggems_b200.ep import ExpertParallelMoE
+    from flaggems_b200.ep import ExpertParallelMoE, balanced_expert_placement
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -389,20 +450,31 @@ def run_ours(args):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        # a short timeout: ranks whose collectives stop matching give up within a minute
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=60))
     assert world == args.gpus or world == 1, f"WORLD_SIZE {world} != --gpus {args.gpus}"
-    peaks = load_peaks()
+    layer = None
+    try:
+        layer = _run_ours(args, world, rank, local_rank, dev, dist, _cabi, ExpertParallelMoE,
+                          balanced_expert_placement)
+    finally:
+        # ordered teardown: graphs, device idle, barrier, peer mappings, buffers; then the group
+        if layer is not None:
+            layer.close()
+        if world > 1:
+            dist.destroy_process_group()
 
+
+def _run_ours(args, world, rank, local_rank, dev, dist, _cabi, ExpertParallelMoE, balanced_expert_placement):
+    peaks = load_peaks()
     e_loc, t_loc = EXPERTS // world, TOKENS // world
     w1, w2, s1, s2 = make_expert_weights(e_loc, rank * e_loc, dev)
     shared = make_shared_weights(dev)
-    layer = ExpertParallelMoE(w1, w2, s1, s2, EXPERTS, rank, world, shared=shared,
-                              p2p_combine_rows=0 if args.a2a_combine else t_loc * TOPK,
-                              p2p_dispatch_rows=0 if (args.a2a_combine or args.a2a_dispatch) else TOKENS * TOPK)
+    transport = "a2a" if args.a2a_combine else ("p2p_combine" if args.a2a_dispatch else "p2p")
+    layer = ExpertParallelMoE(w1, w2, s1, s2, EXPERTS, rank, world, shared=shared, transport=transport,
+                              max_slots_per_rank=t_loc * TOPK)
     tw_all, ti_all = make_router(TOKENS, EXPERTS, TOPK)
     # logical expert -> physical slot (rank * E_loc + local index); identical on every rank
-    from flaggems_b200.ep import balanced_expert_placement
-
     placement = balanced_expert_placement(torch.bincount(ti_all.reshape(-1), minlength=EXPERTS), world)
     ti_all = placement[ti_all]
     rows_per_rank = torch.bincount((ti_all // e_loc).reshape(-1), minlength=world)
@@ -413,13 +485,11 @@ def run_ours(args):
     out_h = torch.empty(t_loc, HIDDEN, dtype=torch.bfloat16).pin_memory()
     hidden_d, tw_d, ti_d = hidden_h.to(dev), tw_h.to(dev), ti_h.to(dev)
 
-    # One rank: the step is replayed from a CUDA graph.  Several ranks: eager by default; --graph
-    # records the step there too (its graphs hold NCCL kernels and have to be released before the
-    # process group goes away, which release_graphs() below does).
-    use_graph = (not (args.no_graph or args.a2a_combine or args.a2a_dispatch)) and (world == 1 or args.graph)
+    # The step is recorded once into a CUDA graph and replayed (same kernels, collectives and
+    # streams as the eager call, one host launch per step) unless an all-to-all transport, which
+    # waits on the host for its counts, or --no-graph is chosen.
+    use_graph = (not args.no_graph) and (world == 1 or transport == "p2p")
     if use_graph:
-        # The step is recorded once into CUDA graphs and replayed: the same kernels, collectives and
-        # streams as the eager call, one host launch per step.
         layer.capture(hidden_d, tw_d, ti_d)
 
         def step_resident():
@@ -498,32 +568,44 @@ def run_ours(args):
             ms = float(t.item())
         return ms
 
-    # Clocks are sampled from the first warm-up step to the last end-to-end step: the same
-    # workload throughout, and long enough for nvidia-smi to report even when the timed region
-    # itself lasts only tens of milliseconds.
+    # Clocks are sampled from the first warm-up step to the end of the schedule: the same
+    # workload throughout, long enough for nvidia-smi to report whatever the step time is.
+    ms_passes, e2e_passes, marks = [], [], []
+    launches0 = launches = 0
     with ClockSampler(local_rank) as clocks:
-        for _ in range(max(args.warmup, 3)):
-            step_resident()
-        launches0 = _cabi.launch_count()
-        # K steps are timed twice and the faster pass is reported: a host hiccup on a shared box
-        # (launches are issued from Python) otherwise lands in a 10-step window undiluted.
-        ms_passes = [timed(step_resident, args.steps) for _ in range(args.passes)]
-        ms = min(ms_passes)
-        launches = (_cabi.launch_count() - launches0) // args.passes
-        if use_graph:
-            launches = layer.kernels_per_replay * args.steps
-        for _ in range(2):
-            step_e2e()
-        if use_graph:
-            extra_streams.extend([st_h2d, st_d2h])
-        e2e_passes = [timed(step_e2e, args.steps) for _ in range(args.passes)]
-        del extra_streams[:]
-        ms_e2e = min(e2e_passes)
-        t_end = time.time() + 0.3
-        while clocks.rows.__len__() < 3 and time.time() < t_end:  # let a few samples land under load
-            step_resident()
+        for phase, n in step_schedule(args):
+            if phase in ("warmup", "clock_tail"):
+                for _ in range(n):
+                    step_resident()
+                if phase == "warmup":
+                    launches0 = _cabi.launch_count()
+            elif phase == "timed":
+                ms_passes.append(timed(step_resident, n))
+                launches = _cabi.launch_count() - launches0
+            elif phase == "e2e_warmup":
+                for _ in range(n):
+                    step_e2e()
+                if use_graph:
+                    extra_streams.extend([st_h2d, st_d2h])
+            elif phase == "e2e":
+                e2e_passes.append(timed(step_e2e, n))
+            elif phase == "phase_trace":
+                del extra_streams[:]
+                barrier()
+                # phase breakdown of one eager step on this rank (CUDA events on the layer's stream)
+                layer.trace = []
+                layer(hidden_d, tw_d, ti_d)
+                torch.cuda.synchronize()
+                marks, layer.trace = layer.trace, None
         torch.cuda.synchronize()
+    ms = statistics.median(ms_passes)
+    ms_e2e = statistics.median(e2e_passes)
+    launches = launches // args.passes
+    if use_graph:
+        launches = layer.kernels_per_replay * args.steps
+    phases = {marks[i][0]: round(marks[i - 1][1].elapsed_time(marks[i][1]), 4) for i in range(1, len(marks))}
     status = _cabi.device_status()
+    barrier()  # from here on no rank issues a collective until close()
 
     # dominant kernel: the grouped GEMM1 (block-scaled, fused SiLU) on this rank's routed rows,
     # timed alone on the launching stream with CUDA events.
@@ -562,16 +644,9 @@ def run_ours(args):
                 "traffic": round(1.2031e9 * e_loc / 32),
                 "hbm_gbs_at_that_traffic": round(1.2031e9 * e_loc / 32 / gemm1_ms / 1e6, 1),
                 "peak_source": f"2 x {peaks['source']} sustained dense bf16 cuBLAS TF/s (fp8 tensor rate is twice bf16)",
+                "frac_of_2x_measured_bf16_burst": round(achieved / (2.0 * peaks["bf16_tflops"]), 4),
                 "frac_of_nominal_4500": round(achieved / 4500.0, 4), "launch_ms": round(gemm1_ms, 4),
                 "algorithmic_flops_per_launch": gemm1_flops, "rows": n_rows}
-
-    # phase breakdown of one step on this rank (CUDA events on the layer's stream)
-    layer.trace = []
-    step_resident()
-    torch.cuda.synchronize()
-    marks = layer.trace
-    layer.trace = None
-    phases = {marks[i][0]: round(marks[i - 1][1].elapsed_time(marks[i][1]), 4) for i in range(1, len(marks))}
 
     value = TOKENS / (ms / 1e3)
     e2e_value = TOKENS / (ms_e2e / 1e3)
@@ -588,68 +663,109 @@ def run_ours(args):
                            "streams (double-buffered)" if use_graph else "pinned host buffers, serial with the kernels")},
         "gpu_launches": int(launches), "roofline": roofline, "device_status": status,
         "launch_mode": "CUDA graph replay (step recorded once)" if use_graph else "eager",
-        "timing": {"passes_of_k_steps": args.passes, "reported": "faster pass",
+        "timing": {"passes_of_k_steps": args.passes, "reported": "median pass",
                    "ms_per_step_passes": [round(x, 4) for x in ms_passes],
                    "e2e_ms_per_step_passes": [round(x, 4) for x in e2e_passes]},
-        "phase_ms_rank0": phases,
+        "phase_ms_rank0_eager_step": phases,
         "dispatch": ("n/a (single rank)" if world == 1 else
-                     "NCCL all_to_all_single" if (args.a2a_combine or args.a2a_dispatch) else
-                     "fused into the quantisation kernel: packed rows stored to the destination rank over NVLink "
-                     "peer memory, counts by a stream-ordered all-gather (no host wait in the step)"),
+                     "NCCL all_to_all_single" if transport != "p2p" else
+                     "fused into the quantisation kernel: packed rows stored into this rank's region of the "
+                     "destination's receive buffer over NVLink peer memory; counts by a stream-ordered all-gather "
+                     "that doubles as the arrival barrier (no host wait in the step)"),
         "combine": ("n/a (single rank)" if world == 1 else
-                    "NCCL all_to_all_single" if args.a2a_combine else
+                    "NCCL all_to_all_single" if transport == "a2a" else
                     "fused into GEMM2's epilogue: rows stored to the home rank over NVLink peer memory"),
+        "collectives_per_step": 0 if world == 1 else (2 if transport == "p2p" else 3 if transport == "p2p_combine" else 4),
         "routed_rows_per_rank": {"max": int(rows_per_rank.max()), "mean": float(rows_per_rank.float().mean())},
         "layer_tflops": round((2.0 * TOKENS * TOPK * 3 * HIDDEN * INTER + 2.0 * TOKENS * 3 * HIDDEN * INTER) / ms / 1e9, 1),
     }
 
     if rank == 0 and world == 1:
-        # CPU baseline on a bounded sample of the same tokens, with the same weights (copied from
-        # the device), doubling as a parity check of the GPU result at the full configuration.
-        torch.set_num_threads(os.cpu_count() or 1)
-        n = args.cpu_tokens
-        out_d = layer(hidden_d, tw_d, ti_d)
-
-        def fetch(e):
-            return w1[e].cpu(), w2[e].cpu(), s1[e].cpu(), s2[e].cpu()
-
-        ref, dt = cpu_layer_sample(hidden_h[:n].clone(), tw_h[:n].clone(), ti_h[:n].clone(), fetch,
-                                   tuple(t.cpu() for t in shared))
-        err = (out_d[:n].cpu().float() - ref.float()).abs()
-        tol = 1e-2 + 1e-2 * ref.float().abs()
-        line["cpu_baseline"] = {"value": round(n / dt, 3), "unit": "tokens/s", "cores": torch.get_num_threads(),
-                                "kind": "port",
-                                "sample": f"first {n} tokens of the step (all experts they route to, same weights), "
-                                          f"oracle/ torch-CPU fp32, {dt:.1f} s"}
-        # Rows are rounded to bf16 before the fp32 top-k sum (as in the reference), so one bf16
-        # ulp of the largest addend can survive cancellation: the strict elementwise bound holds
-        # for all but a few elements; the bound relative to max|ref| holds for all.
-        line["parity_sample"] = {"tokens": n, "max_abs_err": float(err.max()),
-                                 "max_abs_ref": float(ref.float().abs().max()),
-                                 "frac_within_rtol1e-2_atol1e-2": float((err <= tol).float().mean()),
-                                 "all_within_rtol1e-2_atol_1e-2_of_max": bool(
-                                     (err <= 1e-2 * ref.float().abs() + max(1e-2, 1e-2 * float(ref.float().abs().max()))).all())}
+        line.update(cpu_legs_single_gpu(args, layer, hidden_d, tw_d, ti_d, hidden_h, tw_h, ti_h, w1, w2, s1, s2,
+                                        shared))
         if not args.no_extras:
             line["extra"] = dense_extras(peaks)
     if rank == 0:
         print(json.dumps(line), flush=True)
-    if use_graph:
-        layer.release_graphs()
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    return layer
+
+
+def cpu_legs_single_gpu(args, layer, hidden_d, tw_d, ti_d, hidden_h, tw_h, ti_h, w1, w2, s1, s2, shared):
+    """CPU baseline and full-size parity at N=1, on the step's own tensors and weights (copied from
+    the device).  Parity is checked where the oracle can afford it at T=8192: (a) every row routed
+    to a few experts (busiest, emptiest, median ones), per row and per element, through
+    quantisation -> GEMM1 -> SiLU -> quantisation -> GEMM2 -> router weight; (b) the layer's final
+    output (top-k sum + shared expert) on the first --cpu-tokens tokens."""
+    import oracle
+    from flaggems_b200 import _cabi
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    out = {}
+    routed = layer.ops.local_routed(hidden_d, ti_d, tw_d)  # [T*topk, H] bf16 in route-slot order
+    out_d = layer(hidden_d, tw_d, ti_d)
+    torch.cuda.synchronize()
+    experts, counts = sample_experts(ti_h, args.cpu_experts)
+
+    def rows_of(e):
+        tok, slot = torch.nonzero(ti_h == e, as_tuple=True)
+        return tok, tw_h[tok, slot]
+
+    def fetch(e):
+        return w1[e].cpu(), w2[e].cpu(), s1[e].cpu(), s2[e].cpu()
+
+    shared_cpu = tuple(t.cpu() for t in shared)
+    results, dt, n_rows = cpu_expert_sample(experts, rows_of, fetch, shared_cpu, lambda tok: hidden_h[tok])
+    out["cpu_baseline"] = {
+        "value": round(n_rows / TOPK / dt, 3), "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+        "sample": (f"experts {experts} of the step (busiest, emptiest, median load) with ALL {n_rows} rows routed to "
+                   f"them, plus the shared expert on rows/top-{TOPK} tokens, same weights; tokens = rows / {TOPK}; "
+                   f"oracle/ torch-CPU fp32, {dt:.1f} s")}
+    worst, n_el, n_ok = 0.0, 0, 0
+    for e, ref in results.items():
+        tok, slot = torch.nonzero(ti_h == e, as_tuple=True)
+        got = routed[(tok * TOPK + slot).to(routed.device)].cpu().float()
+        err = (got - ref.float()).abs()
+        tol = 1e-2 + 1e-2 * ref.float().abs()
+        worst = max(worst, float((err - tol).max()))
+        n_el += err.numel()
+        n_ok += int((err <= tol).sum())
+    n = args.cpu_tokens
+    add = oracle.dense_block_fp8_mlp(hidden_h[:n].clone(), *shared_cpu)
+    touched = sorted(set(ti_h[:n].reshape(-1).tolist()))
+    remap = {e: i for i, e in enumerate(touched)}
+    ws = [fetch(e) for e in touched]
+    ref = oracle.fused_moe_block_fp8(hidden_h[:n].clone(), torch.stack([w[0] for w in ws]), torch.stack([w[1] for w in ws]),
+                                     torch.stack([w[2] for w in ws]), torch.stack([w[3] for w in ws]), tw_h[:n].clone(),
+                                     ti_h[:n].clone().apply_(lambda e: remap[e]), addend=add)
+    err = (out_d[:n].cpu().float() - ref.float()).abs()
+    tol = 1e-2 + 1e-2 * ref.float().abs()
+    # Rows are rounded to bf16 before the fp32 top-k sum (as in the reference), so one bf16 ulp of
+    # the largest addend can survive cancellation in the FINAL output: there the strict elementwise
+    # bound holds for all but a few elements and the bound relative to max|ref| for all.  The
+    # per-row results before the sum have no such cancellation and meet the strict bound.
+    out["parity_sample"] = {
+        "routed_rows": {"experts": experts, "rows": n_rows, "elements": n_el,
+                        "frac_within_rtol1e-2_atol1e-2": n_ok / max(n_el, 1),
+                        "worst_excess_over_bound": worst},
+        "final_output": {"tokens": n, "max_abs_err": float(err.max()), "max_abs_ref": float(ref.float().abs().max()),
+                         "frac_within_rtol1e-2_atol1e-2": float((err <= tol).float().mean()),
+                         "all_within_rtol1e-2_atol_1e-2_of_max": bool(
+                             (err <= 1e-2 * ref.float().abs() + max(1e-2, 1e-2 * float(ref.float().abs().max()))).all())}}
+    assert _cabi.device_status() == 0
+    return out
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--graph", action="store_true", help="replay CUDA graphs with several ranks as well")
     ap.add_argument("--no-graph", action="store_true", help="issue every step eagerly instead of replaying CUDA graphs")
-    ap.add_argument("--passes", type=int, default=2, help="how many times the K timed steps are run (fastest reported)")
-    ap.add_argument("--cpu-tokens", type=int, default=16, help="tokens in the bounded CPU sample")
+    ap.add_argument("--passes", type=int, default=5, help="how many times the K timed steps are run (median reported)")
+    ap.add_argument("--cpu-tokens", type=int, default=16, help="tokens of the final output compared with the oracle")
+    ap.add_argument("--cpu-experts", type=int, default=4,
+                    help="experts (with all their routed rows) in the bounded CPU sample at N=1")
     ap.add_argument("--no-extras", action="store_true", help="skip the dense GEMM / quant figures at N=1")
     ap.add_argument("--a2a-dispatch", action="store_true",
                     help="send packed rows by NCCL all-to-all instead of storing them to peers from the pack kernel")

@@ -22,6 +22,7 @@ _SIGS = {
     "fg_last_error": (c_char_p, []),
     "fg_device_status": (c_int, [ctypes.POINTER(c_uint)]),
     "fg_launch_count": (c_uint64, []),
+    "fg_selftest_bounded_wait": (c_int, [c_int64, c_int, _P]),
     "fg_act_quant_bf16_e4m3": (c_int, [_P, _P, _P, c_int64, c_int64, c_int, c_int64, c_int64, c_int64, c_int, _P]),
     "fg_per_token_group_quant_fp8": (
         c_int, [_P, c_int, _P, _P, c_int64, c_int64, c_int, c_int64, c_int64, c_int64, c_int64, c_float, c_int, _P]),
@@ -44,8 +45,10 @@ _SIGS = {
                 _P]),
     "fg_ep_pack_rows_fp8_peer": (
         c_int, [_P, c_int, c_int64, c_int64, c_int64, _P, c_int, _P, c_int, c_int, c_int, c_int, _P, _P, c_int64,
-                _P, _P, _P, c_int, _P]),
-    "fg_ep_plan": (c_int, [_P, c_int, c_int, _P, _P]),
+                _P, _P, _P, c_int, c_int64, _P]),
+    "fg_moe_align_block_size_regions": (
+        c_int, [_P, c_int, c_int64, c_int, c_int, _P, c_int, _P, c_int64, _P, c_int64, _P, c_int64, c_int, _P, _P,
+                c_int64, _P, c_int64, _P]),
     "fg_ep_pack_rows_fp8": (
         c_int, [_P, c_int, c_int64, c_int64, c_int64, _P, c_int, _P, c_int, c_int, c_int, c_int, _P, _P, c_int64,
                 _P, _P]),
@@ -57,10 +60,11 @@ _SIGS = {
         c_int, [_P, _P, c_int, _P, c_int, _P, c_int, c_int64, c_int, _P, _P, _P, _P, c_int, c_int64, c_int64, _P]),
     "fg_moe_routed_block_fp8_packed": (
         c_int, [_P, _P, c_int64, c_int64, _P, _P, _P, _P, c_int, c_int64, c_int64, _P, c_int64, c_int, _P, c_int,
-                _P, _P]),
+                c_int64, _P, c_int64, _P, c_int64, _P]),
     "fg_moe_grouped_gemm_fp8_peer": (
         c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int64, _P, _P, _P, c_int64, c_int64, c_int, c_int64, c_int64,
-                c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int64, _P, c_int, _P]),
+                c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int64, _P, c_int, c_int64,
+                _P]),
     "fg_symm_alloc": (c_int, [c_int64, ctypes.POINTER(c_void_p), _P]),
     "fg_symm_open": (c_int, [_P, ctypes.POINTER(c_void_p)]),
     "fg_symm_close": (c_int, [_P]),

@@ -32,6 +32,12 @@ unsigned int* fg_status_word_device_ptr() {
     return ptrs[dev];
 }
 
+int fg_device_index() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) dev = 0;
+    return dev > 63 ? 63 : dev;
+}
+
 int fg_num_sms() {
     static int sms[64] = {0};
     int dev = 0;
@@ -60,7 +66,9 @@ int fg_device_status(unsigned int* status) {
     if (v != 0) FG_CUDA(cudaMemcpyToSymbol(g_fg_status, &zero, sizeof(zero)));
     *status = v;
     if (v != 0) {
-        fg_set_error("device status 0x%08x: a bounded wait inside a kernel ran out (code %u, site %u)", v,
+        fg_set_error("device status 0x%08x: %s (code %u, site %u)", v,
+                     (v >> 16) == 2u ? "a row of the expert-parallel exchange was addressed outside its buffer and dropped"
+                                     : "a bounded wait inside a kernel ran out",
                      v >> 16, v & 0xffffu);
         return FG_ERR_DEVICE_STATUS;
     }

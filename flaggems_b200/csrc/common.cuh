@@ -46,6 +46,9 @@ static inline int64_t fg_cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 int fg_num_sms();
 
+// Index of the current device clamped to [0, 63]: the key of every per-device cache in the library.
+int fg_device_index();
+
 // Adds n to the process-wide count of kernels launched by this library.
 void fg_count_launch(int n);
 

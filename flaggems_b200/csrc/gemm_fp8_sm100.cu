@@ -27,6 +27,7 @@
 #include <cooperative_groups.h>
 #include <cuda.h>
 #include <stdlib.h>
+#include <mutex>
 #include <type_traits>
 
 #include "common.cuh"
@@ -75,6 +76,7 @@ struct GemmParams {
     const int32_t* dest;
     int64_t dest_stride;
     int n_peers;
+    int64_t peer_rows;  // rows each peer buffer holds; a row addressed outside is dropped and reported
     void* peer_out[8];
     unsigned int* status;
 };
@@ -477,8 +479,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 const int32_t* d = p.dest + out_row * p.dest_stride;
                 const int32_t home = d[1];
                 out_row = d[0];
-                row_ok = home >= 0 && home < p.n_peers && out_row >= 0;
+                row_ok = home >= 0 && home < p.n_peers && out_row >= 0 && out_row < p.peer_rows;
+                if (!row_ok && p.status) atomicCAS(p.status, 0u, (2u << 16) | 2u);
                 out_base = reinterpret_cast<uint8_t*>(p.peer_out[row_ok ? home : 0]);
+                if (!row_ok) out_row = 0;
             }
             uint8_t* out_ptr = out_base + out_row * p.ld_c * esz;
             // column of output chunk c (32 wide) handled by this thread
@@ -780,7 +784,10 @@ int make_map(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, uint64_
 // How many clusters of `slices` CTAs of the split-K kernel fit on the device at once (cached).
 template <int BN, bool BS>
 int max_resident_clusters(int slices) {
-    static int cache[9] = {0};
+    static int table[64][9];
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    int* cache = table[fg_device_index()];
     if (cache[slices]) return cache[slices];
     using C = Cfg<BN, false>;
     auto kernel = gemm_fp8_kernel<BN, BS, false, false, true>;
@@ -810,10 +817,15 @@ int launch_splitk(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
                   cudaStream_t st) {
     using C = Cfg<BN, false>;
     auto kernel = gemm_fp8_kernel<BN, BS, false, false, true>;
-    static bool attr_done = false;
-    if (!attr_done) {
-        FG_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-        attr_done = true;
+    static bool attr_done[64];
+    static std::mutex mu;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        bool& done = attr_done[fg_device_index()];
+        if (!done) {
+            FG_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+            done = true;
+        }
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(tiles * slices), 1, 1);
@@ -839,7 +851,10 @@ int launch_splitk(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int pair_tiles, cudaStream_t st) {
     using C = Cfg<256, false, true>;
     auto kernel = gemm_fp8_kernel<256, false, false, false, false, true>;
-    static int max_clusters = 0;
+    static int max_clusters_dev[64];
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    int& max_clusters = max_clusters_dev[fg_device_index()];
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(C::THREADS, 1, 1);
     cfg.dynamicSmemBytes = C::SMEM_BYTES;
@@ -882,10 +897,15 @@ template <int BN, bool BS, bool SILU, bool SMALL_A = false>
 int launch_inst(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int max_tiles, cudaStream_t st) {
     using C = Cfg<BN, SMALL_A>;
     auto kernel = gemm_fp8_kernel<BN, BS, SILU, SMALL_A, false>;
-    static bool attr_done = false;
-    if (!attr_done) {
-        FG_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-        attr_done = true;
+    static bool attr_done[64];
+    static std::mutex mu;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        bool& done = attr_done[fg_device_index()];
+        if (!done) {
+            FG_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+            done = true;
+        }
     }
     int grid = fg_num_sms();
     if (max_tiles < grid) grid = max_tiles;
@@ -999,9 +1019,31 @@ int launch_gemm(GemmParams& p, const void* a, int64_t a_rows, int64_t ld_a, cons
 
 bool dtype_ok(int d) { return d == FG_DTYPE_BF16 || d == FG_DTYPE_F16 || d == FG_DTYPE_F32; }
 
+// One thread waits, with the library's bounded wait, on an mbarrier phase that nothing completes.
+__global__ void bounded_wait_selftest_kernel(unsigned int* status, uint64_t limit_ns, uint32_t site) {
+    __shared__ uint64_t bar;
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        abort_flag = 0u;
+        fence_mbar_init();
+        mbar_wait(&bar, 0u, &abort_flag, status, site, limit_ns);
+    }
+}
+
 }  // namespace
 
 extern "C" {
+
+int fg_selftest_bounded_wait(int64_t limit_ns, int site, void* stream) {
+    FG_REQUIRE(limit_ns > 0 && limit_ns <= 100000000ll, FG_ERR_INVALID_ARGUMENT,
+               "limit_ns must be in (0, 100 ms]");
+    bounded_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(fg_status_word_device_ptr(), (uint64_t)limit_ns,
+                                                                     (uint32_t)site);
+    fg_count_launch(1);
+    FG_LAUNCH_CHECK();
+    return FG_OK;
+}
 
 int fg_scaled_mm_fp8(void* c, const void* a, const void* b, const float* sa, const float* sb, const void* bias,
                      int64_t M, int64_t N, int64_t K, int64_t ld_a, int64_t ld_b, int64_t ld_c, int sa_mode,
@@ -1050,7 +1092,7 @@ int fg_moe_grouped_gemm_fp8(void* c, const void* a, const void* w, const float* 
     return fg_moe_grouped_gemm_fp8_peer(c, a, w, a_scale, w_scale, topk_weights, topk_w_dtype, topk_w_stride,
                                         sorted_ids, expert_ids, num_post_pad, max_rows, numel, num_experts, N, K,
                                         ld_a, ld_c, block_rows, scale_mode, a_scale_per_row, fuse_silu, scatter,
-                                        mul_weight, out_dtype, nullptr, 0, nullptr, 0, stream);
+                                        mul_weight, out_dtype, nullptr, 0, nullptr, 0, 0, stream);
 }
 
 int fg_moe_grouped_gemm_fp8_peer(void* c, const void* a, const void* w, const float* a_scale, const float* w_scale,
@@ -1060,12 +1102,14 @@ int fg_moe_grouped_gemm_fp8_peer(void* c, const void* a, const void* w, const fl
                             int num_experts, int64_t N, int64_t K, int64_t ld_a, int64_t ld_c, int block_rows,
                             int scale_mode, int a_scale_per_row, int fuse_silu, int scatter, int mul_weight,
                             int out_dtype, const int32_t* dest, int64_t dest_stride, void* const* peer_out, int n_peers,
-                            void* stream) {
+                            int64_t peer_rows, void* stream) {
     FG_REQUIRE(max_rows >= 0 && N > 0 && K > 0 && num_experts > 0, FG_ERR_INVALID_ARGUMENT, "bad sizes");
     FG_REQUIRE((c || n_peers > 0) && a && w && a_scale && w_scale && sorted_ids && expert_ids && num_post_pad,
                FG_ERR_INVALID_ARGUMENT, "null pointer");
-    FG_REQUIRE(n_peers >= 0 && n_peers <= 8 && (n_peers == 0 || (dest && peer_out && scatter && dest_stride >= 2)),
-               FG_ERR_INVALID_ARGUMENT, "peer scatter needs 1..8 peers, scatter mode and a (slot, rank) table");
+    FG_REQUIRE(n_peers >= 0 && n_peers <= 8 &&
+                   (n_peers == 0 || (dest && peer_out && scatter && dest_stride >= 2 && peer_rows > 0)),
+               FG_ERR_INVALID_ARGUMENT,
+               "peer scatter needs 1..8 peers, scatter mode, a (slot, rank) table and the peers' row capacity");
     FG_REQUIRE(dtype_ok(out_dtype), FG_ERR_INVALID_ARGUMENT, "bad out_dtype %d", out_dtype);
     FG_REQUIRE(block_rows >= 8 && block_rows <= 128 && block_rows % 8 == 0, FG_ERR_UNSUPPORTED,
                "block_rows %d must be a multiple of 8 in [8, 128]", block_rows);
@@ -1093,7 +1137,7 @@ int fg_moe_grouped_gemm_fp8_peer(void* c, const void* a, const void* w, const fl
     p.grouped = 1; p.sorted_ids = sorted_ids; p.expert_ids = expert_ids; p.num_post_pad = num_post_pad;
     p.block_rows = block_rows; p.numel = numel; p.scatter = scatter; p.mul_weight = mul_weight;
     p.topk_w = topk_weights; p.topk_w_dtype = topk_w_dtype; p.topk_w_stride = topk_w_stride > 0 ? topk_w_stride : 1;
-    p.dest = dest; p.dest_stride = dest_stride; p.n_peers = n_peers;
+    p.dest = dest; p.dest_stride = dest_stride; p.n_peers = n_peers; p.peer_rows = peer_rows;
     for (int i = 0; i < n_peers; ++i) p.peer_out[i] = peer_out[i];
     if (n_peers > 0 && !c) p.c = peer_out[0];
     return launch_gemm(p, a, p.M, ld_a, w, num_experts, K, block, fuse_silu != 0, (cudaStream_t)stream);

@@ -2,6 +2,8 @@
 // distributed shared memory), silu_and_mul, moe_sum.
 #include <cooperative_groups.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -38,7 +40,22 @@ struct AlignArgs {
     int32_t id_div;           // bucket = id / id_div
     int32_t* expert_counts;   // nullable: rows per bucket before padding
     const int32_t* numel_dev; // nullable: device-side slot count (numel is then the capacity)
+    // Region mode (region_rows > 0): the numel slots are numel / region_rows regions of region_rows
+    // slots each, and only the first region_counts[s * region_stride] slots of region s hold rows
+    // (the receive buffer of the expert-parallel layer: one region per source rank).
+    int64_t region_rows;
+    const int32_t* region_counts;
+    int64_t region_stride;
 };
+
+// Whether slot i holds a row (always, outside region mode).
+__device__ __forceinline__ bool slot_present(const AlignArgs& a, int64_t i) {
+    if (a.region_rows <= 0) return true;
+    const int64_t s = i / a.region_rows;
+    int64_t c = a.region_counts[s * a.region_stride];
+    c = c < 0 ? 0 : (c > a.region_rows ? a.region_rows : c);
+    return i - s * a.region_rows < c;
+}
 
 template <typename IdT>
 __global__ void __launch_bounds__(ALIGN_THREADS, 1) moe_align_kernel(AlignArgs a) {
@@ -81,7 +98,7 @@ __global__ void __launch_bounds__(ALIGN_THREADS, 1) moe_align_kernel(AlignArgs a
     for (int64_t i0 = seg_begin; i0 < seg_end; i0 += 32) {
         const int64_t i = i0 + lane;
         int e = -1;
-        if (i < seg_end) {
+        if (i < seg_end && slot_present(a, i)) {
             const long long v = (long long)ids[i * a.ids_stride] / a.id_div;
             if (v >= 0 && v < E) e = (int)v;
         }
@@ -174,7 +191,7 @@ __global__ void __launch_bounds__(ALIGN_THREADS, 1) moe_align_kernel(AlignArgs a
     for (int64_t i0 = seg_begin; i0 < seg_end; i0 += 32) {
         const int64_t i = i0 + lane;
         int e = -1;
-        if (i < seg_end) {
+        if (i < seg_end && slot_present(a, i)) {
             const long long v = (long long)ids[i * a.ids_stride] / a.id_div;
             if (v >= 0 && v < E) e = (int)v;
         }
@@ -265,25 +282,6 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint8_t* __restr
     }
 }
 
-// Send/receive geometry of one rank, from the matrix counts[src][dst] of routed rows.
-__global__ void ep_plan_kernel(const int32_t* __restrict__ counts, int world, int me, int32_t* __restrict__ plan) {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
-    int32_t run = 0;
-    for (int d = 0; d < world; ++d) {  // plan[0..world]: first send-order row for each destination
-        plan[d] = run;
-        run += counts[me * world + d];
-    }
-    plan[world] = run;
-    int32_t total = 0;
-    for (int d = 0; d < world; ++d) {  // plan[9+d]: where this rank's rows start in d's receive buffer
-        int32_t off = 0;
-        for (int r = 0; r < me; ++r) off += counts[r * world + d];
-        plan[9 + d] = off;
-    }
-    for (int r = 0; r < world; ++r) total += counts[r * world + me];
-    plan[17] = total;  // rows this rank receives
-}
-
 unsigned grid_for(int64_t work_items, int per_block) {
     int64_t b = fg_cdiv(work_items, per_block);
     const int64_t cap = (int64_t)fg_num_sms() * 16;
@@ -308,36 +306,60 @@ int fg_moe_align_block_size_ex(const void* topk_ids, int ids_are_i64, int64_t nu
                                const int32_t* expert_map, int expert_map_len, int32_t* sorted_ids, int64_t max_pad,
                                int32_t* expert_ids, int64_t n_blocks, int32_t* num_post_pad, int64_t ids_stride,
                                int id_div, int32_t* expert_counts, const int32_t* numel_dev, void* stream) {
+    return fg_moe_align_block_size_regions(topk_ids, ids_are_i64, numel, num_experts, block_size, expert_map,
+                                           expert_map_len, sorted_ids, max_pad, expert_ids, n_blocks, num_post_pad,
+                                           ids_stride, id_div, expert_counts, numel_dev, 0, nullptr, 0, stream);
+}
+
+int fg_moe_align_block_size_regions(const void* topk_ids, int ids_are_i64, int64_t numel, int num_experts,
+                                    int block_size, const int32_t* expert_map, int expert_map_len, int32_t* sorted_ids,
+                                    int64_t max_pad, int32_t* expert_ids, int64_t n_blocks, int32_t* num_post_pad,
+                                    int64_t ids_stride, int id_div, int32_t* expert_counts, const int32_t* numel_dev,
+                                    int64_t region_rows, const int32_t* region_counts, int64_t region_stride,
+                                    void* stream) {
+    FG_REQUIRE(region_rows >= 0 && (region_rows == 0 || (region_counts && region_stride >= 1 && numel % region_rows == 0)),
+               FG_ERR_INVALID_ARGUMENT, "region mode needs counts, a stride >= 1 and numel divisible by region_rows");
     FG_REQUIRE(ids_stride >= 1 && id_div >= 1, FG_ERR_INVALID_ARGUMENT, "ids_stride and id_div must be >= 1");
     FG_REQUIRE(numel >= 0 && num_experts > 0 && block_size > 0, FG_ERR_INVALID_ARGUMENT,
                "numel %lld, num_experts %d, block_size %d", (long long)numel, num_experts, block_size);
     FG_REQUIRE(num_experts <= ALIGN_THREADS, FG_ERR_UNSUPPORTED, "num_experts %d exceeds the supported maximum %d",
                num_experts, ALIGN_THREADS);
     FG_REQUIRE(numel + (int64_t)num_experts * block_size < (1ll << 31), FG_ERR_UNSUPPORTED, "numel too large");
-    FG_REQUIRE(max_pad >= numel + (int64_t)num_experts * (block_size - 1), FG_ERR_INVALID_ARGUMENT,
-               "sorted_ids holds %lld entries, needs at least numel + E*(block_size-1) = %lld", (long long)max_pad,
-               (long long)(numel + (int64_t)num_experts * (block_size - 1)));
-    FG_REQUIRE(n_blocks >= fg_cdiv(max_pad, block_size) || n_blocks >= max_pad / block_size, FG_ERR_INVALID_ARGUMENT,
-               "expert_ids holds %lld entries, needs %lld", (long long)n_blocks, (long long)(max_pad / block_size));
+    // At most min(numel, E) experts are non-empty and only those are padded.
+    int64_t need_pad = numel + (int64_t)num_experts * (block_size - 1);
+    if (numel * block_size < need_pad) need_pad = numel * block_size;
+    FG_REQUIRE(max_pad >= need_pad, FG_ERR_INVALID_ARGUMENT,
+               "sorted_ids holds %lld entries, needs at least min(numel*block_size, numel + E*(block_size-1)) = %lld",
+               (long long)max_pad, (long long)need_pad);
+    FG_REQUIRE(n_blocks >= need_pad / block_size, FG_ERR_INVALID_ARGUMENT,
+               "expert_ids holds %lld entries, needs %lld", (long long)n_blocks, (long long)(need_pad / block_size));
     FG_REQUIRE(sorted_ids && expert_ids && num_post_pad && (topk_ids || numel == 0), FG_ERR_INVALID_ARGUMENT,
                "null pointer");
     FG_REQUIRE(expert_map == nullptr || expert_map_len >= num_experts, FG_ERR_INVALID_ARGUMENT,
                "expert_map has %d entries for %d experts", expert_map_len, num_experts);
 
     AlignArgs a{topk_ids, numel, num_experts, block_size, expert_map, expert_map_len,
-                sorted_ids, max_pad, expert_ids, n_blocks, num_post_pad, ids_stride, id_div, expert_counts, numel_dev};
+                sorted_ids, max_pad, expert_ids, n_blocks, num_post_pad, ids_stride, id_div, expert_counts, numel_dev,
+                region_rows, region_counts, region_stride};
     // One CTA handles 32 warps x 128 slots comfortably; grow the cluster with numel up to 8.
     int ranks = 1;
     while (ranks < 8 && (int64_t)ranks * ALIGN_THREADS * 4 < numel) ranks *= 2;
     const size_t smem = (size_t)(ALIGN_WARPS + 4) * num_experts * sizeof(int32_t);
 
     auto kernel = ids_are_i64 ? moe_align_kernel<int64_t> : moe_align_kernel<int32_t>;
-    // Opt in to large dynamic shared memory once per kernel and size (a host-side attribute,
-    // kept out of the steady-state call path).
-    static size_t smem_set[2] = {48 * 1024, 48 * 1024};
-    if (smem > smem_set[ids_are_i64 ? 1 : 0]) {
-        FG_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        smem_set[ids_are_i64 ? 1 : 0] = smem;
+    // Opt in to large dynamic shared memory once per device, kernel and size (a per-device
+    // attribute, kept out of the steady-state call path).
+    static std::mutex mu;
+    static size_t smem_set[64][2];
+    {
+        const int dev = fg_device_index();
+        std::lock_guard<std::mutex> lock(mu);
+        size_t& have = smem_set[dev][ids_are_i64 ? 1 : 0];
+        if (have < 48 * 1024) have = 48 * 1024;
+        if (smem > have) {
+            FG_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            have = smem;
+        }
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ranks, 1, 1);
@@ -353,15 +375,6 @@ int fg_moe_align_block_size_ex(const void* topk_ids, int ids_are_i64, int64_t nu
     cfg.numAttrs = 1;
     FG_CUDA(cudaLaunchKernelEx(&cfg, kernel, a));
     fg_count_launch(1);
-    return FG_OK;
-}
-
-int fg_ep_plan(const int32_t* counts, int world, int rank, int32_t* plan, void* stream) {
-    FG_REQUIRE(counts && plan && world >= 1 && world <= 8 && rank >= 0 && rank < world, FG_ERR_INVALID_ARGUMENT,
-               "bad arguments (world must be 1..8)");
-    ep_plan_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(counts, world, rank, plan);
-    fg_count_launch(1);
-    FG_LAUNCH_CHECK();
     return FG_OK;
 }
 

@@ -67,7 +67,7 @@ int check_dims(int64_t n_in, int num_experts, int64_t H, int64_t I, int out_dtyp
 int run_gemms(void* y, const Workspace& ws, int64_t n_in, const void* w1, const void* w2, const float* s1,
               const float* s2, int num_experts, int64_t H, int64_t I, const void* weights, int w_dtype,
               int64_t w_stride, int out_dtype, const int32_t* dest, int64_t dest_stride, void* const* peer_out,
-              int n_peers, void* stream) {
+              int n_peers, int64_t peer_rows, void* stream) {
     int rc = fg_moe_grouped_gemm_fp8(ws.act, ws.a1, w1, ws.a1s, s1, nullptr, 0, 1, ws.sorted_ids, ws.expert_ids,
                                      ws.post_pad, ws.rows, n_in, num_experts, 2 * I, H, H, I, TILE_ROWS, FG_SCALE_BLOCK,
                                      1, /*fuse_silu=*/1, /*scatter=*/0, /*mul_weight=*/0, out_dtype, stream);
@@ -78,7 +78,7 @@ int run_gemms(void* y, const Workspace& ws, int64_t n_in, const void* w1, const 
     return fg_moe_grouped_gemm_fp8_peer(y, ws.a2, w2, ws.a2s, s2, weights, w_dtype, w_stride, ws.sorted_ids,
                                         ws.expert_ids, ws.post_pad, ws.rows, n_in, num_experts, H, I, I, H, TILE_ROWS,
                                         FG_SCALE_BLOCK, 1, /*fuse_silu=*/0, /*scatter=*/1, /*mul_weight=*/1, out_dtype,
-                                        dest, dest_stride, peer_out, n_peers, stream);
+                                        dest, dest_stride, peer_out, n_peers, peer_rows, stream);
 }
 
 // Device address of g_routed_scratch on the current device, looked up once per device.
@@ -128,13 +128,15 @@ int fg_moe_routed_block_fp8_local(void* y, const void* hidden, int hidden_dtype,
                                              topk, (int32_t)n_in, ws.post_pad, stream);
     if (rc != FG_OK) return rc;
     return run_gemms(y, ws, n_in, w1, w2, s1, s2, num_experts, H, I, topk_w, topk_w_dtype, 1, hidden_dtype, nullptr, 0,
-                     nullptr, 0, stream);
+                     nullptr, 0, 0, stream);
 }
 
 int fg_moe_routed_block_fp8_packed(void* y, const void* rows, int64_t R, int64_t row_bytes, const void* w1,
                                    const void* w2, const float* s1, const float* s2, int num_experts, int64_t H,
                                    int64_t I, void* workspace, int64_t workspace_bytes, int out_dtype,
-                                   void* const* peer_out, int n_peers, const int32_t* n_rows_dev, void* stream) {
+                                   void* const* peer_out, int n_peers, int64_t peer_rows, const int32_t* n_rows_dev,
+                                   int64_t region_rows, const int32_t* region_counts, int64_t region_stride,
+                                   void* stream) {
     int rc = check_dims(R, num_experts, H, I, out_dtype);
     if (rc != FG_OK) return rc;
     if (R == 0) return FG_OK;
@@ -150,16 +152,16 @@ int fg_moe_routed_block_fp8_packed(void* y, const void* rows, int64_t R, int64_t
     const int64_t s_cols = H / 128;
     const int32_t* ids = reinterpret_cast<const int32_t*>(base + H + 4 * s_cols);
     const float* wts = reinterpret_cast<const float*>(base + H + 4 * s_cols + 4);
-    rc = fg_moe_align_block_size_ex(ids, 0, R, num_experts, TILE_ROWS, nullptr, 0, ws.sorted_ids, ws.max_pad,
-                                    ws.expert_ids, ws.n_blocks, ws.post_pad, row_bytes / 4, 1, nullptr, n_rows_dev,
-                                    stream);
+    rc = fg_moe_align_block_size_regions(ids, 0, R, num_experts, TILE_ROWS, nullptr, 0, ws.sorted_ids, ws.max_pad,
+                                         ws.expert_ids, ws.n_blocks, ws.post_pad, row_bytes / 4, 1, nullptr,
+                                         n_rows_dev, region_rows, region_counts, region_stride, stream);
     if (rc != FG_OK) return rc;
     rc = fg_gather_rows_fp8(base, reinterpret_cast<const float*>(base + H), ws.a1, ws.a1s, ws.rows, H, s_cols,
                             row_bytes, row_bytes / 4, ws.sorted_ids, 1, (int32_t)R, ws.post_pad, stream);
     if (rc != FG_OK) return rc;
     const int32_t* dest = reinterpret_cast<const int32_t*>(base + H + 4 * s_cols + 8);
     return run_gemms(y, ws, R, w1, w2, s1, s2, num_experts, H, I, wts, FG_DTYPE_F32, row_bytes / 4, out_dtype,
-                     n_peers > 0 ? dest : nullptr, row_bytes / 4, peer_out, n_peers, stream);
+                     n_peers > 0 ? dest : nullptr, row_bytes / 4, peer_out, n_peers, peer_rows, stream);
 }
 
 int fg_moe_routed_block_fp8_local_noalloc(void* y, const void* hidden, int hidden_dtype, const void* topk_ids,

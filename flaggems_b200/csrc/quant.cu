@@ -44,21 +44,40 @@ struct QuantArgs {
     int32_t* inv;  // nullable: inv[route slot] = output row
     const float* tensor_scale;  // per-tensor modes: the given scale, or the global amax
     float* tensor_scale_out;    // dynamic per-tensor mode: where the derived scale is written
-    // Direct dispatch: output row p (send order) is written into the receive buffer of its
-    // destination rank d (plan[d] <= p < plan[d+1]) at row plan[9+d] + (p - plan[d]).
-    const int32_t* plan;  // nullable
+    // Direct dispatch: send_counts[d] rows go to rank d; output row p (send order, destinations
+    // ascending) is the (p - first[d])-th row for its destination d and is written into d's
+    // receive buffer at row meta_rank * region_rows + (p - first[d]): every source rank owns a
+    // fixed region of every receive buffer, so no rank needs another rank's counts to send.
+    const int32_t* send_counts;  // nullable
     int world;
+    int64_t region_rows;
     uint8_t* peer_q[8];
+    unsigned int* status;
 };
 
-// Start of the packed row that output row `r` is written to.
+// Start of the packed row that output row `r` is written to, or nullptr when the row does not
+// fit its region of the destination's receive buffer (recorded in the status word; never stored).
 __device__ __forceinline__ uint8_t* packed_row_ptr(const QuantArgs& a, int64_t r) {
-    if (!a.plan) return a.q + r * a.ld_q;
+    if (!a.send_counts) return a.q + r * a.ld_q;
     int d = 0;
+    int64_t first = 0, run = 0;
 #pragma unroll
-    for (int i = 1; i < 8; ++i)
-        if (i < a.world && r >= a.plan[i]) d = i;
-    return a.peer_q[d] + (int64_t)(a.plan[9 + d] + (int32_t)r - a.plan[d]) * a.ld_q;
+    for (int i = 0; i < 8; ++i) {
+        if (i < a.world) {
+            if (r >= run) {
+                d = i;
+                first = run;
+            }
+            const int32_t c = a.send_counts[i];
+            run += c > 0 ? c : 0;
+        }
+    }
+    const int64_t idx = r - first;
+    if (r >= run || idx >= a.region_rows) {
+        if (a.status) atomicCAS(a.status, 0u, (2u << 16) | 1u);
+        return nullptr;
+    }
+    return a.peer_q[d] + ((int64_t)a.meta_rank * a.region_rows + idx) * a.ld_q;
 }
 
 __device__ __forceinline__ void write_row_meta(const QuantArgs& a, int64_t out_row) {
@@ -69,7 +88,9 @@ __device__ __forceinline__ void write_row_meta(const QuantArgs& a, int64_t out_r
     if (a.meta_w_dtype == FG_DTYPE_BF16) w = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.meta_w)[slot]);
     else if (a.meta_w_dtype == FG_DTYPE_F16) w = __half2float(reinterpret_cast<const __half*>(a.meta_w)[slot]);
     else w = reinterpret_cast<const float*>(a.meta_w)[slot];
-    uint8_t* m = packed_row_ptr(a, out_row) + a.meta_off;
+    uint8_t* m = packed_row_ptr(a, out_row);
+    if (!m) return;
+    m += a.meta_off;
     *reinterpret_cast<int32_t*>(m) = (int32_t)(e % a.meta_mod);
     *reinterpret_cast<float*>(m + 4) = w;
     *reinterpret_cast<int32_t*>(m + 8) = slot;
@@ -222,8 +243,9 @@ __global__ void __launch_bounds__(256) group_quant_kernel(QuantArgs a) {
             for (int o = TPG / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
             const float s = make_scale<MODE>(amax, a.eps, a.pow2);
             const Divider d = make_divider<MODE>(s);
-            if (row[u] < rows) {
-                uint8_t* qrow = a.meta_ids ? packed_row_ptr(a, row[u]) : a.q + (int64_t)row[u] * a.ld_q;
+            uint8_t* qrow = nullptr;
+            if (row[u] < rows) qrow = a.meta_ids ? packed_row_ptr(a, row[u]) : a.q + (int64_t)row[u] * a.ld_q;
+            if (qrow) {
 #pragma unroll
                 for (int w = 0; w < VPT; ++w) {
                     float q[8];
@@ -469,23 +491,27 @@ int fg_ep_pack_rows_fp8(const void* x, int x_dtype, int64_t T, int64_t K, int64_
                         int home_rank, const int32_t* order, void* packed, int64_t row_bytes, int32_t* inv,
                         void* stream) {
     return fg_ep_pack_rows_fp8_peer(x, x_dtype, T, K, ld_x, topk_ids, ids_are_i64, topk_w, topk_w_dtype, topk,
-                                    experts_per_rank, home_rank, order, packed, row_bytes, inv, nullptr, nullptr, 0,
+                                    experts_per_rank, home_rank, order, packed, row_bytes, inv, nullptr, nullptr, 0, 0,
                                     stream);
 }
 
 int fg_ep_pack_rows_fp8_peer(const void* x, int x_dtype, int64_t T, int64_t K, int64_t ld_x, const void* topk_ids,
                              int ids_are_i64, const void* topk_w, int topk_w_dtype, int topk, int experts_per_rank,
                              int home_rank, const int32_t* order, void* packed, int64_t row_bytes, int32_t* inv,
-                             const int32_t* plan, void* const* peer_rows, int world, void* stream) {
+                             const int32_t* send_counts, void* const* peer_rows, int world, int64_t region_rows,
+                             void* stream) {
     FG_REQUIRE(T >= 0 && K > 0 && topk > 0 && experts_per_rank > 0, FG_ERR_INVALID_ARGUMENT, "bad sizes");
     FG_REQUIRE(K % 128 == 0, FG_ERR_UNSUPPORTED, "row length %lld must be a multiple of 128", (long long)K);
     FG_REQUIRE(row_bytes >= K + 4 * (K / 128) + 16 && row_bytes % 16 == 0, FG_ERR_INVALID_ARGUMENT,
                "row_bytes %lld too small or not a multiple of 16", (long long)row_bytes);
     FG_REQUIRE(T * topk < (1ll << 31), FG_ERR_UNSUPPORTED, "too many route slots");
     if (T == 0) return FG_OK;
-    FG_REQUIRE(x && topk_ids && topk_w && order && (packed || plan), FG_ERR_INVALID_ARGUMENT, "null pointer");
-    FG_REQUIRE(plan == nullptr || (peer_rows && world >= 1 && world <= 8), FG_ERR_INVALID_ARGUMENT,
-               "direct dispatch needs 1..8 peer buffers");
+    FG_REQUIRE(x && topk_ids && topk_w && order && (packed || send_counts), FG_ERR_INVALID_ARGUMENT, "null pointer");
+    FG_REQUIRE(send_counts == nullptr ||
+                   (peer_rows && world >= 1 && world <= 8 && home_rank >= 0 && home_rank < world && region_rows > 0),
+               FG_ERR_INVALID_ARGUMENT, "direct dispatch needs 1..8 peer buffers, a rank below world and region_rows > 0");
+    FG_REQUIRE(send_counts == nullptr || T * topk <= region_rows, FG_ERR_INVALID_ARGUMENT,
+               "%lld route slots do not fit a region of %lld rows", (long long)(T * topk), (long long)region_rows);
     QuantArgs a{};
     a.x = x; a.q = (uint8_t*)packed; a.s = reinterpret_cast<float*>((uint8_t*)packed + K);
     a.rows = T * topk; a.K = K; a.group = 128;
@@ -494,9 +520,10 @@ int fg_ep_pack_rows_fp8_peer(const void* x, int x_dtype, int64_t T, int64_t K, i
     a.row_index = order; a.index_div = topk; a.index_limit = (int32_t)(T * topk); a.n_rows_dev = nullptr;
     a.meta_ids = topk_ids; a.meta_ids_i64 = ids_are_i64; a.meta_w = topk_w; a.meta_w_dtype = topk_w_dtype;
     a.meta_mod = experts_per_rank; a.meta_rank = home_rank; a.meta_off = K + 4 * (K / 128); a.inv = inv;
-    a.plan = plan; a.world = world;
-    for (int i = 0; i < 8; ++i) a.peer_q[i] = (plan && i < world) ? (uint8_t*)peer_rows[i] : nullptr;
-    if (plan) {
+    a.send_counts = send_counts; a.world = world; a.region_rows = region_rows;
+    a.status = fg_status_word_device_ptr();
+    for (int i = 0; i < 8; ++i) a.peer_q[i] = (send_counts && i < world) ? (uint8_t*)peer_rows[i] : nullptr;
+    if (send_counts) {
         a.q = (uint8_t*)peer_rows[home_rank];
         a.s = reinterpret_cast<float*>(a.q + K);
     }

@@ -11,13 +11,16 @@ row's result does not depend on the number of ranks.
 
 Per step and rank:
   1. order the T_loc*topk route slots by destination rank (stable), count per destination;
-  2. quantise the local tokens to FP8 (1x128 groups) straight into that send order;
-  3. exchange counts, then FP8 rows + scales + (local expert id, router weight) by
-     ``all_to_all_single`` (NCCL over NVLink; gloo in the CPU tests);
+  2. quantise the local tokens to FP8 (1x128 groups) straight into that send order; the rows
+     (FP8 payload + scales + local expert id, router weight, home slot, home rank) either go into
+     this rank's region of the destination's receive buffer over NVLink peer memory from inside
+     the quantisation kernel ("p2p"), or travel by ``all_to_all_single`` (NCCL; gloo in the CPU
+     tests);
+  3. counts reach the receivers by an all-gather that doubles as the "rows have landed" barrier;
   4. received rows: moe_align over local expert ids, gather into expert-sorted padded order,
-     GEMM1(+SiLU) / quant / GEMM2(x weight), results written back in arrival order;
-  5. return the bf16 rows by the reverse all-to-all;
-  6. home rank: fp32 sum over the top-k slots in slot order (+ the shared-expert output) and
+     GEMM1(+SiLU) / quant / GEMM2(x weight); GEMM2's epilogue stores each result row into the home
+     rank's combine buffer over peer memory (or rows return by the reverse all-to-all);
+  5. home rank: fp32 sum over the top-k slots in slot order (+ the shared-expert output) and
      one bf16 cast.
 The shared expert (a dense block-FP8 MLP applied to every local token) is composed from the
 dense ops of this package and runs on a side stream while the dispatch is in flight.
@@ -66,13 +69,13 @@ def packed_row_bytes(hidden: int) -> int:
 class SymmetricBuffers:
     """``count`` device buffers of ``nbytes`` on every rank, each mapped into every other rank of
     the node through CUDA IPC.  ``ptrs[i][r]`` is the address, valid in this process, of buffer i
-    of rank r.  Creation is collective over ``group``."""
+    of rank r.  Creation is collective over ``group``; so is :meth:`close`."""
 
     def __init__(self, nbytes, count, rank, world, group=None):
         import ctypes
 
         L = _cabi.lib()
-        self.nbytes, self.count, self.rank, self.world = nbytes, count, rank, world
+        self.nbytes, self.count, self.rank, self.world, self.group = nbytes, count, rank, world, group
         self.local, handles = [], []
         for _ in range(count):
             ptr = ctypes.c_void_p()
@@ -99,12 +102,18 @@ class SymmetricBuffers:
         dist.barrier(group=group)
 
     def close(self):
+        """Collective: unmaps the peers' buffers, waits until every rank has done so, then frees
+        this rank's buffers.  The caller has already made sure that no kernel that touches the
+        buffers is in flight on any rank (device synchronise + barrier)."""
         L = _cabi.lib()
         for p in self._opened:
             L.fg_symm_close(p)
+        self._opened = []
+        if self.local:
+            dist.barrier(group=self.group)
         for p in self.local:
             L.fg_symm_free(p)
-        self._opened, self.local = [], []
+        self.local, self.ptrs, self.ptr_arrays = [], [], []
 
 
 class CudaMoEOps:
@@ -164,36 +173,36 @@ class CudaMoEOps:
             meta.data_ptr() + 4, None, _cabi.stream_ptr(dev)))
         return order, meta[1:]
 
-    def pack_to_peers(self, hidden, topk_ids, topk_w, order, counts_matrix, world, rank, peer_rows):
-        """Quantises the local tokens and stores every packed row directly into its destination
-        rank's receive buffer.  Returns the plan tensor; plan[17] is the number of rows this rank
-        receives (device-side)."""
+    def pack_to_peers(self, hidden, topk_ids, topk_w, order, send_counts, world, rank, peer_rows, region_rows):
+        """Quantises the local tokens and stores every packed row directly into this rank's region
+        of its destination rank's receive buffer (``send_counts``: rows per destination, on the
+        device; rows beyond a region are dropped by the kernel and reported in the status word)."""
         t, topk = topk_ids.shape
         dev = hidden.device
-        plan = torch.empty(18, dtype=torch.int32, device=dev)
-        L, st = _cabi.lib(), _cabi.stream_ptr(dev)
-        _cabi.check(L.fg_ep_plan(_cabi.ptr(counts_matrix), world, rank, _cabi.ptr(plan), st))
-        _cabi.check(L.fg_ep_pack_rows_fp8_peer(
+        _cabi.check(_cabi.lib().fg_ep_pack_rows_fp8_peer(
             _cabi.ptr(hidden), _cabi.DTYPE_CODE[hidden.dtype], t, self.hidden, hidden.stride(0),
             _cabi.ptr(topk_ids), 1 if topk_ids.dtype == torch.int64 else 0, _cabi.ptr(topk_w),
             _cabi.DTYPE_CODE[topk_w.dtype], topk, self.num_local_experts, rank, _cabi.ptr(order), None,
-            self.row_bytes, None, _cabi.ptr(plan), peer_rows, world, st))
-        return plan
+            self.row_bytes, None, _cabi.ptr(send_counts), peer_rows, world, region_rows, _cabi.stream_ptr(dev)))
 
-    def experts_from_buffer(self, rows_ptr, capacity, n_rows_dev_ptr, out_dtype, device, peer_out):
-        """Routed-expert pipeline on the rows that peers stored into this rank's receive buffer;
-        the row count is read on the device, results go to the home ranks' buffers."""
+    def experts_from_buffer(self, rows_ptr, world, region_rows, counts_matrix, rank, out_dtype, device, peer_out,
+                            peer_rows):
+        """Routed-expert pipeline on the rows that peers stored into this rank's receive buffer:
+        region s of the buffer holds counts_matrix[s, rank] rows (read on the device); results go
+        to the home ranks' combine buffers of ``peer_rows`` rows each."""
+        capacity = world * region_rows
         ws = self._workspace(capacity, device)
         _cabi.check(_cabi.lib().fg_moe_routed_block_fp8_packed(
             None, rows_ptr, capacity, self.row_bytes, _cabi.ptr(self.w1), _cabi.ptr(self.w2),
             _cabi.ptr(self.w1_scale), _cabi.ptr(self.w2_scale), self.num_local_experts, self.hidden, self.inter,
-            _cabi.ptr(ws), ws.numel(), _cabi.DTYPE_CODE[out_dtype], peer_out, len(peer_out), n_rows_dev_ptr,
-            _cabi.stream_ptr(device)))
+            _cabi.ptr(ws), ws.numel(), _cabi.DTYPE_CODE[out_dtype], peer_out, len(peer_out), peer_rows, None,
+            region_rows, counts_matrix.data_ptr() + 4 * rank, world, _cabi.stream_ptr(device)))
 
-    def experts_packed(self, packed, out_dtype, peer_out=None):
+    def experts_packed(self, packed, out_dtype, peer_out=None, peer_rows=0):
         """Routed-expert pipeline on R received packed rows.  Without ``peer_out`` the result is
         returned as [R, H] in arrival order; with it (a ctypes array of one buffer address per
-        rank) GEMM2 stores every row into its home rank's buffer and None is returned."""
+        rank, each buffer ``peer_rows`` rows) GEMM2 stores every row into its home rank's buffer
+        and None is returned."""
         r = packed.shape[0]
         y = None
         if peer_out is None:
@@ -205,7 +214,8 @@ class CudaMoEOps:
             _cabi.ptr(y), _cabi.ptr(packed), r, self.row_bytes, _cabi.ptr(self.w1), _cabi.ptr(self.w2),
             _cabi.ptr(self.w1_scale), _cabi.ptr(self.w2_scale), self.num_local_experts, self.hidden, self.inter,
             _cabi.ptr(ws), ws.numel(), _cabi.DTYPE_CODE[out_dtype], peer_out,
-            0 if peer_out is None else len(peer_out), None, _cabi.stream_ptr(packed.device)))
+            0 if peer_out is None else len(peer_out), peer_rows, None, 0, None, 0,
+            _cabi.stream_ptr(packed.device)))
         return y
 
     def combine_slots(self, buf_ptr, tokens, topk, dtype, device, addend):
@@ -259,6 +269,9 @@ class CudaMoEOps:
         return torch.cuda.Stream(device=device)
 
 
+TRANSPORTS = ("a2a", "p2p_combine", "p2p")
+
+
 class ExpertParallelMoE:
     """One MoE layer whose ``num_experts`` routed experts are split evenly over ``world`` ranks.
 
@@ -267,35 +280,52 @@ class ExpertParallelMoE:
     ``shared`` = (w1 [2I_s, H], w2 [H, I_s], w1_scale, w2_scale) adds a dense expert applied to
     every token.  ``group`` is a torch.distributed process group (None: default group; a
     single-rank layer needs no process group at all).
+
+    ``transport`` is fixed at construction and must be the same on every rank, so that all ranks
+    issue the same collectives in every step whatever their token counts:
+      "a2a"          rows and results travel by ``all_to_all_single`` (one host wait per step);
+      "p2p_combine"  dispatch by all-to-all, combine fused into GEMM2 over peer memory;
+      "p2p"          dispatch fused into the quantisation kernel as well: no host wait, two small
+                     collectives per step (the count all-gather and one barrier).
+    The peer-memory transports need ``max_slots_per_rank`` = the largest tokens * topk any rank will
+    pass in one step; a step beyond it raises before anything is launched.  Call :meth:`close`
+    (collective) before the process group is destroyed.
     """
 
     def __init__(self, w1, w2, w1_scale, w2_scale, num_experts: int, rank: int = 0, world: int = 1,
-                 group=None, shared=None, ops=None, p2p_combine_rows: int = 0, p2p_dispatch_rows: int = 0):
+                 group=None, shared=None, ops=None, transport: str = "a2a", max_slots_per_rank: int = 0):
         assert num_experts % world == 0, "experts must divide evenly over the ranks"
         assert w1.shape[0] == num_experts // world, "w1 must hold exactly this rank's experts"
+        assert transport in TRANSPORTS, f"transport must be one of {TRANSPORTS}"
+        assert 0 <= rank < world
         self.num_experts, self.rank, self.world, self.group = num_experts, rank, world, group
         self.num_local_experts = num_experts // world
         self.ops = ops if ops is not None else CudaMoEOps(w1, w2, w1_scale, w2_scale, shared)
         self._side = None
-        self.last_counts = None  # (send_counts, recv_counts) of the latest step, for reporting
+        self.last_counts = None  # (send_counts, recv_counts) of the latest all-to-all step, for reporting
         self.trace = None  # set to a list to collect (phase name, CUDA event) marks of a step
-        # Fused combine: GEMM2 writes result rows straight into the home rank's buffer over
-        # NVLink peer memory.  p2p_combine_rows = capacity in route slots (tokens * topk) per rank;
-        # 0 keeps the all-to-all combine.  Two buffers alternate between steps.
-        self._symm, self._step = None, 0
-        if p2p_combine_rows > 0 and world > 1 and ops is None:
+        if world == 1 or ops is not None:
+            transport = "a2a"  # one rank exchanges nothing; the CPU stand-ins have no peer memory
+        self.transport = transport
+        self.max_slots = int(max_slots_per_rank)
+        self._symm = self._recv = None
+        self._graph = None
+        if world > 1 and dist.get_world_size(group) != world:
+            raise ValueError(f"the process group has {dist.get_world_size(group)} ranks, the layer was "
+                             f"built for {world}")
+        if transport != "a2a":
+            assert self.max_slots > 0, "the peer-memory transports need max_slots_per_rank"
             hidden_size = w1.shape[2]
-            self._symm = SymmetricBuffers(p2p_combine_rows * hidden_size * 2, 2, rank, world, group)
-            self._symm_rows = p2p_combine_rows
+            # Combine buffer: one bf16/fp16 row per route slot of this rank, written by the ranks
+            # that hold the slot's expert (GEMM2's epilogue) and read by the top-k sum here.
+            self._symm = SymmetricBuffers(self.max_slots * hidden_size * 2, 1, rank, world, group)
             self._flag = torch.zeros(1, dtype=torch.float32, device=w1.device)
-        # Fused dispatch: the quantisation kernel stores packed rows straight into the destination
-        # rank's receive buffer; counts travel by an all-gather that stays on the stream, so a step
-        # has no host round trip at all.  p2p_dispatch_rows = receive capacity in rows per rank
-        # (the safe value is world * tokens * topk: every route of every rank landing on one rank).
-        self._recv = None
-        if p2p_dispatch_rows > 0 and self._symm is not None:
-            self._recv = SymmetricBuffers(p2p_dispatch_rows * self.ops.row_bytes, 2, rank, world, group)
-            self._recv_rows = p2p_dispatch_rows
+        if transport == "p2p":
+            # Receive buffer: `world` regions of max_slots rows; source rank s writes only region s,
+            # so nobody needs anybody's counts before sending.  One buffer is enough: a peer's next
+            # step cannot store into it before this rank has entered the collective that follows
+            # its own reads (every step is ordered on one stream per rank), see forward().
+            self._recv = SymmetricBuffers(world * self.max_slots * self.ops.row_bytes, 1, rank, world, group)
             self._counts_matrix = torch.zeros(world * world, dtype=torch.int32, device=w1.device)
 
     def _mark(self, name, device):
@@ -317,13 +347,19 @@ class ExpertParallelMoE:
         return both[0].tolist(), both[1].tolist()
 
     # -- forward ---------------------------------------------------------------------------
-    def forward(self, hidden: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
-                _buf: Optional[int] = None) -> torch.Tensor:
+    def forward(self, hidden: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
         assert hidden.dim() == 2 and hidden.is_contiguous()
         assert topk_weights.shape == topk_ids.shape and topk_ids.shape[0] == hidden.shape[0]
         tokens, topk = topk_ids.shape
         ops = self.ops
         dev = hidden.device
+        # Everything that can refuse the step does so here, before the first launch or collective.
+        if self.transport != "a2a":
+            if tokens * topk > self.max_slots:
+                raise ValueError(f"{tokens} tokens x top-{topk} = {tokens * topk} route slots exceed "
+                                 f"max_slots_per_rank = {self.max_slots}")
+            if hidden.dtype not in (torch.bfloat16, torch.float16):
+                raise TypeError("the peer-memory transports carry bf16 or fp16 rows")
         topk_ids = topk_ids.contiguous()
         topk_weights = topk_weights.contiguous()
         if topk_weights.dtype not in _cabi.DTYPE_CODE:
@@ -342,68 +378,69 @@ class ExpertParallelMoE:
             else:
                 shared_out = ops.shared_expert(hidden)
 
+        def join_shared():
+            if side is not None:
+                main = torch.cuda.current_stream(dev)
+                main.wait_stream(side)
+                shared_out.record_stream(main)
+
         self._mark("start", dev)
         if self.world == 1:
             y = ops.local_routed(hidden, topk_ids, topk_weights)
-            inv = None
             self._mark("experts", dev)
-        else:
-            use_p2p = (self._symm is not None and hidden.dtype in (torch.bfloat16, torch.float16)
-                       and tokens * topk <= self._symm_rows)
-            if use_p2p and self._recv is not None and self.world * tokens * topk <= self._recv_rows:
-                # Device-driven step: no host wait, no NCCL payload traffic.
-                if _buf is None:
-                    buf = self._step & 1
-                    self._step += 1
-                else:
-                    buf = _buf
-                order, counts_dev = ops.route(topk_ids, self.world)
-                dist.all_gather_into_tensor(self._counts_matrix, counts_dev.contiguous(), group=self.group)
-                self._mark("route+counts", dev)
-                plan = ops.pack_to_peers(hidden, topk_ids, topk_weights, order, self._counts_matrix, self.world,
-                                         self.rank, self._recv.ptr_arrays[buf])
-                dist.all_reduce(self._flag, group=self.group)  # every rank's rows have landed
-                self._mark("pack+dispatch", dev)
-                ops.experts_from_buffer(self._recv.local[buf], self._recv_rows, plan.data_ptr() + 17 * 4,
-                                        hidden.dtype, dev, self._symm.ptr_arrays[buf])
-                self._mark("experts+combine", dev)
-                dist.all_reduce(self._flag, group=self.group)  # every rank's GEMM2 has finished
-                self._mark("barrier", dev)
-                if side is not None:
-                    main = torch.cuda.current_stream(dev)
-                    main.wait_stream(side)
-                    shared_out.record_stream(main)
-                out = ops.combine_slots(self._symm.local[buf], tokens, topk, hidden.dtype, dev, shared_out)
-                self._mark("sum", dev)
-                return out
-            packed, counts_dev, inv = ops.plan_and_pack(hidden, topk_ids, topk_weights, self.world, self.rank)
-            self._mark("route+pack", dev)
-            send_counts, recv_counts = self._exchange_counts(counts_dev)
-            self.last_counts = (send_counts, recv_counts)
-            self._mark("counts", dev)
-            packed_r = self._all_to_all(packed, send_counts, recv_counts)
-            self._mark("dispatch", dev)
-            if use_p2p:
-                buf = self._step & 1
-                self._step += 1
-                ops.experts_packed(packed_r, hidden.dtype, self._symm.ptr_arrays[buf])
-                self._mark("experts+combine", dev)
-                # every rank's GEMM2 has finished once this stream-ordered collective completes
-                dist.all_reduce(self._flag, group=self.group)
-                self._mark("barrier", dev)
-            else:
-                y_r = ops.experts_packed(packed_r, hidden.dtype)
-                self._mark("experts", dev)
-                y = self._all_to_all(y_r, recv_counts, send_counts)
-                self._mark("combine_a2a", dev)
+            join_shared()
+            out = ops.combine(y, None, tokens, topk, shared_out)
+            self._mark("sum", dev)
+            return out
 
-        if side is not None:
-            main = torch.cuda.current_stream(hidden.device)
-            main.wait_stream(side)
-            shared_out.record_stream(main)
-        if self.world > 1 and use_p2p:
-            out = ops.combine_slots(self._symm.local[buf], tokens, topk, hidden.dtype, dev, shared_out)
+        if self.transport == "p2p":
+            # Device-driven step: no host wait, no payload through NCCL.  Ordering between ranks
+            # comes from the two collectives, which sit on the same stream as the kernels:
+            #  * the count all-gather completes on a rank only after every rank has launched it,
+            #    i.e. after every rank's pack kernel (and its peer stores) has finished;
+            #  * the barrier completes only after every rank's GEMM2 (and its peer stores) has.
+            # The same two facts protect the single receive / combine buffers across steps: a
+            # peer's pack of step k+1 follows its barrier of step k, which needs this rank to have
+            # queued that barrier behind its own reads of step k; a peer's GEMM2 of step k+1
+            # follows its all-gather of step k+1, which this rank queues behind its top-k sum of step k.
+            order, counts_dev = ops.route(topk_ids, self.world)
+            self._mark("route", dev)
+            ops.pack_to_peers(hidden, topk_ids, topk_weights, order, counts_dev, self.world, self.rank,
+                              self._recv.ptr_arrays[0], self.max_slots)
+            self._mark("pack+dispatch", dev)
+            dist.all_gather_into_tensor(self._counts_matrix, counts_dev.contiguous(), group=self.group)
+            self._mark("counts", dev)
+            ops.experts_from_buffer(self._recv.local[0], self.world, self.max_slots, self._counts_matrix, self.rank,
+                                    hidden.dtype, dev, self._symm.ptr_arrays[0], self.max_slots)
+            self._mark("experts+combine", dev)
+            dist.all_reduce(self._flag, group=self.group)  # every rank's GEMM2 has finished
+            self._mark("barrier", dev)
+            join_shared()
+            out = ops.combine_slots(self._symm.local[0], tokens, topk, hidden.dtype, dev, shared_out)
+            self._mark("sum", dev)
+            return out
+
+        packed, counts_dev, inv = ops.plan_and_pack(hidden, topk_ids, topk_weights, self.world, self.rank)
+        self._mark("route+pack", dev)
+        send_counts, recv_counts = self._exchange_counts(counts_dev)
+        self.last_counts = (send_counts, recv_counts)
+        self._mark("counts", dev)
+        packed_r = self._all_to_all(packed, send_counts, recv_counts)
+        self._mark("dispatch", dev)
+        if self.transport == "p2p_combine":
+            ops.experts_packed(packed_r, hidden.dtype, self._symm.ptr_arrays[0], self.max_slots)
+            self._mark("experts+combine", dev)
+            # every rank's GEMM2 has finished once this stream-ordered collective completes
+            dist.all_reduce(self._flag, group=self.group)
+            self._mark("barrier", dev)
+            join_shared()
+            out = ops.combine_slots(self._symm.local[0], tokens, topk, hidden.dtype, dev, shared_out)
         else:
+            y_r = ops.experts_packed(packed_r, hidden.dtype)
+            self._mark("experts", dev)
+            y = self._all_to_all(y_r, recv_counts, send_counts)
+            self._mark("combine_a2a", dev)
+            join_shared()
             out = ops.combine(y, inv, tokens, topk, shared_out)
         self._mark("sum", dev)
         return out
@@ -413,56 +450,57 @@ class ExpertParallelMoE:
     # -- CUDA-graph replay -------------------------------------------------------------------
     def capture(self, hidden: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> None:
         """Record the whole step (every kernel of this rank, the side-stream fork for the shared
-        expert and, with several ranks, the stream-ordered count exchange and barriers) into CUDA
-        graphs, so that a step costs the host one launch whatever the host is busy with.
+        expert and, with several ranks, the stream-ordered count all-gather and barrier) into one
+        CUDA graph, so that a step costs the host one launch whatever the host is busy with.
 
         The three tensors become the step's static inputs: write new values into them (``copy_``)
-        and call :meth:`replay`.  With several ranks two graphs are recorded, one per half of the
-        double-buffered peer buffers, and replayed alternately; every rank must call ``capture``
-        and ``replay`` the same number of times, and :meth:`release_graphs` before the process
-        group is destroyed.  Only the device-driven step can be recorded (the
-        all-to-all variant waits on the host for its counts)."""
+        and call :meth:`replay`.  With several ranks every rank must call ``capture`` and
+        ``replay`` the same number of times, and :meth:`close` (or :meth:`release_graphs`) before
+        the process group is destroyed.  Only the "p2p" transport can be recorded (the all-to-all
+        variants wait on the host for their counts)."""
         assert hidden.is_cuda, "graphs are a CUDA feature"
         dev = hidden.device
-        if self.world > 1:
-            tokens, topk = topk_ids.shape
-            assert (self._symm is not None and self._recv is not None and tokens * topk <= self._symm_rows
-                    and self.world * tokens * topk <= self._recv_rows), \
-                "only the peer-memory (device-driven) step can be recorded"
-        n_graphs = 2 if self.world > 1 else 1
+        assert self.world == 1 or self.transport == "p2p", "only the device-driven step can be recorded"
         self.trace = None
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):  # warm up off the default stream: lazy initialisation, allocator pools
-            for i in range(2 * n_graphs):
-                self.forward(hidden, topk_weights, topk_ids, _buf=i % n_graphs)
+            for _ in range(2):
+                self.forward(hidden, topk_weights, topk_ids)
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
-        self._graphs, self._graph_out = [], []
         launches0 = _cabi.launch_count()
-        for i in range(n_graphs):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, capture_error_mode="thread_local"):
-                out = self.forward(hidden, topk_weights, topk_ids, _buf=i)
-            self._graphs.append(g)
-            self._graph_out.append(out)
-        self.kernels_per_replay = (_cabi.launch_count() - launches0) // n_graphs
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, capture_error_mode="thread_local"):
+            out = self.forward(hidden, topk_weights, topk_ids)
+        self._graph, self._graph_out = g, out
+        self.kernels_per_replay = _cabi.launch_count() - launches0
         self._graph_inputs = (hidden, topk_weights, topk_ids)
-        self._replays = 0
 
     def release_graphs(self) -> None:
-        """Destroy the recorded graphs.  With several ranks this must happen before the process
-        group is destroyed: the graphs hold NCCL kernels, and NCCL does not let go of a communicator
-        while a graph that uses it exists (seen as both ranks sitting in ``destroy_process_group``)."""
-        if getattr(self, "_graphs", None):
+        """Destroy the recorded graph.  With several ranks this must happen before the process
+        group is destroyed: the graph holds NCCL kernels."""
+        if self._graph is not None:
             torch.cuda.synchronize()
-            self._graphs, self._graph_out, self._graph_inputs = [], [], None
+            self._graph, self._graph_out, self._graph_inputs = None, None, None
             torch.cuda.synchronize()
 
     def replay(self) -> torch.Tensor:
-        """One step from the recorded graph; returns the graph's static output tensor (overwritten by
-        the next replay of the same graph)."""
-        i = self._replays % len(self._graphs)
-        self._replays += 1
-        self._graphs[i].replay()
-        return self._graph_out[i]
+        """One step from the recorded graph; returns the graph's static output tensor (overwritten
+        by the next replay)."""
+        self._graph.replay()
+        return self._graph_out
+
+    def close(self) -> None:
+        """Collective, ordered teardown: graphs released, device idle, all ranks past their last
+        step, peer mappings closed on every rank, and only then the shared buffers freed.  After
+        it the process group may be destroyed."""
+        self.release_graphs()
+        if self._symm is None and self._recv is None:
+            return
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        for b in (self._recv, self._symm):
+            if b is not None:
+                b.close()
+        self._symm = self._recv = None

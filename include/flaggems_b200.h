@@ -40,9 +40,17 @@ int fg_version(void);
 const char* fg_last_error(void);
 
 /* Reads and clears the device-side status word of the current device (this call
- * synchronises the device).  *status is 0 when no kernel reported a bounded wait
- * that ran out.  Returns FG_OK, or FG_ERR_DEVICE_STATUS when *status != 0. */
+ * synchronises the device).  *status is 0 when no kernel reported a problem; otherwise
+ * (code << 16) | site of the first report: code 1 = a bounded wait ran out, code 2 = a row of
+ * the expert-parallel exchange was addressed outside its buffer and was dropped.
+ * Returns FG_OK, or FG_ERR_DEVICE_STATUS when *status != 0. */
 int fg_device_status(unsigned int* status);
+
+/* Failure-detection self-test (no counterpart in the reference): launches one thread that waits,
+ * with the same bounded wait every kernel of this library uses, on a barrier that nothing will
+ * ever complete.  The wait gives up after limit_ns (at most 100 ms), the kernel returns
+ * normally and fg_device_status() then reports (1 << 16) | site.  The context stays usable. */
+int fg_selftest_bounded_wait(int64_t limit_ns, int site, void* stream);
 
 /* Number of kernel launches issued by this library in the calling process. */
 uint64_t fg_launch_count(void);
@@ -125,6 +133,19 @@ int fg_moe_align_block_size_ex(const void* topk_ids, int ids_are_i64, int64_t nu
                                int64_t n_blocks, int32_t* num_post_pad, int64_t ids_stride, int id_div,
                                int32_t* expert_counts, const int32_t* numel_dev, void* stream);
 
+/* Same again for a slot range that is split into regions (no counterpart in the reference): the
+ * numel slots are numel / region_rows regions of region_rows slots, and only the first
+ * region_counts[s * region_stride] slots of region s hold rows (counts are clamped to
+ * [0, region_rows]); the other slots are skipped without being read.  This is the receive buffer
+ * of the expert-parallel layer, where every source rank owns one region.  region_rows == 0:
+ * no regions. */
+int fg_moe_align_block_size_regions(const void* topk_ids, int ids_are_i64, int64_t numel, int num_experts,
+                                    int block_size, const int32_t* expert_map, int expert_map_len,
+                                    int32_t* sorted_ids, int64_t max_pad, int32_t* expert_ids, int64_t n_blocks,
+                                    int32_t* num_post_pad, int64_t ids_stride, int id_div, int32_t* expert_counts,
+                                    const int32_t* numel_dev, int64_t region_rows, const int32_t* region_counts,
+                                    int64_t region_stride, void* stream);
+
 /* silu_and_mul_out / _silu_and_mul_kernel: src/flag_gems/fused/silu_and_mul.py:26-31,66-69,
  * src/flag_gems/fused/fused_moe.py:795-800.  out = dtype(x32/(1+exp(-x32)) * y32). */
 int fg_silu_and_mul(const void* x, const void* y, void* out, int64_t M, int64_t N, int64_t ld_x,
@@ -196,18 +217,19 @@ int fg_ep_pack_rows_fp8(const void* x, int x_dtype, int64_t T, int64_t K, int64_
                         void* packed, int64_t row_bytes, int32_t* inv, void* stream);
 
 /* Same, writing each packed row straight into the receive buffer of its destination rank over
- * NVLink peer memory (dispatch fused into the quantisation kernel): peer_rows[d] is rank d's
- * receive buffer, plan the geometry computed by fg_ep_plan.  plan == NULL: as above. */
+ * NVLink peer memory (dispatch fused into the quantisation kernel).  send_counts[d] (device) is
+ * the number of rows for rank d, rows being in send order with destinations ascending;
+ * peer_rows[d] is rank d's receive buffer, in which this rank owns rows
+ * [home_rank * region_rows, (home_rank + 1) * region_rows): the k-th row for rank d lands at row
+ * home_rank * region_rows + k there, so a rank needs nobody else's counts to send.  A row that
+ * would fall outside its region is not stored and the device status word is set (code 2).
+ * send_counts == NULL: as above (rows go to `packed`). */
 int fg_ep_pack_rows_fp8_peer(const void* x, int x_dtype, int64_t T, int64_t K, int64_t ld_x,
                              const void* topk_ids, int ids_are_i64, const void* topk_w,
                              int topk_w_dtype, int topk, int experts_per_rank, int home_rank,
                              const int32_t* order, void* packed, int64_t row_bytes, int32_t* inv,
-                             const int32_t* plan, void* const* peer_rows, int world, void* stream);
-
-/* From counts[src*world + dst] (rows rank src sends to rank dst, gathered from all ranks) writes
- * this rank's plan (18 int32): [0..world] first send-order row per destination, [9+d] first row
- * of this rank's block in d's receive buffer, [17] rows this rank receives. */
-int fg_ep_plan(const int32_t* counts, int world, int rank, int32_t* plan, void* stream);
+                             const int32_t* send_counts, void* const* peer_rows, int world,
+                             int64_t region_rows, void* stream);
 
 /* Bytes of workspace the two functions below need for n_rows_in routed rows. */
 int64_t fg_moe_routed_workspace_bytes(int64_t n_rows_in, int num_experts, int64_t H, int64_t I);
@@ -248,16 +270,23 @@ int fg_moe_routed_block_fp8_local_noalloc(void* y, const void* hidden, int hidde
  * GEMM2's epilogue, which stores each result row straight into the home rank's buffer
  * peer_out[home rank] at row (route slot), over NVLink peer memory; the home rank may read its
  * buffer once every rank's call has completed (a stream-ordered barrier or collective).
- * n_rows_dev (nullable): device-side row count; R is then the capacity of `rows`. */
+ * peer_rows is the number of rows each peer_out buffer holds: a row whose trailer names a home
+ * rank or slot outside the buffers is dropped and the device status word is set (code 2).
+ * n_rows_dev (nullable): device-side row count; R is then the capacity of `rows`.
+ * region_rows > 0: `rows` is split into R / region_rows regions as in
+ * fg_moe_align_block_size_regions (region_counts, region_stride). */
 int fg_moe_routed_block_fp8_packed(void* y, const void* rows, int64_t R, int64_t row_bytes,
                                    const void* w1, const void* w2, const float* s1, const float* s2,
                                    int num_experts, int64_t H, int64_t I, void* workspace,
                                    int64_t workspace_bytes, int out_dtype, void* const* peer_out,
-                                   int n_peers, const int32_t* n_rows_dev, void* stream);
+                                   int n_peers, int64_t peer_rows, const int32_t* n_rows_dev,
+                                   int64_t region_rows, const int32_t* region_counts,
+                                   int64_t region_stride, void* stream);
 
 /* fg_moe_grouped_gemm_fp8 with the peer scatter described above: with scatter != 0 and
  * n_peers > 0, row r (arrival index sid = sorted_ids[r]) goes to peer_out[dest[sid*dest_stride+1]]
- * at row dest[sid*dest_stride]. */
+ * at row dest[sid*dest_stride], provided that rank is below n_peers and the row below peer_rows
+ * (otherwise the row is dropped and the device status word is set, code 2). */
 int fg_moe_grouped_gemm_fp8_peer(void* c, const void* a, const void* w, const float* a_scale,
                                  const float* w_scale, const void* topk_weights, int topk_w_dtype,
                                  int64_t topk_w_stride, const int32_t* sorted_ids,
@@ -267,7 +296,7 @@ int fg_moe_grouped_gemm_fp8_peer(void* c, const void* a, const void* w, const fl
                                  int scale_mode, int a_scale_per_row, int fuse_silu, int scatter,
                                  int mul_weight, int out_dtype, const int32_t* dest,
                                  int64_t dest_stride, void* const* peer_out, int n_peers,
-                                 void* stream);
+                                 int64_t peer_rows, void* stream);
 
 /* Buffers visible to every rank of one node (set-up time only; these four are the only entry
  * points that allocate or free device memory).  fg_symm_alloc: cudaMalloc + a 64-byte CUDA IPC

@@ -33,6 +33,8 @@ from .moe import (  # noqa: F401
     moe_align_block_size,
     silu_and_mul,
     moe_sum,
+    expert_rows_block_fp8,
+    expert_rows_per_channel_fp8,
     fused_moe_block_fp8,
     fused_moe_per_channel_fp8,
     fused_moe_per_tensor_fp8,

@@ -79,6 +79,50 @@ def _silu_mul_f32(z: torch.Tensor, fuse_silu: bool, dtype: torch.dtype) -> torch
     return (g / (1.0 + torch.exp(-g)) * u).to(dtype)
 
 
+def expert_rows_block_fp8(
+    rows: torch.Tensor,
+    w1_e: torch.Tensor,
+    w2_e: torch.Tensor,
+    s1_e: torch.Tensor,
+    s2_e: torch.Tensor,
+    weights: torch.Tensor,
+    block: int = 128,
+    fuse_silu: bool = True,
+    return_intermediate: bool = False,
+):
+    """One expert of the block-FP8 layer applied to the rows routed to it: the loop body of
+    ``fused_moe_block_fp8`` below (tests/test_fused_experts_impl.py:604-662 with the device
+    path's fp32 router-weight multiply, src/flag_gems/fused/fused_moe.py:1485-1493).
+    rows [R, H] bf16/fp16, weights [R]; returns [R, H_out] in the rows' dtype (and the
+    activation [R, I] after SiLU*up when asked)."""
+    hq, hs = per_token_group_quant_fp8(rows, block)
+    z = block_scaled_mm(hq, w1_e, hs, s1_e, block, block, torch.float32)
+    act = _silu_mul_f32(z, fuse_silu, rows.dtype)
+    aq, asc = per_token_group_quant_fp8(act, block)
+    r = block_scaled_mm(aq, w2_e, asc, s2_e, block, block, torch.float32)
+    r = (r * weights.float().reshape(-1, 1)).to(rows.dtype)
+    return (r, act) if return_intermediate else r
+
+
+def expert_rows_per_channel_fp8(
+    rows: torch.Tensor,
+    w1_e: torch.Tensor,
+    w2_e: torch.Tensor,
+    s1_e: torch.Tensor,
+    s2_e: torch.Tensor,
+    weights: torch.Tensor,
+    fuse_silu: bool = True,
+) -> torch.Tensor:
+    """One expert of the per-token x per-channel FP8 layer on the rows routed to it (loop body
+    of ``fused_moe_per_channel_fp8`` below; same "parity unpinned" status)."""
+    hq, hs = per_token_quant_fp8(rows)
+    z = torch.mm(hq.float(), w1_e.float().t()) * hs * s1_e.float().reshape(1, -1)
+    act = _silu_mul_f32(z, fuse_silu, rows.dtype)
+    aq, asc = per_token_quant_fp8(act)
+    r = torch.mm(aq.float(), w2_e.float().t()) * asc * s2_e.float().reshape(1, -1)
+    return (r * weights.float().reshape(-1, 1)).to(rows.dtype)
+
+
 def fused_moe_block_fp8(
     hidden: torch.Tensor,
     w1: torch.Tensor,

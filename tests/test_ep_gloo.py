@@ -195,3 +195,136 @@ def test_single_rank_layer_with_oracle_ops():
     hidden, w1, w2, s1, s2, tw, ti, shared = case
     layer = ExpertParallelMoE(w1, w2, s1, s2, 4, ops=OracleOps(w1, w2, s1, s2, shared))
     assert torch.equal(layer(hidden, tw, ti), expected(case))
+
+
+# ---- unequal token counts, refusals and host-side failures ---------------------------------------
+def _uneven_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from flaggems_b200.ep import ExpertParallelMoE
+
+        case = make_case(seed=11)
+        hidden, w1, w2, s1, s2, tw, ti, shared = case
+        e = w1.shape[0]
+        el = e // world
+        lo = rank * el
+        ops = OracleOps(w1[lo:lo + el], w2[lo:lo + el], s1[lo:lo + el], s2[lo:lo + el], shared)
+        layer = ExpertParallelMoE(w1[lo:lo + el], w2[lo:lo + el], s1[lo:lo + el], s2[lo:lo + el], e, rank, world,
+                                  ops=ops)
+        sl = slice(0, 30) if rank == 0 else slice(30, 48)  # 30 and 18 tokens
+        paths = []
+        for _ in range(2):
+            out = layer(hidden[sl].contiguous(), tw[sl].contiguous(), ti[sl].contiguous())
+            paths.append(layer.transport)
+        ref = expected(case)[sl]
+        q.put((rank, bool(torch.equal(out, ref)), paths))
+        layer.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_unequal_token_counts_take_the_same_path_on_every_rank():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_uneven_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=240) for _ in range(world))
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0, "a rank did not exit cleanly after close()"
+    assert res[0][2] == res[1][2], "ranks chose different transports"
+    assert all(r[1] for r in res)
+
+
+def _failing_worker(rank, world, port, q, mode):
+    import datetime
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    from flaggems_b200.ep import ExpertParallelMoE
+
+    case = make_case(seed=12)
+    hidden, w1, w2, s1, s2, tw, ti, shared = case
+    e = w1.shape[0]
+    el = e // world
+    lo = rank * el
+    ops = OracleOps(w1[lo:lo + el], w2[lo:lo + el], s1[lo:lo + el], s2[lo:lo + el], shared)
+    try:
+        if mode == "world_mismatch":
+            ExpertParallelMoE(w1[:2], w2[:2], s1[:2], s2[:2], e, rank, 4, ops=ops)
+            q.put((rank, "no error"))
+            return
+        layer = ExpertParallelMoE(w1[lo:lo + el], w2[lo:lo + el], s1[lo:lo + el], s2[lo:lo + el], e, rank, world,
+                                  ops=ops)
+        sl = slice(rank * 24, (rank + 1) * 24)
+        if mode == "rank_raises" and rank == 1:
+            raise RuntimeError("rank 1 fails before the step")
+        if mode == "wrong_counts" and rank == 1:
+            # this rank announces counts that do not add up to the rows it sends
+            real = layer._exchange_counts
+
+            def lying(send_counts_dev):
+                send, recv = real(send_counts_dev)
+                send[0] += 3
+                return send, recv
+
+            layer._exchange_counts = lying
+        layer(hidden[sl].contiguous(), tw[sl].contiguous(), ti[sl].contiguous())
+        q.put((rank, "no error"))
+    except Exception as exc:  # noqa: BLE001 - the test asserts on what each rank saw
+        q.put((rank, type(exc).__name__))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:  # noqa: BLE001
+            pass
+
+
+@pytest.mark.timeout(120)
+@pytest.mark.parametrize("mode", ["world_mismatch", "rank_raises", "wrong_counts"])
+def test_host_side_failures_end_in_exceptions_not_hangs(mode):
+    """Failures made on the host (never on a device): a layer built for another world size, a rank
+    that raises before the step, a rank whose announced counts are wrong.  Every rank must come
+    back with an exception within the process group's (shortened) timeout."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_worker, args=(r, world, port, q, mode)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=60) for _ in range(world))
+    for p in procs:
+        p.join(30)
+        if p.is_alive():
+            p.kill()
+            pytest.fail("a rank hung after the failure")
+    if mode == "world_mismatch":
+        assert res == {0: "ValueError", 1: "ValueError"}
+    elif mode == "rank_raises":
+        assert res[1] == "RuntimeError" and res[0] != "no error"
+    else:
+        assert res[0] != "no error" or res[1] != "no error"
+
+
+def test_step_beyond_capacity_is_refused_before_any_collective():
+    """With a peer-memory transport a step with more route slots than max_slots_per_rank raises at
+    once; no process group exists here, so reaching any collective would fail differently."""
+    from flaggems_b200.ep import ExpertParallelMoE
+
+    case = make_case(seed=3, t=20, e=4, topk=2)
+    hidden, w1, w2, s1, s2, tw, ti, shared = case
+    layer = ExpertParallelMoE(w1, w2, s1, s2, 4, ops=OracleOps(w1, w2, s1, s2, shared))
+    layer.world, layer.transport, layer.max_slots = 2, "p2p", 39
+    with pytest.raises(ValueError, match="exceed max_slots_per_rank"):
+        layer(hidden, tw, ti)
+    layer.max_slots = 40
+    with pytest.raises(TypeError, match="bf16 or fp16"):
+        layer(hidden.float(), tw, ti)

@@ -6,6 +6,7 @@ import torch
 
 import flag_gems
 import oracle
+from tests._isolated import check_isolated
 from flaggems_b200 import _cabi
 
 pytestmark = pytest.mark.gpu
@@ -81,10 +82,51 @@ def test_moe_align_out_param_and_vllm_op():
     no = torch.empty(1, dtype=torch.int32, device="cuda")
     flag_gems.moe_align_block_size_triton(ids.cuda(), 60, 32, so, eo, no)
     assert torch.equal(so.cpu(), sr) and torch.equal(eo.cpu(), er) and torch.equal(no.cpu(), nr)
-    flag_gems.patch_empty_vllm()
-    so.fill_(-7), eo.fill_(-7)
-    torch.ops._moe_C.moe_align_block_size(ids.cuda(), 60, 32, so, eo, no)
-    assert torch.equal(so.cpu(), sr) and torch.equal(eo.cpu(), er) and torch.equal(no.cpu(), nr)
+
+
+def test_moe_align_short_buffers_for_decode_batches():
+    """Fewer route slots than experts: at most numel experts are non-empty, so buffers of
+    numel * block_size entries (what a caller sizes for decode batches) are enough."""
+    ids = torch.tensor([[3, 17], [40, 3]], dtype=torch.int32)
+    numel, bs, e = 4, 16, 64
+    so = torch.full((numel * bs,), -7, dtype=torch.int32, device="cuda")
+    eo = torch.full((numel,), -7, dtype=torch.int32, device="cuda")
+    no = torch.empty(1, dtype=torch.int32, device="cuda")
+    flag_gems.moe_align_block_size_triton(ids.cuda(), e, bs, so, eo, no)
+    sr, er, nr = oracle.moe_align_block_size(ids, bs, e)
+    assert int(no) == int(nr) == 48
+    assert torch.equal(so.cpu()[:48], sr[:48]) and torch.equal(eo.cpu()[:3], er[:3])
+    assert bool((so.cpu()[48:] == numel).all()) and int(eo.cpu()[3]) == -1
+    with pytest.raises(AssertionError):
+        flag_gems.moe_align_block_size_triton(ids.cuda(), e, bs, so[:40], eo, no)
+
+
+def test_vllm_moe_ops_defined_by_patch_empty_vllm():
+    """torch.ops._moe_C.* as patch_empty_vllm() defines them, in a process of their own."""
+    check_isolated('''
+import torch, flag_gems, oracle
+flag_gems.patch_empty_vllm()
+g = torch.Generator().manual_seed(8)
+ids = torch.randint(0, 60, (513, 6), generator=g, dtype=torch.int32)
+sr, er, nr = oracle.moe_align_block_size(ids, 32, 60)
+so = torch.full_like(sr, -7, device="cuda"); eo = torch.full_like(er, -7, device="cuda")
+no = torch.empty(1, dtype=torch.int32, device="cuda")
+torch.ops._moe_C.moe_align_block_size(ids.cuda(), 60, 32, so, eo, no)
+assert torch.equal(so.cpu(), sr) and torch.equal(eo.cpu(), er) and torch.equal(no.cpu(), nr)
+x = torch.randn(33, 2, 4096).bfloat16()
+out = torch.empty(33, 4096, dtype=torch.bfloat16, device="cuda")
+torch.ops._moe_C.moe_sum(x.cuda(), out)
+assert torch.equal(out.cpu(), oracle.moe_sum(x))
+gate = torch.randn(64, 32)
+w = torch.empty(64, 4, device="cuda"); i = torch.empty(64, 4, dtype=torch.int32, device="cuda")
+src = torch.empty(64, 4, dtype=torch.int32, device="cuda")
+torch.ops._moe_C.topk_softmax(w, i, src, gate.cuda(), True)
+rw, ri, rs = oracle.topk_softmax(gate, 4, True, torch.int64)
+assert torch.equal(i.cpu().long(), ri) and torch.allclose(w.cpu(), rw, atol=1e-5)
+v, gi = torch.ops._moe_C.grouped_topk(gate.cuda(), 4, 2, 4, True, 1.0, torch.zeros(32, device="cuda"), 0)
+rv, rgi = oracle.grouped_topk(gate, 4, 2, 4, True, 1.0, torch.zeros(32), 0)
+assert torch.equal(gi.cpu(), rgi) and torch.allclose(v.cpu(), rv, atol=1e-5)
+''')
 
 
 def test_moe_align_deterministic():

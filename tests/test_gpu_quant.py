@@ -6,6 +6,7 @@ import torch
 
 import flag_gems
 import oracle
+from tests._isolated import check_isolated
 from flaggems_b200 import _cabi
 
 pytestmark = pytest.mark.gpu
@@ -190,15 +191,27 @@ def test_per_tensor_quant(golden_dir):
 
 
 def test_vllm_op_writes_in_place():
-    flag_gems.patch_empty_vllm()
-    torch.manual_seed(5)
-    x = torch.randn(33, 512).bfloat16()
-    q = torch.empty(33, 512, dtype=torch.float8_e4m3fn, device="cuda")
-    s = torch.empty(4, 33, dtype=torch.float32, device="cuda").t()
-    torch.ops._C.per_token_group_fp8_quant(x.cuda(), q, s, 128, 1e-10, -448.0, 448.0, False)
-    qr, sr = oracle.per_token_group_quant_fp8(x, 128)
-    assert torch.equal(_bits(s.cpu().contiguous()), _bits(sr))
-    _assert_bytes_equal(q, qr)
+    """torch.ops._C.per_token_group_fp8_quant / cutlass_scaled_mm as patch_empty_vllm() defines
+    them (in a process of their own: the registrations must not reach later tests)."""
+    check_isolated('''
+import torch, flag_gems, oracle
+flag_gems.patch_empty_vllm()
+torch.manual_seed(5)
+x = torch.randn(33, 512).bfloat16()
+q = torch.empty(33, 512, dtype=torch.float8_e4m3fn, device="cuda")
+s = torch.empty(4, 33, dtype=torch.float32, device="cuda").t()
+torch.ops._C.per_token_group_fp8_quant(x.cuda(), q, s, 128, 1e-10, -448.0, 448.0, False)
+qr, sr = oracle.per_token_group_quant_fp8(x, 128)
+assert torch.equal(s.cpu().contiguous().view(torch.int32), sr.view(torch.int32))
+assert torch.equal(q.cpu().view(torch.uint8), qr.view(torch.uint8))
+w = torch.randn(256, 512) * 0.02
+wq, sw = oracle.quantize_weight_per_channel(w)
+aq, sa = oracle.per_token_quant_fp8(x)
+c = torch.empty(33, 256, dtype=torch.bfloat16, device="cuda")
+torch.ops._C.cutlass_scaled_mm(c, aq.cuda(), wq.cuda().t(), sa.cuda().view(-1), sw.cuda(), None)
+ref = oracle.scaled_mm(aq, wq.t(), sa, sw)
+torch.testing.assert_close(c.cpu().float(), ref.float(), rtol=1e-2, atol=1e-2)
+''')
 
 
 def test_no_device_errors_recorded():
