@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libflaggems_b200.so")
 
 FG_OK = 0
 DTYPE_CODE = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+DTYPE_E4M3 = 3  # output of fg_scaled_mm_fp8 only
 SCALE_SCALAR, SCALE_VECTOR, SCALE_BLOCK = 0, 1, 2
 
 _P = c_void_p

@@ -51,6 +51,7 @@ struct GemmParams {
     void* c;
     int64_t ld_c;
     int out_dtype;
+    int bias_dtype;  // element type of bias (the output type, or fp32 when the output is e4m3)
     int c_vec_ok;  // rows of C are 16-byte aligned
     const float* sa;
     const float* sb;
@@ -133,6 +134,10 @@ __device__ __forceinline__ float round_through(float v, int dtype) {
     return v;
 }
 
+__host__ __device__ __forceinline__ int out_elem_size(int dtype) {
+    return dtype == FG_DTYPE_F32 ? 4 : (dtype == FG_DTYPE_E4M3 ? 1 : 2);
+}
+
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
 // Stores 32 consecutive output values of one row; ncols (<= 32) of them are in range.
@@ -148,6 +153,26 @@ __device__ __forceinline__ void store_chunk(void* row_ptr, int col0, const float
 #pragma unroll
             for (int i = 0; i < 32; ++i)
                 if (i < ncols) o[i] = v[i];
+        }
+        return;
+    }
+    if (dtype == FG_DTYPE_E4M3) {
+        // round to nearest even, saturating at +-448 (cvt.rn.satfinite.e4m3x2.f32)
+        uint32_t b[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * i], v[4 * i + 1]), __NV_SATFINITE, __NV_E4M3);
+            const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * i + 2], v[4 * i + 3]), __NV_SATFINITE, __NV_E4M3);
+            b[i] = lo | (hi << 16);
+        }
+        uint8_t* o = reinterpret_cast<uint8_t*>(row_ptr) + col0;
+        if (vec_ok && ncols == 32) {
+            reinterpret_cast<uint4*>(o)[0] = make_uint4(b[0], b[1], b[2], b[3]);
+            reinterpret_cast<uint4*>(o)[1] = make_uint4(b[4], b[5], b[6], b[7]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (i < ncols) o[i] = (uint8_t)((b[i >> 2] >> (8 * (i & 3))) & 0xffu);
         }
         return;
     }
@@ -473,7 +498,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             } else {
                 row_ok = row < p.M;
             }
-            const int esz = p.out_dtype == FG_DTYPE_F32 ? 4 : 2;
+            const int esz = out_elem_size(p.out_dtype);
             uint8_t* out_base = reinterpret_cast<uint8_t*>(p.c);
             if (p.n_peers > 0 && p.grouped && p.scatter && row_ok) {
                 const int32_t* d = p.dest + out_row * p.dest_stride;
@@ -551,7 +576,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                             float x = sb * (sa * __uint_as_float(raw[i]));
                             x *= weight;
                             if (p.bias) {
-                                const float b = load_as_float(p.bias, p.out_dtype, n);
+                                const float b = load_as_float(p.bias, p.bias_dtype, n);
                                 x = p.bias_after_round ? round_through(x, p.out_dtype) + b : x + b;
                             }
                             v[i] = x;
@@ -693,7 +718,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             const int width = BN / k_slices;            // columns this CTA finishes (multiple of 4)
             const int c_first = (int)cluster.block_rank() * width;
             const int vec_per_row = width / 4;
-            const int esz = p.out_dtype == FG_DTYPE_F32 ? 4 : 2;
+            const int esz = out_elem_size(p.out_dtype);
             const float* part[8];
             for (int q = 0; q < k_slices; ++q)
                 part[q] = cluster.map_shared_rank(reinterpret_cast<float*>(smem), q);
@@ -715,7 +740,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                         const float sb = p.sb_mode == FG_SCALE_VECTOR ? __ldg(p.sb + n) : p.sb[0];
                         float x = sb * (sa * o[i]);
                         if (p.bias) {
-                            const float b = load_as_float(p.bias, p.out_dtype, n);
+                            const float b = load_as_float(p.bias, p.bias_dtype, n);
                             x = p.bias_after_round ? round_through(x, p.out_dtype) + b : x + b;
                         }
                         o[i] = x;
@@ -727,6 +752,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     if (n0 + c + i >= p.n_out) break;
                     if (p.out_dtype == FG_DTYPE_BF16) reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(o[i]);
                     else if (p.out_dtype == FG_DTYPE_F16) reinterpret_cast<__half*>(out)[i] = __float2half_rn(o[i]);
+                    else if (p.out_dtype == FG_DTYPE_E4M3)
+                        out[i] = (uint8_t)(__nv_cvt_float2_to_fp8x2(make_float2(o[i], 0.0f), __NV_SATFINITE, __NV_E4M3) & 0xffu);
                     else reinterpret_cast<float*>(out)[i] = o[i];
                 }
             }
@@ -923,7 +950,8 @@ int launch_gemm(GemmParams& p, const void* a, int64_t a_rows, int64_t ld_a, cons
                FG_ERR_UNSUPPORTED, "a and b must be 16-byte aligned with row strides that are multiples of 16 bytes");
     FG_REQUIRE(ld_a >= p.K && ld_b >= p.K, FG_ERR_INVALID_ARGUMENT, "row stride smaller than K");
     p.status = fg_status_word_device_ptr();
-    const int esz = p.out_dtype == FG_DTYPE_F32 ? 4 : 2;
+    if (p.out_dtype != FG_DTYPE_E4M3) p.bias_dtype = p.out_dtype;
+    const int esz = out_elem_size(p.out_dtype);
     p.c_vec_ok = ((uintptr_t)p.c % 16 == 0) && ((p.ld_c * esz) % 16 == 0);
 
     const int64_t m_tiles = p.grouped ? a_rows / p.block_rows : fg_cdiv(p.M, BLOCK_M);
@@ -1051,7 +1079,7 @@ int fg_scaled_mm_fp8(void* c, const void* a, const void* b, const float* sa, con
     FG_REQUIRE(M >= 0 && N >= 0 && K >= 0, FG_ERR_INVALID_ARGUMENT, "negative size");
     if (M == 0 || N == 0) return FG_OK;
     FG_REQUIRE(c && a && b && sa && sb, FG_ERR_INVALID_ARGUMENT, "null pointer");
-    FG_REQUIRE(dtype_ok(out_dtype), FG_ERR_INVALID_ARGUMENT, "bad out_dtype %d", out_dtype);
+    FG_REQUIRE(dtype_ok(out_dtype) || out_dtype == FG_DTYPE_E4M3, FG_ERR_INVALID_ARGUMENT, "bad out_dtype %d", out_dtype);
     FG_REQUIRE((sa_mode == FG_SCALE_SCALAR || sa_mode == FG_SCALE_VECTOR) &&
                    (sb_mode == FG_SCALE_SCALAR || sb_mode == FG_SCALE_VECTOR),
                FG_ERR_INVALID_ARGUMENT, "scale modes must be scalar or vector");
@@ -1061,6 +1089,7 @@ int fg_scaled_mm_fp8(void* c, const void* a, const void* b, const float* sa, con
     p.c = c; p.ld_c = ld_c; p.out_dtype = out_dtype;
     p.sa = sa; p.sb = sb; p.bias = bias; p.sa_mode = sa_mode; p.sb_mode = sb_mode;
     p.bias_after_round = bias_after_round;
+    p.bias_dtype = FG_DTYPE_F32;  // used when the output is e4m3; otherwise the bias has the output type
     p.block_rows = BLOCK_M;
     return launch_gemm(p, a, M, ld_a, b, 1, ld_b, false, false, (cudaStream_t)stream);
 }

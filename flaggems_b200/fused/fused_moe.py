@@ -23,7 +23,7 @@ from .moe_align_block_size import ceil_div, moe_align_block_size
 from .moe_sum import moe_sum
 from .silu_and_mul import silu_and_mul_out
 
-logger = logging.getLogger(__name__)
+logger = logging.getLogger(__name__.replace("flaggems_b200", "flag_gems", 1))
 
 # Rows per grouped-GEMM tile; moe_align_block_size is run with this block size inside
 # the layer (the public moe_align_block_size accepts any block size).
@@ -381,13 +381,68 @@ def dispatch_fused_moe_kernel(A, B, C, A_scale, B_scale, B_zp, topk_weights, sor
                                    block_shape, B_bias, FUSE_SILU=FUSE_SILU, direct_sum=direct_sum, out_top_k=out_top_k)
 
 
-def inplace_fused_experts(hidden_states, w1, w2, topk_weights, topk_ids, **kwargs) -> None:
-    """Same semantics as ``fused_experts_impl(..., inplace=True)`` (reference :2188-2238)."""
-    kwargs.pop("inplace", None)
-    fused_experts_impl(hidden_states, w1, w2, topk_weights, topk_ids, inplace=True, **kwargs)
+def inplace_fused_experts(
+    hidden_states: torch.Tensor,
+    w1: torch.Tensor,
+    w2: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    activation: str = "silu",
+    apply_router_weight_on_input: bool = False,
+    use_fp8_w8a8: bool = False,
+    use_int8_w8a8: bool = False,
+    use_int8_w8a16: bool = False,
+    use_int4_w4a16: bool = False,
+    per_channel_quant: bool = False,
+    global_num_experts: int = -1,
+    w1_scale: Optional[torch.Tensor] = None,
+    w2_scale: Optional[torch.Tensor] = None,
+    a1_scale: Optional[torch.Tensor] = None,
+    a2_scale: Optional[torch.Tensor] = None,
+    block_shape: Optional[list] = None,
+    w1_bias: Optional[torch.Tensor] = None,
+    w2_bias: Optional[torch.Tensor] = None,
+) -> None:
+    """``fused_experts_impl(..., inplace=True)``: the result replaces ``hidden_states``; returns
+    None.  Positional order and defaults are the reference's (fused_moe.py:2188-2238), which a
+    custom-op registration binds positionally."""
+    fused_experts_impl(
+        hidden_states, w1, w2, topk_weights, topk_ids, inplace=True, activation=activation,
+        apply_router_weight_on_input=apply_router_weight_on_input, use_fp8_w8a8=use_fp8_w8a8,
+        use_int8_w8a8=use_int8_w8a8, use_int8_w8a16=use_int8_w8a16, use_int4_w4a16=use_int4_w4a16,
+        per_channel_quant=per_channel_quant, global_num_experts=global_num_experts, w1_scale=w1_scale,
+        w2_scale=w2_scale, a1_scale=a1_scale, a2_scale=a2_scale, block_shape=block_shape, w1_bias=w1_bias,
+        w2_bias=w2_bias)
 
 
-def outplace_fused_experts(hidden_states, w1, w2, topk_weights, topk_ids, **kwargs) -> torch.Tensor:
-    """Same semantics as ``fused_experts_impl(..., inplace=False)`` (reference :2241-2290)."""
-    kwargs.pop("inplace", None)
-    return fused_experts_impl(hidden_states, w1, w2, topk_weights, topk_ids, inplace=False, **kwargs)
+def outplace_fused_experts(
+    hidden_states: torch.Tensor,
+    w1: torch.Tensor,
+    w2: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    activation: str = "silu",
+    apply_router_weight_on_input: bool = False,
+    use_fp8_w8a8: bool = False,
+    use_int8_w8a8: bool = False,
+    use_int8_w8a16: bool = False,
+    use_int4_w4a16: bool = False,
+    per_channel_quant: bool = False,
+    global_num_experts: int = -1,
+    w1_scale: Optional[torch.Tensor] = None,
+    w2_scale: Optional[torch.Tensor] = None,
+    a1_scale: Optional[torch.Tensor] = None,
+    a2_scale: Optional[torch.Tensor] = None,
+    block_shape: Optional[list] = None,
+    w1_bias: Optional[torch.Tensor] = None,
+    w2_bias: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """``fused_experts_impl(..., inplace=False)``: returns a new tensor (reference
+    fused_moe.py:2241-2290, same positional order and defaults)."""
+    return fused_experts_impl(
+        hidden_states, w1, w2, topk_weights, topk_ids, inplace=False, activation=activation,
+        apply_router_weight_on_input=apply_router_weight_on_input, use_fp8_w8a8=use_fp8_w8a8,
+        use_int8_w8a8=use_int8_w8a8, use_int8_w8a16=use_int8_w8a16, use_int4_w4a16=use_int4_w4a16,
+        per_channel_quant=per_channel_quant, global_num_experts=global_num_experts, w1_scale=w1_scale,
+        w2_scale=w2_scale, a1_scale=a1_scale, a2_scale=a2_scale, block_shape=block_shape, w1_bias=w1_bias,
+        w2_bias=w2_bias)

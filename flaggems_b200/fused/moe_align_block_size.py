@@ -11,7 +11,7 @@ import torch
 
 from .. import _cabi
 
-logger = logging.getLogger(__name__)
+logger = logging.getLogger(__name__.replace("flaggems_b200", "flag_gems", 1))
 
 
 def ceil_div(a, b):

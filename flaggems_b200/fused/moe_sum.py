@@ -8,7 +8,7 @@ import torch
 
 from .. import _cabi
 
-logger = logging.getLogger(__name__)
+logger = logging.getLogger(__name__.replace("flaggems_b200", "flag_gems", 1))
 
 
 def moe_sum(input: torch.Tensor, output: torch.Tensor):

@@ -10,7 +10,7 @@ import torch
 
 from .. import _cabi
 
-logger = logging.getLogger(__name__)
+logger = logging.getLogger(__name__.replace("flaggems_b200", "flag_gems", 1))
 
 _INDEX_KIND = {torch.int32: 0, torch.uint32: 1, torch.int64: 2}
 

@@ -9,7 +9,7 @@ import torch
 
 from .w8a8_block_fp8_matmul import w8a8_block_fp8_matmul
 
-logger = logging.getLogger(__name__)
+logger = logging.getLogger(__name__.replace("flaggems_b200", "flag_gems", 1))
 
 
 def fp8_matmul(a, a_s, b, b_s, scale_dtype: torch.dtype = torch.float32) -> torch.Tensor:

@@ -2,7 +2,10 @@
 
 Mirrors src/flag_gems/ops/scaled_mm.py:213-452 of the reference: same argument
 normalisation and error messages; the product itself is ``fg_scaled_mm_fp8`` with the
-bias added in fp32 before the output cast (reference kernel :116-136).
+bias added in fp32 before the output cast (reference kernel :116-136).  ``out_dtype=None``
+resolves to the operands' dtype (:214-220): the result is then FP8 e4m3, rounded to nearest
+even and saturated at +-448 (the conversion the reference's ``tl.store`` of an fp32 tile to an
+fp8 pointer performs on NVIDIA hardware).
 """
 import logging
 
@@ -10,7 +13,7 @@ import torch
 
 from .. import _cabi
 
-logger = logging.getLogger(__name__)
+logger = logging.getLogger(__name__.replace("flaggems_b200", "flag_gems", 1))
 
 SCALAR_SCALE = 0
 VECTOR_SCALE = 1
@@ -81,8 +84,9 @@ def _scaled_mm_impl(self, mat2, scale_a, scale_b, bias, out_dtype, out):
     _cabi.require_cuda(self, mat2, scale_a, scale_b, bias, out)
     if self.dtype != torch.float8_e4m3fn:
         raise NotImplementedError(f"_scaled_mm is implemented for float8_e4m3fn operands only, got {self.dtype}")
-    if output_dtype not in _cabi.DTYPE_CODE:
-        raise NotImplementedError(f"_scaled_mm output dtype {output_dtype} is not supported (bf16/fp16/fp32)")
+    fp8_out = output_dtype == torch.float8_e4m3fn
+    if output_dtype not in _cabi.DTYPE_CODE and not fp8_out:
+        raise NotImplementedError(f"_scaled_mm output dtype {output_dtype} is not supported (e4m3/bf16/fp16/fp32)")
     if scale_a.dtype != torch.float32 or scale_b.dtype != torch.float32:
         scale_a, scale_b = scale_a.float(), scale_b.float()
     # The tensor-core path reads both operands K-contiguous; lay them out that way if needed.
@@ -90,15 +94,19 @@ def _scaled_mm_impl(self, mat2, scale_a, scale_b, bias, out_dtype, out):
         self = self.contiguous()
     if mat2.stride(0) != 1 or mat2.stride(1) % 16 != 0:
         mat2 = mat2.t().contiguous().t()
-    if bias is not None and bias.dtype != output_dtype:
-        bias = bias.to(output_dtype)
+    # The kernel reads the bias in the output type; with an FP8 output (out_dtype=None resolves to
+    # the operands' type, reference :214-220) it reads fp32 and adds it before the saturating cast.
+    bias_dtype = torch.float32 if fp8_out else output_dtype
+    if bias is not None and bias.dtype != bias_dtype:
+        bias = bias.to(bias_dtype)
     dst = out if out.stride(1) == 1 else torch.empty((m, n), dtype=output_dtype, device=out.device)
     with _cabi.device_guard(self):
         _cabi.check(
             _cabi.lib().fg_scaled_mm_fp8(
                 _cabi.ptr(dst), _cabi.ptr(self), _cabi.ptr(mat2), _cabi.ptr(scale_a), _cabi.ptr(scale_b),
                 _cabi.ptr(bias), m, n, k, self.stride(0), mat2.stride(1), dst.stride(0),
-                mode_a, mode_b, _cabi.DTYPE_CODE[output_dtype], 0, _cabi.stream_ptr(self.device),
+                mode_a, mode_b, _cabi.DTYPE_E4M3 if fp8_out else _cabi.DTYPE_CODE[output_dtype], 0,
+                _cabi.stream_ptr(self.device),
             )
         )
     if dst is not out:

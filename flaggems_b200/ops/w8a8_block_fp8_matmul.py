@@ -9,7 +9,7 @@ import torch
 
 from .. import _cabi
 
-logger = logging.getLogger(__name__)
+logger = logging.getLogger(__name__.replace("flaggems_b200", "flag_gems", 1))
 
 
 def _cdiv(a, b):

@@ -83,7 +83,9 @@ def _resolve_user_setting(value, kind):
 
 def setup_flaggems_logging(path=None, record=False, once=False):
     """``record=True`` appends one "GEMS <OP>" line per call (or per op with ``once``) to
-    ``path`` (default ~/.flaggems/oplist.log), as src/flag_gems/logging_utils.py:59-80 does."""
+    ``path`` (default ~/.flaggems/oplist.log), as src/flag_gems/logging_utils.py:59-80 does.  The
+    loggers carry the reference's names (``flag_gems.ops.scaled_mm``, ``flag_gems.fused.fused_moe``,
+    ...), so a log written here reads like one written by the reference."""
     global _log_handler
     if not record:
         return
@@ -104,7 +106,7 @@ def setup_flaggems_logging(path=None, record=False, once=False):
                 return True
 
         handler.addFilter(_Once())
-    root = logging.getLogger("flaggems_b200")
+    root = logging.getLogger("flag_gems")
     root.setLevel(logging.DEBUG)
     root.addHandler(handler)
     _log_handler = handler
@@ -113,7 +115,7 @@ def setup_flaggems_logging(path=None, record=False, once=False):
 def teardown_flaggems_logging():
     global _log_handler
     if _log_handler is not None:
-        logging.getLogger("flaggems_b200").removeHandler(_log_handler)
+        logging.getLogger("flag_gems").removeHandler(_log_handler)
         _log_handler.close()
         _log_handler = None
 

@@ -30,6 +30,7 @@ extern "C" {
 #define FG_DTYPE_BF16 0
 #define FG_DTYPE_F16 1
 #define FG_DTYPE_F32 2
+#define FG_DTYPE_E4M3 3 /* output of fg_scaled_mm_fp8 only */
 
 /* scale layout codes of fg_scaled_mm_fp8 / fg_moe_grouped_gemm_fp8 */
 #define FG_SCALE_SCALAR 0 /* one fp32 value                        */
@@ -316,7 +317,10 @@ int fg_symm_free(void* ptr);
  * (ld_b = elements between consecutive n, i.e. b.stride(1) of the column-major
  * [K,N] view), c [M,N] of out_dtype (ld_c).  c = out(sb[n] * (sa[m] * acc)) then
  * + bias in the output type (bias_after_round != 0) or + bias in fp32 before the
- * cast.  sa_mode/sb_mode: FG_SCALE_SCALAR or FG_SCALE_VECTOR.  K % 16 == 0. */
+ * cast.  sa_mode/sb_mode: FG_SCALE_SCALAR or FG_SCALE_VECTOR.  K % 16 == 0.
+ * out_dtype FG_DTYPE_E4M3 (the aten default, out_dtype=None -> the operands' type,
+ * src/flag_gems/ops/scaled_mm.py:214-220): c holds e4m3 bytes, rounded to nearest even and
+ * saturated at +-448; the bias is then fp32 and joins before the cast. */
 int fg_scaled_mm_fp8(void* c, const void* a, const void* b, const float* sa, const float* sb,
                      const void* bias, int64_t M, int64_t N, int64_t K, int64_t ld_a, int64_t ld_b,
                      int64_t ld_c, int sa_mode, int sb_mode, int out_dtype, int bias_after_round,

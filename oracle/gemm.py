@@ -39,6 +39,11 @@ def scaled_mm(
     acc = _bcast_scale(b_scale, n, 1) * acc
     if bias is not None and not bias_after_round:
         acc = acc + bias.float().reshape(1, -1)
+    if out_dtype == torch.float8_e4m3fn:
+        # aten _scaled_mm with out_dtype=None stores the fp32 tile through an fp8 pointer
+        # (src/flag_gems/ops/scaled_mm.py:134-136, :214-220): round to nearest even, saturating
+        # at +-448 (the NVIDIA fp32 -> e4m3 conversion; torch's CPU cast would give NaN above 464)
+        acc = acc.clamp(-448.0, 448.0)
     c = acc.to(out_dtype)
     if bias is not None and bias_after_round:
         c = c + bias.to(out_dtype).reshape(1, -1)

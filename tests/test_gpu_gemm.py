@@ -137,6 +137,41 @@ def test_aten_scaled_mm(m, n, k, mode, out_dtype, use_bias):
     _close(out, ref)
 
 
+@pytest.mark.parametrize("m,n,k", [(16, 16, 16), (17, 31, 32), (64, 48, 80), (300, 520, 256), (4, 4096, 1024)])
+@pytest.mark.parametrize("mode", ["scalar", "rowwise_2d"])
+@pytest.mark.parametrize("use_bias", [False, True])
+def test_aten_scaled_mm_default_out_dtype_is_fp8(m, n, k, mode, use_bias):
+    """torch._scaled_mm(a, b, sa, sb) without out_dtype: the result has the operands' dtype
+    (src/flag_gems/ops/scaled_mm.py:214-220).  FP8 bytes must equal the oracle's wherever the fp32
+    value is not within accumulation-order distance of a rounding boundary: at most a few
+    elements may differ, and then by one FP8 step."""
+    g = torch.Generator().manual_seed(12)
+    mat1 = (torch.randn(m, k, generator=g) * 0.5).to(FP8)
+    mat2 = (torch.randn(k, n, generator=g) * 0.5).to(FP8)
+    if mode == "scalar":
+        sa, sb = torch.tensor([0.75]), torch.tensor([40.0])  # large enough for some values to saturate
+    else:
+        sa, sb = torch.linspace(0.75, 1.25, m).reshape(m, 1), torch.linspace(30.0, 50.0, n).reshape(1, n)
+    bias = (torch.randn(n, generator=g) * 4).bfloat16() if use_bias else None
+    ref = oracle.scaled_mm(mat1, mat2, sa, sb, bias, FP8, bias_after_round=False)
+    with flag_gems.use_gems():
+        res = torch._scaled_mm(mat1.cuda(), mat2.cuda(), sa.cuda(), sb.cuda(),
+                               bias=None if bias is None else bias.cuda())
+        out = torch.empty(m, n, dtype=FP8, device="cuda")
+        torch.ops.aten._scaled_mm.out(mat1.cuda(), mat2.cuda(), sa.cuda(), sb.cuda(),
+                                      bias=None if bias is None else bias.cuda(), out=out)
+    assert res.dtype == FP8 and res.shape == (m, n)
+    assert torch.equal(res.view(torch.uint8), out.view(torch.uint8))
+    got, want = res.cpu().float(), ref.float()
+    assert bool(torch.isfinite(got).all()) and float(got.abs().max()) <= 448.0
+    if mode == "scalar" and m * n >= 100000:
+        assert float(want.abs().max()) == 448.0, "the case is meant to exercise saturation"
+    differ = got != want
+    assert float(differ.float().mean()) <= 2e-3
+    # a differing element is one FP8 step away: relative distance at most 2^-3
+    assert bool(((got - want).abs()[differ] <= 0.126 * want.abs()[differ].clamp(min=2.0 ** -6)).all())
+
+
 # ---- block-scaled ------------------------------------------------------------------------
 
 def _block_case(m, n, k, seed=0):

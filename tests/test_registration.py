@@ -19,17 +19,56 @@ def test_record_writes_op_log(tmp_path):
 
     p = tmp_path / "oplist.log"
     with flag_gems.use_gems(record=True, path=str(p)):
-        logging.getLogger("flaggems_b200.ops.scaled_mm").debug("GEMS SCALED_MM")
-    assert "GEMS SCALED_MM" in p.read_text()
+        logging.getLogger("flag_gems.ops.scaled_mm").debug("GEMS SCALED_MM")
+    text = p.read_text()
+    # the reference's tests/test_enable_api.py:72-97 greps "[DEBUG] flag_gems.ops.<op>" prefixes
+    assert "[DEBUG] flag_gems.ops.scaled_mm: GEMS SCALED_MM" in text
+
+
+def test_module_loggers_carry_the_reference_names():
+    import importlib
+
+    fm = importlib.import_module("flaggems_b200.fused.fused_moe")
+    sm = importlib.import_module("flaggems_b200.ops.scaled_mm")
+    gq = importlib.import_module("flaggems_b200.ops.per_token_group_quant_fp8")
+    assert sm.logger.name == "flag_gems.ops.scaled_mm"
+    assert fm.logger.name == "flag_gems.fused.fused_moe"
+    assert gq.logger.name == "flag_gems.ops.per_token_group_quant_fp8"
+
+
+def test_inplace_outplace_signatures_bind_positionally():
+    """Parameter names, order and defaults of src/flag_gems/fused/fused_moe.py:2188-2209 and
+    :2241-2262: a custom-op registration passes all 21 arguments by position."""
+    import inspect
+
+    names = ["hidden_states", "w1", "w2", "topk_weights", "topk_ids", "activation", "apply_router_weight_on_input",
+             "use_fp8_w8a8", "use_int8_w8a8", "use_int8_w8a16", "use_int4_w4a16", "per_channel_quant",
+             "global_num_experts", "w1_scale", "w2_scale", "a1_scale", "a2_scale", "block_shape", "w1_bias",
+             "w2_bias"]
+    defaults = ["silu", False, False, False, False, False, False, -1, None, None, None, None, None, None, None]
+    for fn in (flag_gems.inplace_fused_experts, flag_gems.outplace_fused_experts):
+        sig = inspect.signature(fn)
+        assert list(sig.parameters) == names
+        assert [p.default for p in list(sig.parameters.values())[5:]] == defaults
+        assert all(p.kind == inspect.Parameter.POSITIONAL_OR_KEYWORD for p in sig.parameters.values())
+        bound = sig.bind(*range(len(names)))  # every argument by position
+        assert bound.arguments["activation"] == 5 and bound.arguments["w2_bias"] == len(names) - 1
+    impl = list(inspect.signature(flag_gems.fused_experts_impl).parameters)
+    assert impl[:7] == ["hidden_states", "w1", "w2", "topk_weights", "topk_ids", "inplace", "activation"]
+    assert len(impl) == 25
 
 
 def test_patch_empty_vllm_is_idempotent_and_defines_ops():
-    flag_gems.patch_empty_vllm()
-    flag_gems.patch_empty_vllm()
-    assert hasattr(torch.ops._C, "cutlass_scaled_mm")
-    assert hasattr(torch.ops._C, "per_token_group_fp8_quant")
-    assert hasattr(torch.ops._moe_C, "moe_align_block_size")
-    assert hasattr(torch.ops._moe_C, "moe_sum")
+    from tests._isolated import check_isolated
+
+    check_isolated('''
+import torch, flag_gems
+flag_gems.patch_empty_vllm()
+flag_gems.patch_empty_vllm()
+for ns, op in (("_C", "cutlass_scaled_mm"), ("_C", "per_token_group_fp8_quant"), ("_moe_C", "moe_align_block_size"),
+               ("_moe_C", "moe_sum"), ("_moe_C", "topk_softmax"), ("_moe_C", "grouped_topk")):
+    assert hasattr(getattr(torch.ops, ns), op), op
+''')
 
 
 def test_api_surface_matches_reference_names():
