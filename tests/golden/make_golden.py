@@ -196,6 +196,41 @@ def main():
     save("fused_moe_block_fp8", dict(hidden=hidden, w1=w1.view(torch.uint8), w2=w2.view(torch.uint8),
                                      w1_scale=w1s, w2_scale=w2s, topk_weights=tw, topk_ids=ti, out=out))
 
+    # ---- per-row fake-quantised FP8 MoE: tests/test_fused_experts_impl.py:465-528, on the input
+    # recipe of test_accuracy_fused_moe_fp8 (:375-462): weights quantised per tensor (one scale per
+    # expert), dequantised to bf16 for the golden.  A second set of cases quantises the weights
+    # per output channel instead: the golden takes dequantised weights, so the same function
+    # bounds the per-token x per-channel mode as well.
+    fm = lift("tests/test_fused_experts_impl.py", ["_fake_quantize_fp8", "_fake_quantize_int8",
+                                                   "torch_fused_moe_quantized_reference"])
+    fm["torch_fused_moe_quantized_reference"].__globals__.update(fm)
+    g2 = torch.Generator().manual_seed(0)
+    cases = []
+    for granularity in ("per_tensor", "per_channel"):
+        for (t, e, h, i, topk) in [(4, 8, 128, 256, 2), (32, 4, 128, 128, 4)]:
+            hidden = torch.randn(t, h, generator=g2).bfloat16()
+            w1f = torch.randn(e, 2 * i, h, generator=g2) * (1.0 / h ** 0.5)
+            w2f = torch.randn(e, h, i, generator=g2) * (1.0 / i ** 0.5)
+            quant = []
+            for w in (w1f, w2f):
+                if granularity == "per_tensor":
+                    sc = w.abs().amax(dim=(1, 2)).clamp(min=1e-10) / 448.0  # [E]
+                    q = (w / sc[:, None, None]).clamp(-448, 448).to(torch.float8_e4m3fn)
+                    deq = (q.float() * sc[:, None, None]).bfloat16()
+                else:
+                    sc = w.abs().amax(dim=2).clamp(min=1e-10) / 448.0  # [E, N]
+                    q = (w / sc[:, :, None]).clamp(-448, 448).to(torch.float8_e4m3fn)
+                    deq = (q.float() * sc[:, :, None]).bfloat16()
+                quant.append((q, sc, deq))
+            gating = torch.randn(t, e, generator=g2)
+            tw, ti = torch.topk(torch.softmax(gating, -1), topk)
+            tw = (tw / tw.sum(-1, keepdim=True)).bfloat16()
+            out = fm["torch_fused_moe_quantized_reference"](hidden, quant[0][2], quant[1][2], tw, ti, quant_mode="fp8")
+            cases.append(dict(granularity=granularity, hidden=hidden, w1=quant[0][0].view(torch.uint8),
+                              w2=quant[1][0].view(torch.uint8), w1_scale=quant[0][1], w2_scale=quant[1][1],
+                              topk_weights=tw, topk_ids=ti, out=out))
+    save("fused_moe_fake_quant_fp8", cases)
+
 
 if __name__ == "__main__":
     if not os.path.isdir(REF):

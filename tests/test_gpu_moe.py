@@ -18,9 +18,15 @@ def _router(t, e, topk, g):
     return (tw / tw.sum(-1, keepdim=True)).bfloat16(), ti
 
 
-def _close(got, ref, rel=1e-2):
+def _close(got, ref, rel=1e-2, strict_frac=0.999):
+    """Two bounds.  Every element: rtol 1e-2 with atol relative to the output range (rows are
+    rounded to bf16 before the fp32 top-k sum, as in the reference, so one bf16 ulp of the
+    largest addend can survive cancellation in a small sum).  And the bound the path is specified
+    with, rtol 1e-2 + atol 1e-2 per element, must hold for at least `strict_frac` of the elements."""
     got, ref = got.cpu().float(), ref.float()
     torch.testing.assert_close(got, ref, rtol=1e-2, atol=max(1e-2, rel * float(ref.abs().max())))
+    frac = float(((got - ref).abs() <= 1e-2 + 1e-2 * ref.abs()).float().mean())
+    assert frac >= strict_frac, f"only {frac:.5f} of the elements are within rtol 1e-2 / atol 1e-2"
 
 
 @pytest.mark.parametrize("t,h,i,e,topk", [(64, 256, 128, 8, 2), (333, 512, 256, 8, 2), (16, 1024, 384, 4, 1),
@@ -78,8 +84,7 @@ def test_fused_moe_per_tensor(static):
     ref = oracle.fused_moe_per_tensor_fp8(hidden, w1, w2, s1, s2, tw, ti, a1, a2)
     # a value that sits on an FP8 rounding boundary of the shared intermediate scale may flip:
     # allow 2 % of the output range on top of rtol 1e-2
-    got, ref = out.cpu().float(), ref.float()
-    torch.testing.assert_close(got, ref, rtol=1e-2, atol=max(1e-2, 2e-2 * float(ref.abs().max())))
+    _close(out, ref, rel=2e-2, strict_frac=0.99)
 
 
 @pytest.mark.parametrize("block_m", [16, 64, 128])
