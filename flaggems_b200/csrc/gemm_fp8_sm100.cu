@@ -36,6 +36,21 @@
 using namespace fgptx;
 namespace cg = cooperative_groups;
 
+// Optional stall accounting for kernel development (-DFG_GEMM_PROFILE; never in the shipped build):
+// per CTA, cycles the producer, the MMA warp and one epilogue warp spend in each of their waits.
+#ifdef FG_GEMM_PROFILE
+__device__ long long g_gemm_prof[256 * 12];
+#define FG_PROF_DECL(name) long long name = 0
+#define FG_PROF_T0(t) const long long t = clock64()
+#define FG_PROF_ADD(acc, t) acc += clock64() - t
+#define FG_PROF_OUT(slot, v) if (blockIdx.x < 256) g_gemm_prof[blockIdx.x * 12 + (slot)] = (v)
+#else
+#define FG_PROF_DECL(name)
+#define FG_PROF_T0(t)
+#define FG_PROF_ADD(acc, t)
+#define FG_PROF_OUT(slot, v)
+#endif
+
 namespace {
 
 constexpr int BLOCK_M = 128;
@@ -347,6 +362,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            FG_PROF_DECL(prof_wait);
             for (int t = tile_first; t < num_tiles && ok; t += tile_step) {
                 const TileCoord tc = tile_coord(t, num_m, num_n);
                 const int expert = p.grouped ? p.expert_ids[tc.m_blk] : 0;
@@ -354,7 +370,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 const int m0 = tc.m_blk * a_rows_step + (int)cta_rank * BLOCK_M;
                 const int n0 = tc.n_blk * OUT_TILE_N;
                 for (int kb = kb_begin; kb < kb_end; ++kb) {
+                    FG_PROF_T0(tw);
                     ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 1);
+                    FG_PROF_ADD(prof_wait, tw);
                     if (!ok) break;
                     uint8_t* sa = smem + stage * C::STAGE_BYTES;
                     uint8_t* sb = sa + C::A_BYTES;
@@ -387,6 +405,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     }
                 }
             }
+            FG_PROF_OUT(0, prof_wait);
         }
     } else if (warp == 1) {
         // ------------------------------- MMA issuer ---------------------------------------
@@ -402,6 +421,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             uint32_t acc_iter = 0;
             bool ok = true;
             bool full_ready = false, tmem_ready = false;  // probed ahead for (stage, phase) / acc_iter
+            FG_PROF_DECL(prof_tmem);
+            FG_PROF_DECL(prof_full);
+            FG_PROF_DECL(prof_blocks);
+            FG_PROF_T0(prof_start);
             auto issue_block = [&](uint32_t a_addr, uint32_t d_tmem, auto zero_first) {
                 const uint64_t a_desc = umma_desc_k_sw128(a_addr);
                 const uint64_t b_desc = umma_desc_k_sw128(a_addr + C::A_BYTES);
@@ -423,15 +446,22 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     const uint32_t buf = acc_iter & 1u;
                     const bool new_acc = BLOCK_SCALED || kb == kb_begin;
                     if (new_acc) {
+                        FG_PROF_T0(tw);
                         ok = __all_sync(0xffffffffu, tmem_ready || mbar_wait(&tmem_empty[buf], ((acc_iter >> 1) & 1u) ^ 1u,
                                                                              abort_flag, p.status, 2));
+                        FG_PROF_ADD(prof_tmem, tw);
                         if (!ok) break;
                         // Orders the epilogue's TMEM reads (published by its arrive) before the MMAs
                         // that overwrite the buffer.  The operand tiles need no fence: TMA writes
                         // and MMA reads are async-proxy accesses ordered by the full barrier.
                         tc_fence_after_sync();
                     }
+                    FG_PROF_T0(tw2);
                     ok = __all_sync(0xffffffffu, full_ready || mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3));
+                    FG_PROF_ADD(prof_full, tw2);
+#ifdef FG_GEMM_PROFILE
+                    ++prof_blocks;
+#endif
                     if (!ok) break;
                     const uint32_t a_addr = smem_u32(smem + stage * C::STAGE_BYTES);
                     const uint32_t d_tmem = tmem_base + buf * BN;
@@ -459,6 +489,14 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     if (last) ++acc_iter;
                 }
             }
+#ifdef FG_GEMM_PROFILE
+            if (lane == 0) {
+                FG_PROF_OUT(1, prof_tmem);
+                FG_PROF_OUT(2, prof_full);
+                FG_PROF_OUT(3, clock64() - prof_start);
+                FG_PROF_OUT(4, prof_blocks);
+            }
+#endif
         }
       }
     } else {
@@ -472,6 +510,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         uint8_t* epi_stage = epi_stage_base + ew * C::EPI_STAGE_BYTES;
         uint32_t acc_iter = 0;
         bool ok = true;
+        FG_PROF_DECL(prof_epi_wait);
+        FG_PROF_DECL(prof_epi_tail);
+        FG_PROF_DECL(prof_epi_ld);
+        FG_PROF_DECL(prof_epi_fma);
+        FG_PROF_T0(prof_epi_start);
 
         for (int t = tile_first; t < num_tiles && ok; t += tile_step) {
             const TileCoord tc = tile_coord(t, num_m, num_n);
@@ -634,8 +677,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     }
                     const uint64_t sc0 = pack_f32x2(sc0f, sc0f), sc1 = pack_f32x2(sc1f, sc1f);
                     const uint32_t buf = acc_iter & 1u;
+                    FG_PROF_T0(tw);
                     ok = mbar_wait(&tmem_full[buf], (acc_iter >> 1) & 1u, abort_flag, p.status, 5);
+                    FG_PROF_ADD(prof_epi_wait, tw);
                     if (!ok) break;
+                    FG_PROF_T0(t_ld);
                     tc_fence_after_sync();
                     const uint32_t tbuf = lane_addr + buf * BN;
                     auto release = [&]() {
@@ -647,19 +693,40 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                             if constexpr (PAIR) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty[buf]), 0u));
                             else mbar_arrive(&tmem_empty[buf]);
                         }
+                        FG_PROF_ADD(prof_epi_ld, t_ld);
                     };
-                    if constexpr (C::COLS >= 64) {
-                        // Rounds of 64 columns: one load instruction, one wait, 32 packed FMAs each.
+                    if constexpr (C::COLS == 128) {
+                        // Four 32-column loads through two register sets, software-pipelined: the
+                        // third and fourth load travel while the first two sets are folded, and the
+                        // buffer goes back to the MMA warp before the last 32 packed FMAs.  Measured
+                        // on the bare loop: 286 cycles per K block against 405 for two rounds of
+                        // (64-column load, wait, fold); the 64 packed FMAs of a thread alone take
+                        // 256 cycles per K block and scheduler, the MMAs of a K block 525.
+                        uint32_t v0[32], v1[32];
+                        tmem_ld_32x32b_x32(tbuf + chunk_col(0), v0);
+                        tmem_ld_32x32b_x32(tbuf + chunk_col(1), v1);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) ffma2(acc[i], v0[2 * i], v0[2 * i + 1], sc0);
+                        tmem_ld_32x32b_x32(tbuf + chunk_col(2), v0);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) ffma2(acc[16 + i], v1[2 * i], v1[2 * i + 1], sc0);
+                        tmem_ld_32x32b_x32(tbuf + chunk_col(3), v1);
+                        tmem_ld_wait();
+                        release();
+                        FG_PROF_T0(t_f);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) ffma2(acc[32 + i], v0[2 * i], v0[2 * i + 1], sc1);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) ffma2(acc[48 + i], v1[2 * i], v1[2 * i + 1], sc1);
+                        FG_PROF_ADD(prof_epi_fma, t_f);
+                    } else if constexpr (C::COLS == 64) {
                         uint32_t raw[64];
+                        tmem_ld_32x32b_x64(tbuf + chunk_col(0), raw);
+                        tmem_ld_wait();
+                        release();
 #pragma unroll
-                        for (int r = 0; r < C::COLS / 64; ++r) {
-                            tmem_ld_32x32b_x64(tbuf + chunk_col(2 * r), raw);
-                            tmem_ld_wait();
-                            if (r == C::COLS / 64 - 1) release();
-                            const uint64_t sc = (FUSE_SILU && r == 1) ? sc1 : sc0;
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) ffma2(acc[32 * r + i], raw[2 * i], raw[2 * i + 1], sc);
-                        }
+                        for (int i = 0; i < 32; ++i) ffma2(acc[i], raw[2 * i], raw[2 * i + 1], sc0);
                     } else {
                         uint32_t raw[32];
                         tmem_ld_32x32b_x32(tbuf + chunk_col(0), raw);
@@ -671,6 +738,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     ++acc_iter;
                 }
                 if (!ok) break;
+                FG_PROF_T0(t_tail);
                 if constexpr (SPLITK) {
                     float* dst = reinterpret_cast<float*>(smem) + (size_t)r_in_tile * (BN + 4) + 128 * half;
 #pragma unroll
@@ -701,8 +769,18 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     else if (row_ok && nc > 0)
                         store_chunk(out_ptr, col, v, nc, p.out_dtype, p.c_vec_ok);
                 }
+                FG_PROF_ADD(prof_epi_tail, t_tail);
             }
         }
+#ifdef FG_GEMM_PROFILE
+        if (ew == 0 && lane == 0) {
+            FG_PROF_OUT(5, prof_epi_wait);
+            FG_PROF_OUT(6, prof_epi_tail);
+            FG_PROF_OUT(7, clock64() - prof_epi_start);
+            FG_PROF_OUT(8, prof_epi_ld);
+            FG_PROF_OUT(9, prof_epi_fma);
+        }
+#endif
     }
 
     if constexpr (SPLITK) {
@@ -1062,6 +1140,15 @@ __global__ void bounded_wait_selftest_kernel(unsigned int* status, uint64_t limi
 }  // namespace
 
 extern "C" {
+
+#ifdef FG_GEMM_PROFILE
+// Development only: copies the stall counters of the last GEMM launch to the host.
+int fg_debug_gemm_profile(long long* out, int n) {
+    FG_CUDA(cudaDeviceSynchronize());
+    FG_CUDA(cudaMemcpyFromSymbol(out, g_gemm_prof, sizeof(long long) * (size_t)(n < 3072 ? n : 3072)));
+    return FG_OK;
+}
+#endif
 
 int fg_selftest_bounded_wait(int64_t limit_ns, int site, void* stream) {
     FG_REQUIRE(limit_ns > 0 && limit_ns <= 100000000ll, FG_ERR_INVALID_ARGUMENT,

@@ -272,6 +272,121 @@ __global__ void __launch_bounds__(256) group_quant_kernel(QuantArgs a) {
     }
 }
 
+// ---- small groups, 16-bit inputs: the bandwidth path ---------------------------------------
+// A lane owns 16 consecutive elements (two 16-byte loads, one 16-byte store), a team of
+// GROUP/16 lanes owns a group.  The inputs stay in registers as raw 16-bit pairs: max|x| is taken
+// on the pairs (exact in the input type), and they are widened to fp32 only where they are
+// scaled, so that a thread carries 8 registers of data per group in flight instead of 16 and five
+// CTAs (40 warps, 48 registers each) fit an SM; six CTAs spill and measured no faster.  PACKED selects the expert-parallel dispatch format (scales and a trailer behind
+// the payload of each row, rows optionally stored into peers' receive buffers).
+template <typename T> struct Pair16;
+template <> struct Pair16<__nv_bfloat16> {
+    using V = __nv_bfloat162;
+    static __device__ __forceinline__ V absmax(V m, uint32_t w) {
+        return __hmax2(m, __habs2(*reinterpret_cast<const V*>(&w)));
+    }
+    static __device__ __forceinline__ float reduce(V m) { return fmaxf(__bfloat162float(m.x), __bfloat162float(m.y)); }
+    static __device__ __forceinline__ void widen(uint32_t w, float& lo, float& hi) {
+        lo = __uint_as_float(w << 16);
+        hi = __uint_as_float(w & 0xffff0000u);
+    }
+};
+template <> struct Pair16<__half> {
+    using V = __half2;
+    static __device__ __forceinline__ V absmax(V m, uint32_t w) {
+        return __hmax2(m, __habs2(*reinterpret_cast<const V*>(&w)));
+    }
+    static __device__ __forceinline__ float reduce(V m) { return fmaxf(__half2float(m.x), __half2float(m.y)); }
+    static __device__ __forceinline__ void widen(uint32_t w, float& lo, float& hi) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+        lo = f.x;
+        hi = f.y;
+    }
+};
+
+template <typename T, int MODE, int TPG, bool PACKED>
+__global__ void __launch_bounds__(256, 5) group_quant16_kernel(QuantArgs a) {
+    constexpr int UNROLL = 2;
+    constexpr int GROUP = TPG * 16;
+    using P = Pair16<T>;
+    const int64_t rows = resolve_rows(a);
+    const int gpr = (int)(a.K / GROUP);
+    const int64_t total = rows * gpr;
+    const int lane_in_team = threadIdx.x % TPG;
+    const int64_t team = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / TPG;
+    const int64_t teams = (int64_t)gridDim.x * blockDim.x / TPG;
+    const int64_t stride = teams * UNROLL;
+    const T* x = reinterpret_cast<const T*>(a.x);
+    // Trip count from the first team of the warp, so the whole warp runs the same iterations.
+    const int64_t warp_first = team - (threadIdx.x % 32) / TPG;
+    const int64_t iters = warp_first < total ? (total - warp_first + stride - 1) / stride : 0;
+    const int step_row = (int)(stride / gpr), step_cg = (int)(stride % gpr);
+    int row[UNROLL], cg[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+        const int64_t g0 = team + (int64_t)u * teams;
+        row[u] = (int)(g0 / gpr);
+        cg[u] = (int)(g0 % gpr);
+    }
+    for (int64_t it = 0; it < iters; ++it) {
+        uint4 v[UNROLL][2];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int64_t src = row[u] < rows ? source_row(a, row[u]) : -1;
+            if (src >= 0) {
+                const uint4* p = reinterpret_cast<const uint4*>(x + src * a.ld_x + cg[u] * GROUP + lane_in_team * 16);
+                v[u][0] = p[0];
+                v[u][1] = p[1];
+            } else {
+                v[u][0] = v[u][1] = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const uint32_t w[8] = {v[u][0].x, v[u][0].y, v[u][0].z, v[u][0].w, v[u][1].x, v[u][1].y, v[u][1].z, v[u][1].w};
+            typename P::V m2 = P::absmax(P::absmax(typename P::V(), w[0]), w[1]);
+#pragma unroll
+            for (int i = 2; i < 8; ++i) m2 = P::absmax(m2, w[i]);
+            float amax = P::reduce(m2);
+#pragma unroll
+            for (int o = TPG / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            const float s = make_scale<MODE>(amax, a.eps, a.pow2);
+            const Divider d = make_divider<MODE>(s);
+            uint8_t* qrow = nullptr;
+            if (row[u] < rows) qrow = PACKED ? packed_row_ptr(a, row[u]) : a.q + (int64_t)row[u] * a.ld_q;
+            if (qrow) {
+                uint32_t o[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float a0, a1, b0, b1, q0, q1, q2, q3;
+                    P::widen(w[2 * i], a0, a1);
+                    P::widen(w[2 * i + 1], b0, b1);
+                    apply_divider2<MODE>(a0, a1, d, q0, q1);
+                    apply_divider2<MODE>(b0, b1, d, q2, q3);
+                    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q0, q1), __NV_SATFINITE, __NV_E4M3);
+                    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q2, q3), __NV_SATFINITE, __NV_E4M3);
+                    o[i] = lo | (hi << 16);
+                }
+                *reinterpret_cast<uint4*>(qrow + cg[u] * GROUP + lane_in_team * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+                if (lane_in_team == 0) {
+                    if constexpr (PACKED) {  // scales sit behind the payload of the same row
+                        reinterpret_cast<float*>(qrow + a.K)[cg[u]] = s;
+                        if (cg[u] == 0) write_row_meta(a, row[u]);
+                    } else {
+                        a.s[(int64_t)row[u] * a.s_row_stride + (int64_t)cg[u] * a.s_col_stride] = s;
+                    }
+                }
+            }
+            cg[u] += step_cg;
+            row[u] += step_row;
+            if (cg[u] >= gpr) {
+                cg[u] -= gpr;
+                row[u] += 1;
+            }
+        }
+    }
+}
+
 // ---- any group size (multiple of 8), one CTA per group: per-token rows, block_size = K ...
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256) row_quant_kernel(QuantArgs a) {
@@ -395,7 +510,7 @@ int launch_quant_t(const QuantArgs& a, cudaStream_t st) {
     auto small = [&](auto kernel, int tpg) -> int {
         const int64_t threads = groups * tpg;
         int64_t blocks = fg_cdiv(threads, 256 * 2);
-        const int64_t cap = (int64_t)fg_num_sms() * 16;
+        const int64_t cap = (int64_t)fg_num_sms() * 24;
         if (blocks > cap) blocks = cap;
         if (blocks < 1) blocks = 1;
         kernel<<<(unsigned)blocks, 256, 0, st>>>(a);
@@ -403,6 +518,21 @@ int launch_quant_t(const QuantArgs& a, cudaStream_t st) {
         FG_LAUNCH_CHECK();
         return FG_OK;
     };
+    if constexpr (sizeof(T) == 2) {
+        // 16-byte stores need 16-byte aligned output rows; otherwise the generic kernel below
+        const bool q16 = ((uintptr_t)a.q % 16 == 0) && (a.ld_q % 16 == 0);
+        if (q16 && a.meta_ids) {
+            if (a.group == 128) return small(group_quant16_kernel<T, MODE, 8, true>, 8);
+        } else if (q16) {
+            switch (a.group) {
+                case 64: return small(group_quant16_kernel<T, MODE, 4, false>, 4);
+                case 128: return small(group_quant16_kernel<T, MODE, 8, false>, 8);
+                case 256: return small(group_quant16_kernel<T, MODE, 16, false>, 16);
+                case 512: return small(group_quant16_kernel<T, MODE, 32, false>, 32);
+                default: break;
+            }
+        }
+    }
     switch (a.group) {
         // sixteen elements (two 16-byte loads) per lane: the shuffle reduction, the scale and the
         // index arithmetic are paid once per 16 elements, and four loads per lane are in flight

@@ -7,7 +7,9 @@ src/flag_gems/fused/moe_align_block_size.py:817-818), which assumes replicated t
 external all-reduce.  This layer keeps the per-row arithmetic of that function (block-FP8
 quantisation -> grouped GEMM1 with fused SiLU*up -> re-quantisation -> grouped GEMM2 with the
 router weight applied in fp32 before the bf16 cast -> fp32 top-k sum in slot order), so a
-row's result does not depend on the number of ranks.
+routed row's result does not depend on the number of ranks.  (The shared expert is a dense GEMM
+over the rank's own tokens; its tile and split-K choice follows that token count, so its last
+bit may.)
 
 Per step and rank:
   1. order the T_loc*topk route slots by destination rank (stable), count per destination;

@@ -43,9 +43,10 @@ def _is_op_registered(lib_name, op_name):
 
 
 def custom_per_token_group_fp8_quant(input, output_q, output_s, group_size, eps, fp8_min, fp8_max,
-                                     scale_ue8m0=False):
+                                     scale_ue8m0=False, dummy_is_scale_transposed=False, dummy_is_tma_aligned=False):
     """Writes straight into the caller's buffers (row- or column-major scales are inferred
-    from the strides of ``output_s`` as the reference adapter does)."""
+    from the strides of ``output_s`` as the reference adapter does).  The two trailing flags exist
+    only in newer vLLM schemas, where they are placeholders; the layout is read from the strides."""
     from .. import _cabi
 
     assert input.dim() == 2 and input.stride(-1) == 1
@@ -68,9 +69,12 @@ def custom_cutlass_scaled_mm(output, input, weight, scale_a, scale_b, bias=None)
 
 
 def custom_moe_align_block_size(topk_ids, num_experts, block_size, sorted_token_ids, experts_ids,
-                                num_tokens_post_pad):
+                                num_tokens_post_pad, maybe_expert_map=None):
     from ..fused.moe_align_block_size import moe_align_block_size_triton
 
+    if maybe_expert_map is not None:
+        # newer vLLM schemas carry this argument; the reference's op (patch_util.py:78-81) has none
+        raise NotImplementedError("moe_align_block_size with maybe_expert_map is not implemented")
     moe_align_block_size_triton(topk_ids, num_experts, block_size, sorted_token_ids, experts_ids,
                                 num_tokens_post_pad)
 

@@ -18,13 +18,17 @@ from tests.test_ep_gloo import expected, make_case  # noqa: E402
 pytestmark = pytest.mark.gpu
 
 
-def _layer_single(case, dev):
+def _layer_single(case, dev, sl=slice(None)):
+    """The single-rank layer (all experts local) on the tokens `sl` of the case.  A routed row's
+    bits do not depend on which other rows are in the step; the shared expert is a dense GEMM whose
+    tile / split-K choice follows the number of local tokens, so a rank's reference is the
+    single-rank layer on that rank's own tokens."""
     from flaggems_b200.ep import ExpertParallelMoE
 
     hidden, w1, w2, s1, s2, tw, ti, shared = case
     layer = ExpertParallelMoE(w1.to(dev), w2.to(dev), s1.to(dev), s2.to(dev), w1.shape[0],
                               shared=tuple(t.to(dev) for t in shared))
-    return layer(hidden.to(dev), tw.to(dev), ti.to(dev))
+    return layer(hidden[sl].contiguous().to(dev), tw[sl].contiguous().to(dev), ti[sl].contiguous().to(dev))
 
 
 def test_single_gpu_layer_matches_oracle():
@@ -83,7 +87,7 @@ def _worker(rank, world, port, q):
         el, tl = e // world, t // world
         lo = rank * el
         sl = slice(rank * tl, (rank + 1) * tl)
-        single = _layer_single(case, dev)[sl]
+        single = _layer_single(case, dev, sl)
         equal, repeat, graph_ok, err = True, True, True, 0.0
         n_slots = tl * ti.shape[1]
         h, w, i = hidden[sl].to(dev), tw[sl].to(dev), ti[sl].to(dev)
@@ -192,10 +196,14 @@ def test_emulated_ranks_equal_single_gpu(world):
 
     dev = torch.device("cuda", 0)
     case = make_case(seed=5, t=160, h=512, i=256, e=16, topk=4)
-    single = _layer_single(case, dev)
+    tl = 160 // world
+    single = torch.cat([_layer_single(case, dev, slice(r * tl, (r + 1) * tl)) for r in range(world)])
     out = _emulated_ranks(case, world, dev)
     assert _cabi.device_status() == 0
     assert torch.equal(out, single)
+    # and the routed rows alone do not depend on the sharding at all
+    whole = _layer_single(case, dev)
+    torch.testing.assert_close(out.float(), whole.float(), rtol=0, atol=2.0 ** -6)
 
 
 def test_rows_outside_their_region_are_dropped_and_reported():
@@ -215,7 +223,7 @@ def test_rows_outside_their_region_are_dropped_and_reported():
         _cabi.device_status()
     assert _cabi.device_status() == 0  # read-and-clear; the context is still usable
     out = _emulated_ranks(case, 2, dev)
-    assert torch.equal(out, _layer_single(case, dev))
+    assert torch.equal(out, torch.cat([_layer_single(case, dev, slice(0, 32)), _layer_single(case, dev, slice(32, 64))]))
 
 
 def test_combine_rows_outside_the_home_buffer_are_dropped_and_reported():

@@ -196,22 +196,31 @@ import vllm._custom_ops
 import flag_gems, oracle
 from flaggems_b200 import _cabi
 flag_gems.apply_gems_patches_to_vllm(verbose=False)
+def call(op, *args):
+    # the installed vLLM may declare trailing arguments the reference's schemas do not have
+    extra = []
+    for a in op.default._schema.arguments[len(args):]:
+        if a.has_default_value():
+            break
+        t = str(a.type)
+        extra.append(None if t.startswith("Optional") else False if t == "bool" else 0)
+    return op(*args, *extra)
 n0 = _cabi.launch_count()
 x = torch.randn(33, 2, 1024).bfloat16()
 out = torch.empty(33, 1024, dtype=torch.bfloat16, device="cuda")
-torch.ops._moe_C.moe_sum(x.cuda(), out)
+call(torch.ops._moe_C.moe_sum, x.cuda(), out)
 assert torch.equal(out.cpu(), oracle.moe_sum(x))
 g = torch.Generator().manual_seed(8)
 ids = torch.randint(0, 60, (513, 6), generator=g, dtype=torch.int32)
 sr, er, nr = oracle.moe_align_block_size(ids, 32, 60)
 so = torch.full_like(sr, -7, device="cuda"); eo = torch.full_like(er, -7, device="cuda")
 no = torch.empty(1, dtype=torch.int32, device="cuda")
-torch.ops._moe_C.moe_align_block_size(ids.cuda(), 60, 32, so, eo, no)
+call(torch.ops._moe_C.moe_align_block_size, ids.cuda(), 60, 32, so, eo, no)
 assert torch.equal(so.cpu(), sr) and torch.equal(eo.cpu(), er) and torch.equal(no.cpu(), nr)
 a = torch.randn(64, 512).bfloat16()
 q = torch.empty(64, 512, dtype=torch.float8_e4m3fn, device="cuda")
 s = torch.empty(64, 4, dtype=torch.float32, device="cuda")
-torch.ops._C.per_token_group_fp8_quant(a.cuda(), q, s, 128, 1e-10, -448.0, 448.0, False)
+call(torch.ops._C.per_token_group_fp8_quant, a.cuda(), q, s, 128, 1e-10, -448.0, 448.0, False)
 qr, sr2 = oracle.per_token_group_quant_fp8(a, 128)
 assert torch.equal(q.cpu().view(torch.uint8), qr.view(torch.uint8)) and torch.equal(s.cpu(), sr2)
 assert _cabi.launch_count() - n0 >= 3
