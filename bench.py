@@ -32,7 +32,6 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
 import threading
 import time
@@ -105,44 +104,69 @@ def make_shared_weights(device, seed=0):
 # clocks
 # ---------------------------------------------------------------------------------------------
 class ClockSampler:
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """SM clock and throttle reasons of one GPU, sampled in a thread of this process through NVML
+    (read-only queries).  NVML is initialised in __enter__, before anything is timed: a freshly
+    started `nvidia-smi` process spends its first second enumerating every GPU of the box, and eight
+    of them doing so beside the timed passes slowed 8-rank steps by half."""
+    REASONS = ((0x8, "hw_slowdown"), (0x40, "hw_thermal_slowdown"), (0x20, "sw_thermal_slowdown"),
+               (0x4, "sw_power_cap"))
 
-    def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index, interval_ms=100):
+        self.index, self.interval = index, max(int(interval_ms), 10) / 1e3
+        self.sm, self.reasons_seen, self.max_sm, self.handle, self.nvml = [], 0, None, None, None
+        self._stop = threading.Event()
+        self.thread = None
 
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            try:
+                uuid = "GPU-" + str(torch.cuda.get_device_properties(self.index).uuid)
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:  # noqa: BLE001 - fall back to the ordinal
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_sm = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self._sample()
+            self.thread = threading.Thread(target=self._run, daemon=True)
             self.thread.start()
-        except OSError:
-            self.proc = None
+        except Exception:  # noqa: BLE001 - no NVML: the clocks record stays empty
+            self.nvml = None
         return self
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+    def _sample(self):
+        n = self.nvml
+        self.sm.append(float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)))
+        try:
+            self.reasons_seen |= int(n.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+        except Exception:  # noqa: BLE001 - older bindings
+            self.reasons_seen |= int(n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+
+    def _run(self):
+        while not self._stop.wait(self.interval):
+            try:
+                self._sample()
+            except Exception:  # noqa: BLE001
+                return
 
     def __exit__(self, *a):
-        if self.proc is not None:
-            self.proc.terminate()
-            try:
-                self.proc.wait(timeout=5)
-            except subprocess.TimeoutExpired:
-                self.proc.kill()
+        self._stop.set()
+        if self.thread is not None:
             self.thread.join(timeout=2)
+        if self.nvml is not None:
+            try:
+                self.nvml.nvmlShutdown()
+            except Exception:  # noqa: BLE001
+                pass
 
     def summary(self):
-        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active")
-                                                         for r in self.rows)]
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(sm)}
+        # the first sample was taken before any work was queued; the median is over the rest
+        under_load = self.sm[1:] if len(self.sm) > 1 else self.sm
+        return {"sm_mhz": statistics.median(under_load) if under_load else None, "sm_max_mhz": self.max_sm,
+                "reasons": [name for bit, name in self.REASONS if self.reasons_seen & bit],
+                "samples": len(under_load), "source": "NVML, in-process thread"}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -572,7 +596,7 @@ def _run_ours(args, world, rank, local_rank, dev, dist, _cabi, ExpertParallelMoE
     # workload throughout, long enough for nvidia-smi to report whatever the step time is.
     ms_passes, e2e_passes, marks = [], [], []
     launches0 = launches = 0
-    with ClockSampler(local_rank) as clocks:
+    with ClockSampler(local_rank, args.clock_interval_ms) as clocks:
         for phase, n in step_schedule(args):
             if phase in ("warmup", "clock_tail"):
                 for _ in range(n):
@@ -592,7 +616,10 @@ def _run_ours(args, world, rank, local_rank, dev, dist, _cabi, ExpertParallelMoE
             elif phase == "phase_trace":
                 del extra_streams[:]
                 barrier()
-                # phase breakdown of one eager step on this rank (CUDA events on the layer's stream)
+                # phase breakdown of one eager step on this rank (CUDA events on the layer's stream);
+                # the first eager step after the graph replays re-warms the eager path untimed
+                layer(hidden_d, tw_d, ti_d)
+                torch.cuda.synchronize()
                 layer.trace = []
                 layer(hidden_d, tw_d, ti_d)
                 torch.cuda.synchronize()
@@ -766,6 +793,8 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=16, help="tokens of the final output compared with the oracle")
     ap.add_argument("--cpu-experts", type=int, default=4,
                     help="experts (with all their routed rows) in the bounded CPU sample at N=1")
+    ap.add_argument("--clock-interval-ms", type=int, default=50,
+                    help="NVML sampling interval for the clocks record (one sampler thread per rank)")
     ap.add_argument("--no-extras", action="store_true", help="skip the dense GEMM / quant figures at N=1")
     ap.add_argument("--a2a-dispatch", action="store_true",
                     help="send packed rows by NCCL all-to-all instead of storing them to peers from the pack kernel")
