@@ -101,8 +101,15 @@ struct GemmParams {
 // rows of A and 128 of the 256 rows of B, and holds the accumulator of its 128 rows in its TMEM;
 // one MMA instruction issued by the even CTA drives both tensor cores.  Per CTA and K block that
 // is 32 KB through L2 and shared memory instead of 48 KB for the same arithmetic.
-template <int BN, bool SMALL_A, bool PAIR = false>
+// ASTORE (block-scaled 256-wide tiles with 16-bit outputs): at the end of a tile the epilogue warps
+// only convert their accumulators and park the tile in shared memory; a store warp writes it to
+// global (or peer) memory while the epilogue warps are already folding the next tile's K blocks.
+// In block-scaled mode those warps are needed in every K block, so whatever they do at a tile's end
+// stalls the tensor core once its two accumulator buffers are full.  The parked tile takes the
+// room of one ring stage (three stages instead of four).
+template <int BN, bool SMALL_A, bool PAIR = false, bool ASTORE = false>
 struct Cfg {
+    static_assert(!ASTORE || (BN == 256 && !SMALL_A && !PAIR), "the store warp serves the 256-wide tile");
     static_assert(BN == 32 || BN == 64 || BN == 128 || BN == 256, "unsupported tile width");
     static_assert(!SMALL_A || BN == 32, "the narrow-A layout exists for the 32-wide tile only");
     static_assert(!PAIR || BN == 256, "the CTA-pair layout is built for the 256-wide tile");
@@ -124,14 +131,15 @@ struct Cfg {
     static constexpr int A_BYTES = A_ROWS_SMEM * BLOCK_K;
     static constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * BLOCK_K;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = PAIR ? 6 : BN == 256 ? 4 : BN == 128 ? 6 : BN == 64 ? 8 : (SMALL_A ? 22 : 9);
+    static constexpr int STAGES = ASTORE ? 3 : PAIR ? 6 : BN == 256 ? 4 : BN == 128 ? 6 : BN == 64 ? 8 : (SMALL_A ? 22 : 9);
+    static constexpr int PARK_BYTES = ASTORE ? BLOCK_M * BN * 2 + BLOCK_M * 8 : 0;  // parked tile + one pointer per row
     static constexpr int TAIL_PAD = SMALL_A ? BLOCK_M * BLOCK_K : 0;
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
-    static constexpr int BAR_BYTES = 512;  // (2*STAGES + 4) mbarriers, TMEM base slot, abort flag
-    static_assert((2 * STAGES + 4) * 8 + 16 <= BAR_BYTES, "barrier area too small");
+    static constexpr int BAR_BYTES = 512;  // (2*STAGES + 6) mbarriers, TMEM base slot, abort flag, turn counter
+    static_assert((2 * STAGES + 6) * 8 + 16 <= BAR_BYTES, "barrier area too small");
     static constexpr int EPI_STAGE_BYTES = 2048;  // per epilogue warp: 32 rows x 64 bytes
     static constexpr int SMEM_BYTES =
-        STAGES * STAGE_BYTES + TAIL_PAD + BAR_BYTES + EPI_WARPS * EPI_STAGE_BYTES + 1024;
+        STAGES * STAGE_BYTES + TAIL_PAD + BAR_BYTES + EPI_WARPS * EPI_STAGE_BYTES + PARK_BYTES + 1024;
     static_assert(SMEM_BYTES <= 232448, "over the 227 KB shared memory limit");
     // split-K parks a 128 x BN fp32 partial tile (rows padded by 4 floats) in the ring's memory
     static_assert(SMALL_A || PAIR || BLOCK_M * (BN + 4) * 4 <= STAGES * STAGE_BYTES, "partial tile does not fit");
@@ -276,16 +284,25 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int num_m, int num_n) {
 // leaves its fp32 partial tile in its own shared memory and the cluster adds them up through
 // distributed shared memory (no global scratch, no atomics).  For decode-sized M, where there are
 // fewer tiles than SMs and the job is to pull the weights from HBM with every SM.
-template <int BN, bool BLOCK_SCALED, bool FUSE_SILU, bool SMALL_A, bool SPLITK, bool PAIR = false>
-__global__ void __launch_bounds__(Cfg<BN, SMALL_A, PAIR>::THREADS, 1)
+template <int BN, bool BLOCK_SCALED, bool FUSE_SILU, bool SMALL_A, bool SPLITK, bool PAIR = false, bool ASTORE = false>
+__global__ void __launch_bounds__(Cfg<BN, SMALL_A, PAIR, ASTORE>::THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                 const GemmParams p) {
-    using C = Cfg<BN, SMALL_A, PAIR>;
+    using C = Cfg<BN, SMALL_A, PAIR, ASTORE>;
+    static_assert(!ASTORE || (BLOCK_SCALED && !SPLITK), "the store warp serves the block-scaled tiles");
     static_assert(!SPLITK || (!FUSE_SILU && !SMALL_A && BN >= 128), "split-K is built for the plain wide tiles");
     static_assert(!PAIR || (!SPLITK && !FUSE_SILU && !SMALL_A), "the CTA pair serves the plain dense tiles");
     static_assert(!FUSE_SILU || BN >= 128, "fused SiLU needs a tile of at least 128 columns");
     constexpr int STAGES = C::STAGES;
     constexpr int OUT_TILE_N = FUSE_SILU ? BN / 2 : BN;  // output columns per tile
+    // DUAL (block-scaled wide tiles): warps 1 and 2 issue the MMAs of alternate K blocks.  A K block's
+    // trip through the issuing warp (two barrier waits of ~100 cycles each even when they are already
+    // complete, four MMAs at ~46 cycles of issue each, two commits) measured ~530 cycles, more than
+    // the 512 cycles the tensor core needs for the block, so one warp starves it.  In block-scaled
+    // mode every K block has its own accumulator buffer (block j -> buffer j & 1), so the two warps
+    // never accumulate into the same buffer and need no ordering beyond a turn counter that keeps
+    // the tensor core's queue in K-block order.
+    constexpr bool DUAL = BLOCK_SCALED && !PAIR && !SMALL_A && !SPLITK && BN == 256;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -293,9 +310,14 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* tmem_full = empty_bar + STAGES;
     uint64_t* tmem_empty = tmem_full + 2;
-    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    uint64_t* park_full = tmem_empty + 2;   // ASTORE: the parked tile is complete (all epilogue warps)
+    uint64_t* park_free = park_full + 1;    // ASTORE: the store warp has written it out
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(park_free + 1);
     volatile uint32_t* abort_flag = tmem_base_slot + 1;
+    volatile uint32_t* issued_blocks = tmem_base_slot + 2;  // DUAL: K blocks whose MMAs have been issued
     uint8_t* epi_stage_base = smem + STAGES * C::STAGE_BYTES + C::TAIL_PAD + C::BAR_BYTES;
+    uint8_t* park_tile = epi_stage_base + C::EPI_WARPS * C::EPI_STAGE_BYTES;        // [128][OUT_TILE_N] 16-bit, swizzled
+    unsigned long long* park_rows = reinterpret_cast<unsigned long long*>(park_tile + BLOCK_M * BN * 2);  // row pointers
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;  // 0: issues the MMAs, owns the shared barriers
@@ -309,7 +331,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             mbar_init(&tmem_full[b], 1);
             mbar_init(&tmem_empty[b], PAIR ? 2 * C::EPI_WARPS : C::EPI_WARPS);
         }
+        mbar_init(park_full, C::EPI_WARPS);
+        mbar_init(park_free, 1);
         *abort_flag = 0u;
+        *issued_blocks = 0u;
         fence_mbar_init();
         tma_prefetch_desc(&tm_a);
         tma_prefetch_desc(&tm_b);
@@ -407,6 +432,113 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             }
             FG_PROF_OUT(0, prof_wait);
         }
+    } else if (ASTORE && warp == 3) {
+        // ------------------------------- store warp -----------------------------------------
+        // Writes parked tiles out: one 16-byte piece per lane, a whole row (or two) per instruction,
+        // to the row's own destination (plain, scattered or on a peer GPU).
+        constexpr int ROW_BYTES = OUT_TILE_N * 2;
+        constexpr int LANES_PER_ROW = ROW_BYTES / 16;      // 32 or 16
+        constexpr int ROWS_PER_STEP = 32 / LANES_PER_ROW;  // 1 or 2
+        uint32_t it = 0;
+        bool ok = true;
+        for (int t = tile_first; t < num_tiles && ok; t += tile_step) {
+            const TileCoord tc = tile_coord(t, num_m, num_n);
+            const int expert = p.grouped ? p.expert_ids[tc.m_blk] : 0;
+            if (expert < 0) continue;
+            const int n0 = tc.n_blk * OUT_TILE_N;
+            ok = __all_sync(0xffffffffu, mbar_wait(park_full, it & 1u, abort_flag, p.status, 8));
+            if (!ok) break;
+            const int sub = lane / LANES_PER_ROW, q = lane % LANES_PER_ROW;
+#pragma unroll 4
+            for (int r0 = 0; r0 < BLOCK_M; r0 += ROWS_PER_STEP) {
+                const int r = r0 + sub;
+                const unsigned long long dst = park_rows[r];
+                const int col = n0 + ((q ^ (r & 7)) << 3);
+                if (dst != 0ull && col < p.n_out) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(park_tile + r * ROW_BYTES + (q << 4));
+                    *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(dst) + (size_t)col * 2) = v;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(park_free);
+            ++it;
+        }
+    } else if (DUAL && (warp == 1 || warp == 2)) {
+        // ------------------------------- MMA issuers, alternate K blocks ----------------------
+        constexpr uint32_t idesc = umma_idesc_e4m3_f32(BLOCK_M, BN);
+        const uint32_t me = (uint32_t)(warp - 1);
+        uint32_t j = 0;  // K blocks of this CTA so far, over all its tiles
+        bool ok = true;
+        FG_PROF_DECL(prof_tmem);
+        FG_PROF_DECL(prof_full);
+        FG_PROF_DECL(prof_turn);
+        FG_PROF_DECL(prof_blocks);
+        FG_PROF_T0(prof_start);
+        for (int t = tile_first; t < num_tiles && ok; t += tile_step) {
+            const TileCoord tc = tile_coord(t, num_m, num_n);
+            const int expert = p.grouped ? p.expert_ids[tc.m_blk] : 0;
+            if (expert < 0) continue;
+            for (int kb = kb_begin; kb < kb_end && ok; ++kb, ++j) {
+                if ((j & 1u) != me) continue;
+                const uint32_t stage = j % STAGES, phase = (j / STAGES) & 1u;
+                FG_PROF_T0(tw);
+                ok = __all_sync(0xffffffffu, mbar_wait(&tmem_empty[me], ((j >> 1) & 1u) ^ 1u, abort_flag, p.status, 2));
+                FG_PROF_ADD(prof_tmem, tw);
+                if (!ok) break;
+                // Orders the epilogue's TMEM reads (published by its arrive) before the MMAs that
+                // overwrite the buffer.
+                tc_fence_after_sync();
+                FG_PROF_T0(tw2);
+                ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 3));
+                FG_PROF_ADD(prof_full, tw2);
+                if (!ok) break;
+                // My turn: the other warp has handed block j - 1 to the tensor core.
+                FG_PROF_T0(tw3);
+                {
+                    uint32_t spins = 0;
+                    const uint64_t t0 = global_timer_ns();
+                    while (*issued_blocks != j) {
+                        if ((++spins & 0xffu) == 0u) {
+                            if (*abort_flag) { ok = false; break; }
+                            if (global_timer_ns() - t0 > 2000000000ull) {
+                                *abort_flag = 1u;
+                                if (p.status) atomicCAS(p.status, 0u, (1u << 16) | 6u);
+                                ok = false;
+                                break;
+                            }
+                        }
+                    }
+                }
+                FG_PROF_ADD(prof_turn, tw3);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                if (elect_one()) {
+                    const uint32_t a_addr = smem_u32(smem + stage * C::STAGE_BYTES);
+                    const uint64_t a_desc = umma_desc_k_sw128(a_addr);
+                    const uint64_t b_desc = umma_desc_k_sw128(a_addr + C::A_BYTES);
+                    const uint32_t d_tmem = tmem_base + me * BN;
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+                        umma_f8f6f4(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, k == 0 ? 0u : 1u);
+                    *issued_blocks = j + 1u;
+                    umma_commit(&tmem_full[me]);
+                    umma_commit(&empty_bar[stage]);
+                }
+                __syncwarp();
+#ifdef FG_GEMM_PROFILE
+                ++prof_blocks;
+#endif
+            }
+        }
+#ifdef FG_GEMM_PROFILE
+        if (lane == 0 && me == 0) {
+            FG_PROF_OUT(1, prof_tmem);
+            FG_PROF_OUT(2, prof_full);
+            FG_PROF_OUT(3, clock64() - prof_start);
+            FG_PROF_OUT(4, 2 * prof_blocks);
+            FG_PROF_OUT(11, prof_turn);
+        }
+#endif
     } else if (warp == 1) {
         // ------------------------------- MMA issuer ---------------------------------------
         // The whole warp walks the loop (so that addresses and descriptors stay warp-uniform) and
@@ -515,6 +647,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         FG_PROF_DECL(prof_epi_ld);
         FG_PROF_DECL(prof_epi_fma);
         FG_PROF_T0(prof_epi_start);
+        uint32_t park_iter = 0;  // ASTORE: tiles parked so far
 
         for (int t = tile_first; t < num_tiles && ok; t += tile_step) {
             const TileCoord tc = tile_coord(t, num_m, num_n);
@@ -660,21 +793,49 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 const float* as_row = p.sa + srow * p.ld_as;
                 const float* bs0 = bs_e + nb0 * p.bs_stride_n;
                 const float* bs1 = bs_e + nb1 * p.bs_stride_n;
-                float as_next = as_row[(int64_t)kb_begin * p.as_stride_k];
-                float b0_next = __ldg(bs0 + (int64_t)kb_begin * p.bs_stride_k);
-                float b1_next = FUSE_SILU ? __ldg(bs1 + (int64_t)kb_begin * p.bs_stride_k) : 0.0f;
                 auto chunk_col = [&](int c) -> uint32_t {
                     if constexpr (FUSE_SILU) return (uint32_t)((c < 2 ? 0 : BN / 2) + 64 * half + 32 * (c & 1));
                     else return (uint32_t)(128 * half + 32 * c);
                 };
-                for (int kb = kb_begin; kb < kb_end; ++kb) {
-                    const float sc0f = as_next * b0_next;
-                    const float sc1f = FUSE_SILU ? as_next * b1_next : sc0f;
-                    if (kb + 1 < kb_end) {  // next block's scales travel while this block is folded in
-                        as_next = as_row[(int64_t)(kb + 1) * p.as_stride_k];
-                        b0_next = __ldg(bs0 + (int64_t)(kb + 1) * p.bs_stride_k);
-                        if constexpr (FUSE_SILU) b1_next = __ldg(bs1 + (int64_t)(kb + 1) * p.bs_stride_k);
+                // Scales of four K blocks at a time, fetched one group ahead (a group lasts ~3000
+                // cycles, so the loads are long complete when their turn comes): 16-byte loads where
+                // the K-block scales of a row are contiguous and aligned, four scalar loads otherwise.
+                const bool as_vec = p.as_stride_k == 1 && ((reinterpret_cast<uintptr_t>(as_row) & 15) == 0);
+                const bool bs_vec = p.bs_stride_k == 1 && ((reinterpret_cast<uintptr_t>(bs0) & 15) == 0) &&
+                                    ((reinterpret_cast<uintptr_t>(bs1) & 15) == 0);
+                auto load4 = [&](const float* base, int64_t stride, bool vec, int kb0, bool ldg) -> float4 {
+                    if (vec && (kb0 & 3) == 0 && kb0 + 4 <= num_k_blocks) {
+                        return ldg ? __ldg(reinterpret_cast<const float4*>(base + kb0))
+                                   : *reinterpret_cast<const float4*>(base + kb0);
                     }
+                    float v[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int kk = min(kb0 + i, num_k_blocks - 1);
+                        v[i] = ldg ? __ldg(base + (int64_t)kk * stride) : base[(int64_t)kk * stride];
+                    }
+                    return make_float4(v[0], v[1], v[2], v[3]);
+                };
+                float4 a_nx = load4(as_row, p.as_stride_k, as_vec, kb_begin, false);
+                float4 b0_nx = load4(bs0, p.bs_stride_k, bs_vec, kb_begin, true);
+                float4 b1_nx = FUSE_SILU ? load4(bs1, p.bs_stride_k, bs_vec, kb_begin, true) : b0_nx;
+                float g0[4] = {0.f, 0.f, 0.f, 0.f}, g1[4] = {0.f, 0.f, 0.f, 0.f};  // products of the current group
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
+                    const int in_group = (kb - kb_begin) & 3;
+                    if (in_group == 0) {
+                        g0[0] = a_nx.x * b0_nx.x; g0[1] = a_nx.y * b0_nx.y; g0[2] = a_nx.z * b0_nx.z; g0[3] = a_nx.w * b0_nx.w;
+                        if constexpr (FUSE_SILU) {
+                            g1[0] = a_nx.x * b1_nx.x; g1[1] = a_nx.y * b1_nx.y; g1[2] = a_nx.z * b1_nx.z; g1[3] = a_nx.w * b1_nx.w;
+                        }
+                        if (kb + 4 < kb_end) {
+                            a_nx = load4(as_row, p.as_stride_k, as_vec, kb + 4, false);
+                            b0_nx = load4(bs0, p.bs_stride_k, bs_vec, kb + 4, true);
+                            if constexpr (FUSE_SILU) b1_nx = load4(bs1, p.bs_stride_k, bs_vec, kb + 4, true);
+                        }
+                    }
+                    const float sc0f = in_group == 0 ? g0[0] : in_group == 1 ? g0[1] : in_group == 2 ? g0[2] : g0[3];
+                    const float sc1f = !FUSE_SILU ? sc0f
+                                       : in_group == 0 ? g1[0] : in_group == 1 ? g1[1] : in_group == 2 ? g1[2] : g1[3];
                     const uint64_t sc0 = pack_f32x2(sc0f, sc0f), sc1 = pack_f32x2(sc1f, sc1f);
                     const uint32_t buf = acc_iter & 1u;
                     FG_PROF_T0(tw);
@@ -739,7 +900,48 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 }
                 if (!ok) break;
                 FG_PROF_T0(t_tail);
-                if constexpr (SPLITK) {
+                if constexpr (ASTORE) {
+                    // Park the converted tile for the store warp: rows of OUT_TILE_N 16-bit values, the
+                    // 16-byte pieces of a row XOR-swizzled by (row & 7) so that the 32 rows a warp writes
+                    // at once and the row the store warp reads at once both spread over all banks.
+                    ok = mbar_wait(park_free, (park_iter & 1u) ^ 1u, abort_flag, p.status, 7);
+                    if (!ok) break;
+                    constexpr int ROW_BYTES = OUT_TILE_N * 2;
+                    uint8_t* prow = park_tile + r_in_tile * ROW_BYTES;
+#pragma unroll
+                    for (int c = 0; c < OUT_CHUNKS; ++c) {
+                        uint32_t w[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const uint64_t a = acc[16 * c + i];
+                            float lo, hi;
+                            if constexpr (FUSE_SILU) {
+                                const uint64_t u = acc[32 + 16 * c + i];
+                                lo = silu_mul(f32x2_lo(a), f32x2_lo(u));
+                                hi = silu_mul(f32x2_hi(a), f32x2_hi(u));
+                            } else {
+                                lo = f32x2_lo(a) * weight;
+                                hi = f32x2_hi(a) * weight;
+                            }
+                            if (p.out_dtype == FG_DTYPE_BF16) {
+                                __nv_bfloat162 h2 = __floats2bfloat162_rn(lo, hi);
+                                w[i] = *reinterpret_cast<uint32_t*>(&h2);
+                            } else {
+                                __half2 h2 = __floats2half2_rn(lo, hi);
+                                w[i] = *reinterpret_cast<uint32_t*>(&h2);
+                            }
+                        }
+                        const int piece0 = ((FUSE_SILU ? 64 * half : 128 * half) + 32 * c) / 8;
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            *reinterpret_cast<uint4*>(prow + (((piece0 + k) ^ (r_in_tile & 7)) << 4)) =
+                                make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
+                    }
+                    if (half == 0) park_rows[r_in_tile] = row_ok ? reinterpret_cast<unsigned long long>(out_ptr) : 0ull;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(park_full);
+                    ++park_iter;
+                } else if constexpr (SPLITK) {
                     float* dst = reinterpret_cast<float*>(smem) + (size_t)r_in_tile * (BN + 4) + 128 * half;
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
@@ -998,10 +1200,10 @@ bool pair_enabled() {
     return v != 0;
 }
 
-template <int BN, bool BS, bool SILU, bool SMALL_A = false>
+template <int BN, bool BS, bool SILU, bool SMALL_A = false, bool ASTORE = false>
 int launch_inst(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int max_tiles, cudaStream_t st) {
-    using C = Cfg<BN, SMALL_A>;
-    auto kernel = gemm_fp8_kernel<BN, BS, SILU, SMALL_A, false>;
+    using C = Cfg<BN, SMALL_A, false, ASTORE>;
+    auto kernel = gemm_fp8_kernel<BN, BS, SILU, SMALL_A, false, false, ASTORE>;
     static bool attr_done[64];
     static std::mutex mu;
     {
@@ -1102,6 +1304,10 @@ int launch_gemm(GemmParams& p, const void* a, int64_t a_rows, int64_t ld_a, cons
                             : launch_splitk<128, false>(ta, tb, p, t, k_slices, st);
     }
     if (bn == 256) {
+        // 16-bit outputs with 16-byte aligned rows: the tile is parked and written out by the store warp
+        const bool park = block_scaled && esz == 2 && p.c_vec_ok && p.n_out % 8 == 0;
+        if (park) return fuse_silu ? launch_inst<256, true, true, false, true>(ta, tb, p, t, st)
+                                   : launch_inst<256, true, false, false, true>(ta, tb, p, t, st);
         if (block_scaled) return fuse_silu ? launch_inst<256, true, true>(ta, tb, p, t, st)
                                            : launch_inst<256, true, false>(ta, tb, p, t, st);
         return fuse_silu ? launch_inst<256, false, true>(ta, tb, p, t, st)

@@ -70,6 +70,7 @@ __device__ __forceinline__ bool elect_one() {
 // warp to give up records (code 1, site) in the global status word and raises the flag.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           unsigned int* status, uint32_t site, uint64_t limit_ns = 2000000000ull) {
+    if (mbar_test_wait(bar, parity)) return true;  // the cheap probe first: a phase that is already complete
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
     uint32_t spins = 0;
