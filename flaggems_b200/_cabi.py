@@ -66,6 +66,14 @@ _SIGS = {
         c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int64, _P, _P, _P, c_int64, c_int64, c_int, c_int64, c_int64,
                 c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int64, _P, c_int, c_int64,
                 _P]),
+    "fg_scaled_grouped_mm_workspace_bytes": (c_int64, [c_int64, c_int, c_int64]),
+    "fg_scaled_grouped_mm_fp8": (
+        c_int, [_P, _P, _P, _P, _P, _P, c_int64, _P, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int,
+                _P, c_int64, _P]),
+    "fg_group_ids_from_offsets": (c_int, [_P, c_int, c_int64, _P, _P]),
+    "fg_grouped_gemm_fp8_bias": (
+        c_int, [_P, _P, _P, _P, _P, _P, c_int64, _P, _P, _P, c_int64, c_int64, c_int, c_int64, c_int64, c_int64,
+                c_int64, c_int, _P]),
     "fg_symm_alloc": (c_int, [c_int64, ctypes.POINTER(c_void_p), _P]),
     "fg_symm_open": (c_int, [_P, ctypes.POINTER(c_void_p)]),
     "fg_symm_close": (c_int, [_P]),

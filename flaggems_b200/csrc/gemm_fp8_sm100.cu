@@ -66,7 +66,8 @@ struct GemmParams {
     void* c;
     int64_t ld_c;
     int out_dtype;
-    int bias_dtype;  // element type of bias (the output type, or fp32 when the output is e4m3)
+    int bias_dtype;  // element type of bias (the output type, or fp32 when the output is e4m3 / for grouped mm)
+    int64_t bias_stride_e;  // grouped: elements between the bias rows of consecutive experts (0: one row)
     int c_vec_ok;  // rows of C are 16-byte aligned
     const float* sa;
     const float* sb;
@@ -752,7 +753,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                             float x = sb * (sa * __uint_as_float(raw[i]));
                             x *= weight;
                             if (p.bias) {
-                                const float b = load_as_float(p.bias, p.bias_dtype, n);
+                                const float b = load_as_float(p.bias, p.bias_dtype, n + (int64_t)expert * p.bias_stride_e);
                                 x = p.bias_after_round ? round_through(x, p.out_dtype) + b : x + b;
                             }
                             v[i] = x;
@@ -1230,7 +1231,6 @@ int launch_gemm(GemmParams& p, const void* a, int64_t a_rows, int64_t ld_a, cons
                FG_ERR_UNSUPPORTED, "a and b must be 16-byte aligned with row strides that are multiples of 16 bytes");
     FG_REQUIRE(ld_a >= p.K && ld_b >= p.K, FG_ERR_INVALID_ARGUMENT, "row stride smaller than K");
     p.status = fg_status_word_device_ptr();
-    if (p.out_dtype != FG_DTYPE_E4M3) p.bias_dtype = p.out_dtype;
     const int esz = out_elem_size(p.out_dtype);
     p.c_vec_ok = ((uintptr_t)p.c % 16 == 0) && ((p.ld_c * esz) % 16 == 0);
 
@@ -1382,7 +1382,7 @@ int fg_scaled_mm_fp8(void* c, const void* a, const void* b, const float* sa, con
     p.c = c; p.ld_c = ld_c; p.out_dtype = out_dtype;
     p.sa = sa; p.sb = sb; p.bias = bias; p.sa_mode = sa_mode; p.sb_mode = sb_mode;
     p.bias_after_round = bias_after_round;
-    p.bias_dtype = FG_DTYPE_F32;  // used when the output is e4m3; otherwise the bias has the output type
+    p.bias_dtype = out_dtype == FG_DTYPE_E4M3 ? FG_DTYPE_F32 : out_dtype;  // fp32 bias only with the e4m3 output
     p.block_rows = BLOCK_M;
     return launch_gemm(p, a, M, ld_a, b, 1, ld_b, false, false, (cudaStream_t)stream);
 }
@@ -1415,6 +1415,29 @@ int fg_moe_grouped_gemm_fp8(void* c, const void* a, const void* w, const float* 
                                         sorted_ids, expert_ids, num_post_pad, max_rows, numel, num_experts, N, K,
                                         ld_a, ld_c, block_rows, scale_mode, a_scale_per_row, fuse_silu, scatter,
                                         mul_weight, out_dtype, nullptr, 0, nullptr, 0, 0, stream);
+}
+
+// Grouped GEMM with a per-row x per-column scale pair and an optional fp32 bias row per group (or one
+// row for all groups): the device work of aten _scaled_grouped_mm, see fg_scaled_grouped_mm_fp8.
+int fg_grouped_gemm_fp8_bias(void* c, const void* a, const void* w, const float* a_scale, const float* w_scale,
+                             const float* bias, int64_t bias_stride_g, const int32_t* sorted_ids,
+                             const int32_t* expert_ids, const int32_t* num_post_pad, int64_t max_rows, int64_t numel,
+                             int num_groups, int64_t N, int64_t K, int64_t ld_a, int64_t ld_c, int out_dtype,
+                             void* stream) {
+    FG_REQUIRE(max_rows >= 0 && N > 0 && K > 0 && num_groups > 0, FG_ERR_INVALID_ARGUMENT, "bad sizes");
+    FG_REQUIRE(c && a && w && a_scale && w_scale && sorted_ids && expert_ids && num_post_pad, FG_ERR_INVALID_ARGUMENT,
+               "null pointer");
+    FG_REQUIRE(dtype_ok(out_dtype), FG_ERR_INVALID_ARGUMENT, "bad out_dtype %d", out_dtype);
+    FG_REQUIRE(N < (1ll << 31) && K < (1ll << 31), FG_ERR_UNSUPPORTED, "dimension too large");
+    if (max_rows == 0) return FG_OK;
+    GemmParams p{};
+    p.M = max_rows / BLOCK_M * BLOCK_M; p.N = (int)N; p.K = (int)K; p.n_out = (int)N;
+    p.c = c; p.ld_c = ld_c; p.out_dtype = out_dtype;
+    p.sa = a_scale; p.sb = w_scale; p.sa_mode = FG_SCALE_VECTOR; p.sb_mode = FG_SCALE_VECTOR; p.sb_stride_e = N;
+    p.bias = bias; p.bias_dtype = FG_DTYPE_F32; p.bias_stride_e = bias_stride_g; p.bias_after_round = 0;
+    p.grouped = 1; p.sorted_ids = sorted_ids; p.expert_ids = expert_ids; p.num_post_pad = num_post_pad;
+    p.block_rows = BLOCK_M; p.numel = numel; p.scatter = 1; p.mul_weight = 0; p.topk_w_stride = 1;
+    return launch_gemm(p, a, p.M, ld_a, w, num_groups, K, false, false, (cudaStream_t)stream);
 }
 
 int fg_moe_grouped_gemm_fp8_peer(void* c, const void* a, const void* w, const float* a_scale, const float* w_scale,

@@ -282,6 +282,21 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint8_t* __restr
     }
 }
 
+// Group of every row from the ends of the groups: ids[r] = number of offsets <= r (rows past the last
+// end get num_groups, which the alignment kernel ignores).
+__global__ void __launch_bounds__(256) group_ids_kernel(const int32_t* __restrict__ offs, int num_groups, int64_t rows,
+                                                        int32_t* __restrict__ ids) {
+    for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += (int64_t)gridDim.x * blockDim.x) {
+        int lo = 0, hi = num_groups;  // first g with offs[g] > r
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if ((int64_t)offs[mid] > r) hi = mid;
+            else lo = mid + 1;
+        }
+        ids[r] = lo;
+    }
+}
+
 unsigned grid_for(int64_t work_items, int per_block) {
     int64_t b = fg_cdiv(work_items, per_block);
     const int64_t cap = (int64_t)fg_num_sms() * 16;
@@ -375,6 +390,16 @@ int fg_moe_align_block_size_regions(const void* topk_ids, int ids_are_i64, int64
     cfg.numAttrs = 1;
     FG_CUDA(cudaLaunchKernelEx(&cfg, kernel, a));
     fg_count_launch(1);
+    return FG_OK;
+}
+
+int fg_group_ids_from_offsets(const int32_t* offs, int num_groups, int64_t rows, int32_t* ids, void* stream) {
+    FG_REQUIRE(num_groups > 0 && rows >= 0, FG_ERR_INVALID_ARGUMENT, "bad sizes");
+    if (rows == 0) return FG_OK;
+    FG_REQUIRE(offs && ids, FG_ERR_INVALID_ARGUMENT, "null pointer");
+    group_ids_kernel<<<grid_for(rows, 256), 256, 0, (cudaStream_t)stream>>>(offs, num_groups, rows, ids);
+    fg_count_launch(1);
+    FG_LAUNCH_CHECK();
     return FG_OK;
 }
 

@@ -100,7 +100,75 @@ int builtin_scratch(void** out) {
 
 }  // namespace
 
+namespace {
+
+// Scratch of fg_scaled_grouped_mm_fp8.
+struct GroupedMmWorkspace {
+    int32_t* group_ids;
+    int32_t* sorted_ids;
+    int32_t* expert_ids;
+    int32_t* post_pad;
+    uint8_t* a_sorted;
+    float* sa_sorted;
+    int64_t max_pad, n_blocks, rows, bytes;
+};
+
+GroupedMmWorkspace carve_grouped_mm(void* base, int64_t m_total, int num_groups, int64_t K) {
+    GroupedMmWorkspace w{};
+    w.max_pad = m_total + (int64_t)num_groups * (TILE_ROWS - 1);
+    w.n_blocks = fg_cdiv(w.max_pad, TILE_ROWS);
+    w.rows = w.max_pad / TILE_ROWS * TILE_ROWS;
+    uint8_t* p = reinterpret_cast<uint8_t*>(base);
+    int64_t off = 0;
+    auto take = [&](int64_t bytes) {
+        uint8_t* r = p ? p + off : nullptr;
+        off += align_up(bytes, 256);
+        return r;
+    };
+    w.group_ids = (int32_t*)take(4 * m_total);
+    w.sorted_ids = (int32_t*)take(4 * w.max_pad);
+    w.expert_ids = (int32_t*)take(4 * w.n_blocks);
+    w.post_pad = (int32_t*)take(256);
+    w.a_sorted = take(w.rows * K);
+    w.sa_sorted = (float*)take(4 * w.rows);
+    w.bytes = off;
+    return w;
+}
+
+}  // namespace
+
 extern "C" {
+
+int64_t fg_scaled_grouped_mm_workspace_bytes(int64_t m_total, int num_groups, int64_t K) {
+    if (m_total < 0 || num_groups <= 0 || K <= 0) return -1;
+    return carve_grouped_mm(nullptr, m_total, num_groups, K).bytes;
+}
+
+int fg_scaled_grouped_mm_fp8(void* c, const void* a, const void* b, const float* scale_a, const float* scale_b,
+                             const float* bias, int64_t bias_stride_g, const int32_t* offs, int num_groups,
+                             int64_t m_total, int64_t N, int64_t K, int64_t ld_a, int64_t ld_c, int out_dtype,
+                             void* workspace, int64_t workspace_bytes, void* stream) {
+    FG_REQUIRE(m_total >= 0 && N > 0 && K > 0 && num_groups > 0, FG_ERR_INVALID_ARGUMENT, "bad sizes");
+    FG_REQUIRE(num_groups <= 1024, FG_ERR_UNSUPPORTED, "at most 1024 groups");
+    FG_REQUIRE(K % 16 == 0, FG_ERR_UNSUPPORTED, "K = %lld must be a multiple of 16", (long long)K);
+    if (m_total == 0) return FG_OK;
+    FG_REQUIRE(c && a && b && scale_a && scale_b && offs && workspace, FG_ERR_INVALID_ARGUMENT, "null pointer");
+    FG_REQUIRE((uintptr_t)workspace % 256 == 0, FG_ERR_INVALID_ARGUMENT, "workspace must be 256-byte aligned");
+    const GroupedMmWorkspace ws = carve_grouped_mm(workspace, m_total, num_groups, K);
+    FG_REQUIRE(workspace_bytes >= ws.bytes, FG_ERR_INVALID_ARGUMENT, "workspace holds %lld bytes, needs %lld",
+               (long long)workspace_bytes, (long long)ws.bytes);
+    int rc = fg_group_ids_from_offsets(offs, num_groups, m_total, ws.group_ids, stream);
+    if (rc != FG_OK) return rc;
+    rc = fg_moe_align_block_size(ws.group_ids, 0, m_total, num_groups, TILE_ROWS, nullptr, 0, ws.sorted_ids, ws.max_pad,
+                                 ws.expert_ids, ws.n_blocks, ws.post_pad, stream);
+    if (rc != FG_OK) return rc;
+    rc = fg_gather_rows_fp8(a, scale_a, ws.a_sorted, ws.sa_sorted, ws.rows, K, 1, ld_a, 1, ws.sorted_ids, 1,
+                            (int32_t)m_total, ws.post_pad, stream);
+    if (rc != FG_OK) return rc;
+    return fg_grouped_gemm_fp8_bias(c, ws.a_sorted, b, ws.sa_sorted, scale_b, bias, bias_stride_g, ws.sorted_ids,
+                                    ws.expert_ids, ws.post_pad, ws.rows, m_total, num_groups, N, K, K, ld_c, out_dtype,
+                                    stream);
+}
 
 int64_t fg_moe_routed_workspace_bytes(int64_t n_rows_in, int num_experts, int64_t H, int64_t I) {
     if (n_rows_in < 0 || num_experts <= 0 || H <= 0 || I <= 0) return -1;

@@ -13,16 +13,17 @@ import warnings
 
 import torch
 
+from .ops.scaled_grouped_mm import scaled_grouped_mm
 from .ops.scaled_mm import scaled_mm, scaled_mm_out
 
 aten_lib = torch.library.Library("aten", "IMPL")
 
-# (aten key, implementation): the FP8 hot path has two aten-visible entry points
-# (reference: src/flag_gems/__init__.py:230-231).
+# (aten key, implementation): the aten-visible entry points of the FP8 hot path
+# (reference: src/flag_gems/__init__.py:229-231; _scaled_grouped_mm exists from torch 2.8 on).
 _FULL_CONFIG = (
     ("_scaled_mm", scaled_mm),
     ("_scaled_mm.out", scaled_mm_out),
-)
+) + ((("_scaled_grouped_mm", scaled_grouped_mm),) if hasattr(torch, "_scaled_grouped_mm") else ())
 
 FULL_CONFIG_BY_FUNC = {}
 for _key, _fn in _FULL_CONFIG:

@@ -363,6 +363,35 @@ int fg_moe_grouped_gemm_fp8(void* c, const void* a, const void* w, const float* 
                             int block_rows, int scale_mode, int a_scale_per_row, int fuse_silu,
                             int scatter, int mul_weight, int out_dtype, void* stream);
 
+/* ---- aten _scaled_grouped_mm ------------------------------------------------ */
+
+/* scaled_grouped_mm, the "A 2-D, B 3-D" form: src/flag_gems/ops/scaled_grouped_mm.py:470-583 (kernel
+ * :65-240).  a e4m3 [m_total, K] (row stride ld_a), rows [offs[g-1], offs[g]) belong to group g
+ * (offs: device int32 [num_groups], ascending, offs[-1] <= m_total); b e4m3 [num_groups, N, K]
+ * contiguous (the K-contiguous storage of the reference's [G, K, N] operand); scale_a fp32 [m_total],
+ * scale_b fp32 [num_groups, N]; bias fp32, NULL, one row [N] (bias_stride_g = 0) or one row per
+ * group (bias_stride_g = N).  c[m, n] = out((acc * scale_a[m]) * scale_b[g, n] + bias) (ld_c).
+ * The other three forms of the reference op (both 3-D, B 2-D, both 2-D) are composed from this one by
+ * the Python host.  Group ends are read on the device: no host synchronisation.  Scratch is the
+ * caller's workspace of fg_scaled_grouped_mm_workspace_bytes(m_total, num_groups, K) bytes, 256-byte
+ * aligned. */
+int64_t fg_scaled_grouped_mm_workspace_bytes(int64_t m_total, int num_groups, int64_t K);
+int fg_scaled_grouped_mm_fp8(void* c, const void* a, const void* b, const float* scale_a, const float* scale_b,
+                             const float* bias, int64_t bias_stride_g, const int32_t* offs, int num_groups,
+                             int64_t m_total, int64_t N, int64_t K, int64_t ld_a, int64_t ld_c, int out_dtype,
+                             void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Pieces of the above.  fg_group_ids_from_offsets: ids[r] = number of offsets <= r (the group of
+ * row r; num_groups for rows past the last end).  fg_grouped_gemm_fp8_bias: the grouped GEMM of
+ * fused_moe_kernel (src/flag_gems/fused/fused_moe.py:1015-1509) with per-row x per-column scales, rows
+ * scattered back through sorted_ids, and an fp32 bias added before the cast. */
+int fg_group_ids_from_offsets(const int32_t* offs, int num_groups, int64_t rows, int32_t* ids, void* stream);
+int fg_grouped_gemm_fp8_bias(void* c, const void* a, const void* w, const float* a_scale, const float* w_scale,
+                             const float* bias, int64_t bias_stride_g, const int32_t* sorted_ids,
+                             const int32_t* expert_ids, const int32_t* num_post_pad, int64_t max_rows,
+                             int64_t numel, int num_groups, int64_t N, int64_t K, int64_t ld_a, int64_t ld_c,
+                             int out_dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -27,7 +27,7 @@ from .quant import (  # noqa: F401
     quantize_weight_per_channel,
     quantize_weight_block,
 )
-from .gemm import scaled_mm, block_scaled_mm  # noqa: F401
+from .gemm import scaled_mm, block_scaled_mm, scaled_grouped_mm  # noqa: F401
 from .router import topk_softmax, grouped_topk  # noqa: F401
 from .moe import (  # noqa: F401
     moe_align_block_size,

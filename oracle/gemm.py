@@ -81,3 +81,49 @@ def block_scaled_mm(
         part = torch.mm(af[:, ks], bf[:, ks].t())
         c += part * a_s[:, i : i + 1] * bs_cols[:, i].reshape(1, -1)
     return c.reshape(a.shape[:-1] + (n,)).to(out_dtype)
+
+
+def scaled_grouped_mm(mat_a, mat_b, scale_a, scale_b, offs=None, bias=None, out_dtype=torch.bfloat16):
+    """aten _scaled_grouped_mm in fp32 on the CPU: ``(chunk_a @ chunk_b) * scale_a * scale_b (+ bias)`` per group,
+    cast to out_dtype, for the four operand forms (A 2-D / B 3-D rows grouped by offs; both 3-D; A 3-D / B 2-D
+    columns grouped; both 2-D with the K range split).
+
+    Follows the reference's own statement of the op, src/flag_gems/ops/scaled_grouped_mm.py:379-467
+    (``_scaled_grouped_mm_fallback``), which is also the golden of tests/test_scaled_grouped_mm.py:129-215.
+    """
+    a_is_2d, b_is_2d = mat_a.dim() == 2, mat_b.dim() == 2
+    a, b = mat_a.float(), mat_b.float()
+    sa, sb = scale_a.float(), scale_b.float()
+    bias = None if bias is None else bias.float()
+    starts = [0] + ([] if offs is None else offs.tolist())
+
+    def finish(chunk, s_a, s_b, bi):
+        chunk = chunk * s_a.reshape(-1, 1) * s_b.reshape(1, -1)
+        if bi is not None:
+            chunk = chunk + bi
+        return chunk.to(out_dtype)
+
+    chunks = []
+    if a_is_2d and not b_is_2d:
+        for g in range(b.shape[0]):
+            lo, hi = starts[g], starts[g + 1]
+            bi = None if bias is None else (bias if bias.dim() == 1 else bias[g])
+            chunks.append(finish(a[lo:hi] @ b[g], sa[lo:hi], sb[g], bi))
+        return torch.cat(chunks, 0)
+    if not a_is_2d and b_is_2d:
+        for g in range(a.shape[0]):
+            lo, hi = starts[g], starts[g + 1]
+            chunks.append(finish(a[g] @ b[:, lo:hi], sa[g], sb[lo:hi], None if bias is None else bias[lo:hi]))
+        return torch.cat(chunks, 1)
+    if a_is_2d and b_is_2d:
+        groups = len(starts) - 1
+        sa, sb = sa.reshape(groups, a.shape[0]), sb.reshape(groups, b.shape[1])
+        for g in range(groups):
+            lo, hi = starts[g], starts[g + 1]
+            bi = None if bias is None else (bias if bias.dim() == 1 else bias[g])
+            chunks.append(finish(a[:, lo:hi] @ b[lo:hi], sa[g], sb[g], bi))
+        return torch.stack(chunks, 0)
+    for g in range(a.shape[0]):
+        bi = None if bias is None else (bias if bias.dim() == 1 else bias[g])
+        chunks.append(finish(a[g] @ b[g], sa[g], sb[g], bi))
+    return torch.stack(chunks, 0)

@@ -280,3 +280,105 @@ def test_gemm_full_size_linearity():
 
 def test_no_device_errors_recorded():
     assert _cabi.device_status() == 0
+
+
+# ---- aten _scaled_grouped_mm ---------------------------------------------------------------
+def _grouped_case(case, g, groups=3, m=5, n=16, k=32):
+    def mk(*shape):
+        return (torch.randn(*shape, generator=g) * 0.25).to(FP8)
+
+    if case == "m_varying":
+        sizes = [2, 3, 4] if groups == 3 else [int(x) for x in torch.randint(0, 3 * m, (groups,), generator=g)]
+        total = sum(sizes)
+        offs = torch.tensor(sizes, dtype=torch.int32).cumsum(0).to(torch.int32)
+        return mk(total, k), mk(groups, n, k).transpose(1, 2), torch.linspace(0.75, 1.25, total), \
+            torch.linspace(1.25, 0.75, groups * n).reshape(groups, n), offs
+    if case == "batch":
+        return mk(groups, m, k), mk(groups, n, k).transpose(1, 2), torch.linspace(0.75, 1.25, groups * m).reshape(groups, m), \
+            torch.linspace(1.25, 0.75, groups * n).reshape(groups, n), None
+    if case == "k_varying":
+        offs = torch.tensor([8, 20, k], dtype=torch.int32)
+        return mk(m, k), mk(n, k).t(), torch.linspace(0.75, 1.25, 3 * m), torch.linspace(1.25, 0.75, 3 * n), offs
+    offs = torch.tensor([8, 20, 32], dtype=torch.int32)
+    return mk(groups, m, k), mk(32, k).t(), torch.linspace(0.75, 1.25, groups * m).reshape(groups, m), \
+        torch.linspace(1.25, 0.75, 32), offs
+
+
+@pytest.mark.parametrize("case", ["m_varying", "batch", "k_varying", "n_varying"])
+@pytest.mark.parametrize("use_bias", [False, True])
+@pytest.mark.parametrize("out_dtype", [None, torch.float32])
+def test_aten_scaled_grouped_mm(case, use_bias, out_dtype):
+    """The four operand forms, shapes, scales and bias kinds of tests/test_scaled_grouped_mm.py:60-127, through
+    torch._scaled_grouped_mm under use_gems(); rtol/atol 1e-2 against the fp32 oracle (the reference's own
+    FP8 tolerance there is rtol 0.5 / atol 0.25)."""
+    g = torch.Generator().manual_seed(21)
+    a, b, sa, sb, offs = _grouped_case(case, g)
+    n = b.shape[-1]
+    bias = None
+    if use_bias:
+        bias = torch.randn(3, n, generator=g) if case in ("batch", "k_varying") else torch.randn(n, generator=g)
+    target = out_dtype or torch.bfloat16
+    ref = oracle.scaled_grouped_mm(a, b, sa, sb, offs, bias, target)
+    dev = lambda t: None if t is None else t.cuda()  # noqa: E731
+    with flag_gems.use_gems():
+        res = torch._scaled_grouped_mm(dev(a), dev(b), dev(sa), dev(sb), offs=dev(offs), bias=dev(bias),
+                                       out_dtype=out_dtype, use_fast_accum=True)
+    assert res.dtype == target and res.shape == ref.shape
+    _close(res, ref)
+
+
+@pytest.mark.parametrize("groups,m_avg,n,k", [(8, 300, 512, 1024), (64, 40, 2048, 7168), (5, 1, 256, 128)])
+def test_scaled_grouped_mm_ragged_groups(groups, m_avg, n, k):
+    """Groups of very different sizes, some empty, rows left over after the last group end untouched."""
+    g = torch.Generator().manual_seed(22)
+    sizes = torch.randint(0, 2 * m_avg + 1, (groups,), generator=g)
+    sizes[1] = 0
+    total = int(sizes.sum()) + 3  # three rows past the last group end
+    offs = sizes.cumsum(0).to(torch.int32)
+    a = (torch.randn(total, k, generator=g) * 0.5).to(FP8)
+    w = (torch.randn(groups, n, k, generator=g) * 0.5).to(FP8)
+    sa, sb = torch.rand(total, generator=g) + 0.5, torch.rand(groups, n, generator=g) * 0.02
+    bias = torch.randn(groups, n, generator=g)
+    out = flag_gems.scaled_grouped_mm(a.cuda(), w.cuda().transpose(1, 2), sa.cuda(), sb.cuda(), offs.cuda(), bias.cuda())
+    used = int(offs[-1])
+    ref = oracle.scaled_grouped_mm(a[:used], w.transpose(1, 2), sa[:used], sb, offs, bias)
+    _close(out[:used], ref)
+    assert _cabi.device_status() == 0
+
+
+# ---- batched block-scaled products ------------------------------------------------------------
+@pytest.mark.parametrize("b,m,n,k", [(4, 37, 256, 512), (2, 300, 384, 1024), (16, 8, 128, 512)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_w8a8_block_fp8_bmm(b, m, n, k, out_dtype):
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(b, m, k, generator=g).bfloat16()
+    xq, xs = oracle.per_token_group_quant_fp8(x, 128)
+    yq = torch.empty(b, n, k, dtype=FP8)
+    ys = torch.empty(b, n // 128, k // 128)
+    for i in range(b):
+        yq[i], ys[i] = oracle.quantize_weight_block(torch.randn(n, k, generator=g) * 0.05)
+    z = flag_gems.w8a8_block_fp8_bmm(xq.cuda(), yq.cuda(), xs.cuda(), ys.cuda(), [128, 128], output_dtype=out_dtype)
+    assert z.shape == (b, m, n) and z.dtype == out_dtype
+    for i in range(b):
+        _close(z[i], oracle.block_scaled_mm(xq[i], yq[i], xs[i], ys[i], out_dtype=out_dtype))
+    z2 = torch.full((b, m, n), 7.0, dtype=out_dtype, device="cuda")
+    ret = flag_gems.w8a8_block_fp8_bmm(xq.cuda(), yq.cuda(), xs.cuda(), ys.cuda(), z=z2, output_dtype=out_dtype)
+    assert ret.data_ptr() == z2.data_ptr() and torch.equal(z2, z)
+
+
+def test_fp8_einsum_bhr_hdr_bhd():
+    """DeepSeek-style absorbed projection: out[b,h,d] = sum_r x[b,h,r] y[h,d,r], permuted views, no copies."""
+    g = torch.Generator().manual_seed(32)
+    b, h, r, d = 48, 8, 512, 256
+    x = torch.randn(b, h, r, generator=g).bfloat16()
+    xq, xs = oracle.per_token_group_quant_fp8(x, 128)
+    yq = torch.empty(h, d, r, dtype=FP8)
+    ys = torch.empty(h, d // 128, r // 128)
+    for i in range(h):
+        yq[i], ys[i] = oracle.quantize_weight_block(torch.randn(d, r, generator=g) * 0.05)
+    z = flag_gems.fp8_einsum("bhr,hdr->bhd", xq.cuda(), xs.cuda(), yq.cuda(), ys.cuda())
+    assert z.shape == (b, h, d) and z.dtype == torch.bfloat16 and z.is_contiguous()
+    for i in range(h):
+        _close(z[:, i], oracle.block_scaled_mm(xq[:, i].contiguous(), yq[i], xs[:, i].contiguous(), ys[i]))
+    with pytest.raises(AssertionError):
+        flag_gems.fp8_einsum("bhr,hrd->bhd", xq.cuda(), xs.cuda(), yq.cuda(), ys.cuda())

@@ -6,10 +6,12 @@ import flag_gems
 
 def test_use_gems_registers_and_restores():
     with flag_gems.use_gems():
-        assert flag_gems.all_registered_keys() == ["_scaled_mm", "_scaled_mm.out"]
-        assert flag_gems.all_registered_ops() == ["scaled_mm", "scaled_mm_out"]
-    with flag_gems.use_gems(exclude=["scaled_mm_out"]):
+        assert flag_gems.all_registered_keys() == ["_scaled_mm", "_scaled_mm.out", "_scaled_grouped_mm"]
+        assert flag_gems.all_registered_ops() == ["scaled_mm", "scaled_mm_out", "scaled_grouped_mm"]
+    with flag_gems.use_gems(exclude=["scaled_mm_out", "scaled_grouped_mm"]):
         assert flag_gems.all_registered_keys() == ["_scaled_mm"]
+    with flag_gems.use_gems(include=["scaled_grouped_mm"]):
+        assert flag_gems.all_registered_keys() == ["_scaled_grouped_mm"]
     with flag_gems.use_gems(include=["scaled_mm_out"]):
         assert flag_gems.all_registered_keys() == ["_scaled_mm.out"]
 
@@ -96,3 +98,55 @@ def test_unsupported_modes_raise_cleanly():
         flag_gems.fused_experts_impl(h, w1, w2, tw, ti)
     with pytest.raises(AssertionError):
         flag_gems.fused_experts_impl(h, w1, w2, tw, ti, activation="gelu", use_fp8_w8a8=True)
+
+
+def test_scaled_grouped_mm_argument_checks():
+    """Messages of src/flag_gems/ops/scaled_grouped_mm.py:262-366, raised before any device work."""
+    import pytest
+
+    fp8 = torch.float8_e4m3fn
+    a2, b3 = torch.zeros(9, 32).to(fp8), torch.zeros(3, 32, 16).to(fp8)
+    sa, sb = torch.ones(9), torch.ones(3, 16)
+    offs = torch.tensor([2, 5, 9], dtype=torch.int32)
+    f = flag_gems.scaled_grouped_mm
+    with pytest.raises(RuntimeError, match="offs must be provided"):
+        f(a2, b3, sa, sb)
+    with pytest.raises(RuntimeError, match="offs has to be int32"):
+        f(a2, b3, sa, sb, offs.long())
+    with pytest.raises(RuntimeError, match="offs length must match the group count"):
+        f(a2, b3, sa, sb, offs[:2])
+    with pytest.raises(RuntimeError, match="scale_a must be a 1D tensor with length 9"):
+        f(a2, b3, sa[:8], sb, offs)
+    with pytest.raises(RuntimeError, match="scale_b must have shape"):
+        f(a2, b3, sa, sb[:2], offs)
+    with pytest.raises(RuntimeError, match="cannot be multiplied"):
+        f(a2, torch.zeros(3, 16, 16).to(fp8), sa, sb, offs)
+    with pytest.raises(RuntimeError, match="same dtype"):
+        f(a2, b3.float(), sa, sb, offs)
+    with pytest.raises(RuntimeError, match="scale_result is not supported"):
+        f(a2, b3, sa, sb, offs, scale_result=torch.ones(1))
+    with pytest.raises(RuntimeError, match="bias must have shape"):
+        f(a2, b3, sa, sb, offs, bias=torch.zeros(7))
+    with pytest.raises(RuntimeError, match="offs must be None when both inputs are 3D"):
+        f(torch.zeros(3, 5, 32).to(fp8), b3, torch.ones(3, 5), sb, offs)
+    with pytest.raises(RuntimeError, match="mat_a has to be 2D or 3D"):
+        f(a2[0], b3, sa, sb, offs)
+    with pytest.raises(Exception, match="CUDA tensors only"):  # valid arguments on the CPU: no fallback
+        f(a2, b3, sa, sb, offs)
+
+
+def test_scaled_grouped_mm_oracle_against_einsum():
+    """The oracle of the new op against an independent formulation, all four operand forms."""
+    import oracle
+
+    g = torch.Generator().manual_seed(0)
+    fp8 = torch.float8_e4m3fn
+    a = (torch.randn(3, 5, 32, generator=g) * 0.25).to(fp8)
+    b = (torch.randn(3, 32, 16, generator=g) * 0.25).to(fp8)
+    sa, sb = torch.rand(3, 5, generator=g) + 0.5, torch.rand(3, 16, generator=g) + 0.5
+    ref = torch.einsum("gmk,gkn->gmn", a.float(), b.float()) * sa[:, :, None] * sb[:, None, :]
+    out = oracle.scaled_grouped_mm(a, b, sa, sb, out_dtype=torch.float32)
+    torch.testing.assert_close(out, ref)
+    offs = torch.tensor([5, 10, 15], dtype=torch.int32)
+    out2 = oracle.scaled_grouped_mm(a.reshape(15, 32), b, sa.reshape(-1), sb, offs, out_dtype=torch.float32)
+    torch.testing.assert_close(out2.reshape(3, 5, 16), ref)
