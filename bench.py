@@ -782,6 +782,95 @@ def cpu_legs_single_gpu(args, layer, hidden_d, tw_d, ti_d, hidden_h, tw_h, ti_h,
     return out
 
 
+# ---------------------------------------------------------------------------------------------
+# small single-kernel cases for profiler captures (not benchmark lines)
+# ---------------------------------------------------------------------------------------------
+def run_capture_case(args):
+    """A few launches of ONE kernel on a case small enough for a profiler capture (inputs larger than
+    L2, at most a few GB on the device).  Prints a JSON line marked "capture_case": never a bench value.
+      moe_gemm1    grouped block-scaled GEMM1 with fused SiLU, 32 experts / the rows the T=8192 router sends
+                   them (one rank's share at 8 ranks; an eighth of the single-GPU launch)
+      moe_gemm2    the matching GEMM2 (router weight, rows scattered back)
+      block_mm     w8a8 block-scaled GEMM, M = N = 8192, K = 7168
+      scaled_mm    per-token x per-channel GEMM, same shape
+      group_quant  per_token_group_quant_fp8 and act_quant on [16384, 7168] bf16"""
+    import flag_gems
+    from flaggems_b200 import _cabi
+    from flaggems_b200.fused.fused_moe import _TILE_ROWS, _group_quant, _grouped_gemm
+    from flaggems_b200.fused.moe_align_block_size import moe_align_block_size
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev)
+    g.manual_seed(0)
+    name, n_launch = args.workload, max(1, args.steps)
+    if name in ("moe_gemm1", "moe_gemm2"):
+        e = 32
+        w1, w2, s1, s2 = make_expert_weights(e, 0, dev)
+        from flaggems_b200.ep import balanced_expert_placement
+
+        _, ti = make_router(TOKENS, EXPERTS, TOPK)
+        ti = balanced_expert_placement(torch.bincount(ti.reshape(-1), minlength=EXPERTS), EXPERTS // e)[ti]
+        ids = ti[ti < e].to(torch.int32).to(dev)  # the experts rank 0 holds at 8 ranks
+        n_rows = ids.numel()
+        hid = torch.randn(n_rows, HIDDEN, device=dev, generator=g).bfloat16()
+        sorted_ids, expert_ids, post_pad = moe_align_block_size(ids, _TILE_ROWS, e)
+        rows = sorted_ids.numel() // _TILE_ROWS * _TILE_ROWS
+        a1, a1s = _group_quant(hid, 128, sorted_ids, 1, n_rows, post_pad, rows)
+        act = torch.empty((rows, INTER), dtype=torch.bfloat16, device=dev)
+
+        def gemm1():
+            _grouped_gemm(act, a1, w1, a1s, s1.float().contiguous(), None, sorted_ids, expert_ids, post_pad, n_rows,
+                          _cabi.SCALE_BLOCK, fuse_silu=True, scatter=False, mul_weight=False)
+
+        gemm1()
+        a2, a2s = _group_quant(act, 128, None, 1, 0, post_pad, rows)
+        out = torch.empty((n_rows, HIDDEN), dtype=torch.bfloat16, device=dev)
+        wts = torch.rand(n_rows, device=dev, generator=g).bfloat16()
+
+        def gemm2():
+            _grouped_gemm(out, a2, w2, a2s, s2.float().contiguous(), wts, sorted_ids, expert_ids, post_pad, n_rows,
+                          _cabi.SCALE_BLOCK, fuse_silu=False, scatter=True, mul_weight=True)
+
+        fn = gemm1 if name == "moe_gemm1" else gemm2
+        flops = 2.0 * n_rows * (2 * INTER if name == "moe_gemm1" else HIDDEN) * (HIDDEN if name == "moe_gemm1" else INTER)
+        info = {"experts": e, "rows": n_rows, "rows_padded": int(post_pad)}
+    elif name in ("block_mm", "scaled_mm"):
+        m = n = 8192
+        k = 7168
+        a = torch.randn(m, k, device=dev, generator=g).bfloat16()
+        w = torch.randn(n, k, device=dev, generator=g) * 0.02
+        if name == "block_mm":
+            aq, a_s = flag_gems.per_token_group_quant_fp8(a, 128)
+            wq, ws = block_quant_weight_gpu(w)
+            fn = lambda: flag_gems.w8a8_block_fp8_matmul(aq, wq, a_s, ws, [128, 128])  # noqa: E731
+        else:
+            aq, sa = flag_gems.fused.fused_moe._fp8_quantize(a, None, True, None)
+            sw = w.abs().amax(1).clamp_min(1e-10) / 448.0
+            wq = (w / sw[:, None]).clamp(-448, 448).to(FP8)
+            c = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+            fn = lambda: flag_gems.cutlass_scaled_mm(c, aq, wq.t(), sa.view(-1), sw)  # noqa: E731
+        flops, info = 2.0 * m * n * k, {"M": m, "N": n, "K": k}
+    elif name == "group_quant":
+        x = torch.randn(16384, 7168, device=dev, generator=g).bfloat16()
+
+        def fn():
+            flag_gems.per_token_group_quant_fp8(x, 128)
+            flag_gems.act_quant_triton(x, 128)
+
+        flops, info = 0.0, {"M": 16384, "K": 7168, "bytes_per_kernel": 16384 * 7168 * (2 + 1 + 4 / 128)}
+    else:
+        raise SystemExit(f"unknown --workload {name!r}")
+    for _ in range(2):
+        fn()
+    ms = time_events(fn, n_launch)
+    line = {"capture_case": name, "launches_timed": n_launch, "ms_per_call": round(ms, 4), **info,
+            "device_status": _cabi.device_status()}
+    if flops:
+        line["tflops"] = round(flops / ms / 1e9, 1)
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -800,8 +889,13 @@ def main():
                     help="send packed rows by NCCL all-to-all instead of storing them to peers from the pack kernel")
     ap.add_argument("--a2a-combine", action="store_true",
                     help="return expert outputs by NCCL all-to-all instead of the fused peer-memory combine")
+    ap.add_argument("--workload", default="moe_layer",
+                    help="moe_layer (the benchmark) or a single-kernel capture case: moe_gemm1, moe_gemm2, block_mm, "
+                         "scaled_mm, group_quant")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload != "moe_layer":
+        run_capture_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -29,6 +29,8 @@ _SIGS = {
         c_int, [_P, c_int, _P, _P, c_int64, c_int64, c_int, c_int64, c_int64, c_int64, c_int64, c_float, c_int, _P]),
     "fg_per_token_quant_fp8": (
         c_int, [_P, c_int, _P, _P, c_int64, c_int64, c_int64, c_int64, _P, c_int32, c_int32, _P, _P]),
+    "fg_per_token_quant_int8": (
+        c_int, [_P, c_int, _P, _P, c_int64, c_int64, c_int64, c_int64, _P, c_int32, c_int32, _P, _P]),
     "fg_per_tensor_quant_fp8": (
         c_int, [_P, c_int, _P, _P, c_int, _P, c_int64, c_int64, c_int64, c_int64, _P, c_int32, c_int32, _P, _P]),
     "fg_abs_max": (c_int, [_P, c_int, c_int64, c_int64, c_int64, _P, _P, _P]),
@@ -89,6 +91,9 @@ _SIGS = {
     "fg_grouped_topk": (
         c_int, [_P, _P, _P, _P, c_int, c_int64, c_int, c_int64, c_int, c_int, c_int, c_int, ctypes.c_float, c_int,
                 _P, _P]),
+    "fg_moe_grouped_gemm_int8": (
+        c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int64, _P, _P, _P, c_int64, c_int64, c_int, c_int64, c_int64,
+                c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P]),
     "fg_moe_grouped_gemm_fp8": (
         c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int64, _P, _P, _P, c_int64, c_int64, c_int, c_int64, c_int64,
                 c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P]),

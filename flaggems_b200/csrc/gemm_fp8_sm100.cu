@@ -78,6 +78,7 @@ struct GemmParams {
     int64_t bs_stride_n, bs_stride_k, bs_stride_e;  // block mode: strides of Bs
     int64_t sb_stride_e;                            // vector mode: per-expert stride of sb
     int grouped;
+    int int8;  // operands are signed 8-bit integers (accumulators int32)
     const int32_t* sorted_ids;
     const int32_t* expert_ids;
     const int32_t* num_post_pad;
@@ -285,12 +286,21 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int num_m, int num_n) {
 // leaves its fp32 partial tile in its own shared memory and the cluster adds them up through
 // distributed shared memory (no global scratch, no atomics).  For decode-sized M, where there are
 // fewer tiles than SMs and the job is to pull the weights from HBM with every SM.
-template <int BN, bool BLOCK_SCALED, bool FUSE_SILU, bool SMALL_A, bool SPLITK, bool PAIR = false, bool ASTORE = false>
+// INT8: signed 8-bit operands with 32-bit integer accumulators (tcgen05 kind::i8) for the int8 w8a8 expert
+// GEMMs; the epilogue converts the accumulators to fp32 and applies the per-row x per-column scales.
+template <int BN, bool BLOCK_SCALED, bool FUSE_SILU, bool SMALL_A, bool SPLITK, bool PAIR = false, bool ASTORE = false,
+          bool INT8 = false>
 __global__ void __launch_bounds__(Cfg<BN, SMALL_A, PAIR, ASTORE>::THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                 const GemmParams p) {
     using C = Cfg<BN, SMALL_A, PAIR, ASTORE>;
     static_assert(!ASTORE || (BLOCK_SCALED && !SPLITK), "the store warp serves the block-scaled tiles");
+    static_assert(!INT8 || (!BLOCK_SCALED && !SPLITK && !PAIR && !SMALL_A), "int8 serves the plain and grouped tiles");
+    // accumulator word -> fp32
+    auto acc_f = [](uint32_t raw) -> float {
+        if constexpr (INT8) return __int2float_rn((int)raw);
+        else return __uint_as_float(raw);
+    };
     static_assert(!SPLITK || (!FUSE_SILU && !SMALL_A && BN >= 128), "split-K is built for the plain wide tiles");
     static_assert(!PAIR || (!SPLITK && !FUSE_SILU && !SMALL_A), "the CTA pair serves the plain dense tiles");
     static_assert(!FUSE_SILU || BN >= 128, "fused SiLU needs a tile of at least 128 columns");
@@ -548,7 +558,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         // path: the state of the next K block's barriers is therefore probed (non-blocking)
         // before the current block's MMAs are issued, and the blocking wait is only the fallback.
         if (cta_rank == 0) {
-            constexpr uint32_t idesc = umma_idesc_e4m3_f32(PAIR ? 2 * BLOCK_M : BLOCK_M, BN);
+            constexpr uint32_t idesc = INT8 ? umma_idesc_s8_s32(BLOCK_M, BN)
+                                            : umma_idesc_e4m3_f32(PAIR ? 2 * BLOCK_M : BLOCK_M, BN);
             int stage = 0;
             uint32_t phase = 0;
             uint32_t acc_iter = 0;
@@ -567,6 +578,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     const uint32_t accumulate = (decltype(zero_first)::value && k == 0) ? 0u : 1u;
                     if constexpr (PAIR)
                         umma_f8f6f4_2cta(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, accumulate);
+                    else if constexpr (INT8)
+                        umma_i8(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, accumulate);
                     else
                         umma_f8f6f4(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, accumulate);
                 }
@@ -732,8 +745,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                             const int n = min(col + i, p.n_out - 1);
                             const float sg = p.sb_mode == FG_SCALE_VECTOR ? __ldg(sbp + n) : sbp[0];
                             const float su = p.sb_mode == FG_SCALE_VECTOR ? __ldg(sbp + up_off + n) : sbp[0];
-                            const float g = __uint_as_float(raw[i]) * sa * sg;
-                            const float u = __uint_as_float(raw_up[i]) * sa * su;
+                            const float g = acc_f(raw[i]) * sa * sg;
+                            const float u = acc_f(raw_up[i]) * sa * su;
                             v[i] = silu_mul(g, u);
                         }
                     } else if constexpr (SPLITK) {
@@ -750,7 +763,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                         for (int i = 0; i < 32; ++i) {
                             const int n = min(col + i, p.n_out - 1);
                             const float sb = p.sb_mode == FG_SCALE_VECTOR ? __ldg(sbp + n) : sbp[0];
-                            float x = sb * (sa * __uint_as_float(raw[i]));
+                            float x = sb * (sa * acc_f(raw[i]));
                             x *= weight;
                             if (p.bias) {
                                 const float b = load_as_float(p.bias, p.bias_dtype, n + (int64_t)expert * p.bias_stride_e);
@@ -1201,10 +1214,10 @@ bool pair_enabled() {
     return v != 0;
 }
 
-template <int BN, bool BS, bool SILU, bool SMALL_A = false, bool ASTORE = false>
+template <int BN, bool BS, bool SILU, bool SMALL_A = false, bool ASTORE = false, bool INT8 = false>
 int launch_inst(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int max_tiles, cudaStream_t st) {
     using C = Cfg<BN, SMALL_A, false, ASTORE>;
-    auto kernel = gemm_fp8_kernel<BN, BS, SILU, SMALL_A, false, false, ASTORE>;
+    auto kernel = gemm_fp8_kernel<BN, BS, SILU, SMALL_A, false, false, ASTORE, INT8>;
     static bool attr_done[64];
     static std::mutex mu;
     {
@@ -1297,6 +1310,14 @@ int launch_gemm(GemmParams& p, const void* a, int64_t a_rows, int64_t ld_a, cons
     if (pair) return launch_pair(ta, tb, p, (int)pair_tiles, st);
 
     const int t = (int)tiles;
+    if (p.int8) {
+        FG_REQUIRE(!block_scaled && (bn == 256 || bn == 128) && k_slices == 1 && !pair, FG_ERR_UNSUPPORTED,
+                   "int8 operands are built for the grouped expert GEMMs");
+        if (bn == 256) return fuse_silu ? launch_inst<256, false, true, false, false, true>(ta, tb, p, t, st)
+                                        : launch_inst<256, false, false, false, false, true>(ta, tb, p, t, st);
+        return fuse_silu ? launch_inst<128, false, true, false, false, true>(ta, tb, p, t, st)
+                         : launch_inst<128, false, false, false, false, true>(ta, tb, p, t, st);
+    }
     if (k_slices > 1) {
         if (bn == 256) return block_scaled ? launch_splitk<256, true>(ta, tb, p, t, k_slices, st)
                                            : launch_splitk<256, false>(ta, tb, p, t, k_slices, st);
@@ -1440,7 +1461,7 @@ int fg_grouped_gemm_fp8_bias(void* c, const void* a, const void* w, const float*
     return launch_gemm(p, a, p.M, ld_a, w, num_groups, K, false, false, (cudaStream_t)stream);
 }
 
-int fg_moe_grouped_gemm_fp8_peer(void* c, const void* a, const void* w, const float* a_scale, const float* w_scale,
+static int grouped_gemm_common(int int8, void* c, const void* a, const void* w, const float* a_scale, const float* w_scale,
                             const void* topk_weights, int topk_w_dtype, int64_t topk_w_stride,
                             const int32_t* sorted_ids,
                             const int32_t* expert_ids, const int32_t* num_post_pad, int64_t max_rows, int64_t numel,
@@ -1479,13 +1500,40 @@ int fg_moe_grouped_gemm_fp8_peer(void* c, const void* a, const void* w, const fl
         p.sb_mode = scale_mode == FG_SCALE_VECTOR ? FG_SCALE_VECTOR : FG_SCALE_SCALAR;
         p.sb_stride_e = N;
     }
-    p.grouped = 1; p.sorted_ids = sorted_ids; p.expert_ids = expert_ids; p.num_post_pad = num_post_pad;
+    p.grouped = 1; p.int8 = int8; p.sorted_ids = sorted_ids; p.expert_ids = expert_ids; p.num_post_pad = num_post_pad;
     p.block_rows = block_rows; p.numel = numel; p.scatter = scatter; p.mul_weight = mul_weight;
     p.topk_w = topk_weights; p.topk_w_dtype = topk_w_dtype; p.topk_w_stride = topk_w_stride > 0 ? topk_w_stride : 1;
     p.dest = dest; p.dest_stride = dest_stride; p.n_peers = n_peers; p.peer_rows = peer_rows;
     for (int i = 0; i < n_peers; ++i) p.peer_out[i] = peer_out[i];
     if (n_peers > 0 && !c) p.c = peer_out[0];
     return launch_gemm(p, a, p.M, ld_a, w, num_experts, K, block, fuse_silu != 0, (cudaStream_t)stream);
+}
+
+int fg_moe_grouped_gemm_fp8_peer(void* c, const void* a, const void* w, const float* a_scale, const float* w_scale,
+                                 const void* topk_weights, int topk_w_dtype, int64_t topk_w_stride,
+                                 const int32_t* sorted_ids, const int32_t* expert_ids, const int32_t* num_post_pad,
+                                 int64_t max_rows, int64_t numel, int num_experts, int64_t N, int64_t K, int64_t ld_a,
+                                 int64_t ld_c, int block_rows, int scale_mode, int a_scale_per_row, int fuse_silu,
+                                 int scatter, int mul_weight, int out_dtype, const int32_t* dest, int64_t dest_stride,
+                                 void* const* peer_out, int n_peers, int64_t peer_rows, void* stream) {
+    return grouped_gemm_common(0, c, a, w, a_scale, w_scale, topk_weights, topk_w_dtype, topk_w_stride, sorted_ids,
+                               expert_ids, num_post_pad, max_rows, numel, num_experts, N, K, ld_a, ld_c, block_rows,
+                               scale_mode, a_scale_per_row, fuse_silu, scatter, mul_weight, out_dtype, dest, dest_stride,
+                               peer_out, n_peers, peer_rows, stream);
+}
+
+int fg_moe_grouped_gemm_int8(void* c, const void* a, const void* w, const float* a_scale, const float* w_scale,
+                             const void* topk_weights, int topk_w_dtype, int64_t topk_w_stride,
+                             const int32_t* sorted_ids, const int32_t* expert_ids, const int32_t* num_post_pad,
+                             int64_t max_rows, int64_t numel, int num_experts, int64_t N, int64_t K, int64_t ld_a,
+                             int64_t ld_c, int block_rows, int scale_mode, int a_scale_per_row, int fuse_silu,
+                             int scatter, int mul_weight, int out_dtype, void* stream) {
+    FG_REQUIRE(scale_mode == FG_SCALE_SCALAR || scale_mode == FG_SCALE_VECTOR, FG_ERR_UNSUPPORTED,
+               "int8 expert GEMMs take per-tensor or per-token x per-channel scales");
+    return grouped_gemm_common(1, c, a, w, a_scale, w_scale, topk_weights, topk_w_dtype, topk_w_stride, sorted_ids,
+                               expert_ids, num_post_pad, max_rows, numel, num_experts, N, K, ld_a, ld_c, block_rows,
+                               scale_mode, a_scale_per_row, fuse_silu, scatter, mul_weight, out_dtype, nullptr, 0,
+                               nullptr, 0, 0, stream);
 }
 
 }  // extern "C"

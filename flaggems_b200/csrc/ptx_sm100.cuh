@@ -154,6 +154,23 @@ __device__ __forceinline__ void umma_f8f6f4(uint32_t d_tmem, uint64_t a_desc, ui
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Signed 8-bit integer operands, 32-bit integer accumulators (kind::i8), same tile shapes and K = 32.
+__host__ __device__ constexpr uint32_t umma_idesc_s8_s32(int m, int n) {
+    return (2u << 4)                      // D format s32
+           | (1u << 7) | (1u << 10)       // A, B format signed 8-bit
+           | (0u << 15) | (0u << 16)      // A, B K-major
+           | ((uint32_t)(n >> 3) << 17)   // N / 8
+           | ((uint32_t)(m >> 4) << 24);  // M / 16
+}
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // Arrives on the mbarrier once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))

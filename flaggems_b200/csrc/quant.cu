@@ -6,6 +6,7 @@
 //   QM_TOKEN  per-token (MoE)    s = max(max(amax,1e-10)/448, 1/(448*512)), q = x / s
 //   QM_TENSOR_STATIC / _DYNAMIC  one scale for the whole tensor: given (q = x / s) or derived from a
 //             precomputed global amax (s = max(amax,1e-10)/448, q = x * (1/s))
+//   QM_INT8_TOKEN  per-token int8 (MoE) s = max(amax,1e-10) / 127, q = clamp(round_half_even(x / s), -128, 127)
 // The results are bit-exact with IEEE fp32 evaluation of those formulas: products use
 // __fmul_rn, the quotient x / s is a correctly rounded division built from one correctly
 // rounded reciprocal per group and two FMAs per element (Markstein's correction), with a
@@ -15,7 +16,7 @@
 
 namespace {
 
-enum { QM_ACT = 0, QM_GROUP = 1, QM_TOKEN = 2, QM_TENSOR_STATIC = 3, QM_TENSOR_DYNAMIC = 4 };
+enum { QM_ACT = 0, QM_GROUP = 1, QM_TOKEN = 2, QM_TENSOR_STATIC = 3, QM_TENSOR_DYNAMIC = 4, QM_INT8_TOKEN = 5 };
 
 struct QuantArgs {
     const void* x;
@@ -117,9 +118,28 @@ __device__ __forceinline__ float make_scale(float amax, float eps, int pow2) {
         float s = __fdiv_rn(fmaxf(amax, eps), 448.0f);
         if (pow2) s = ceil_pow2_bits(fmaxf(fabsf(s), __uint_as_float(0x2edbe6ffu)));  // floor 1e-10
         return s;
+    } else if constexpr (MODE == QM_INT8_TOKEN) {
+        return __fdiv_rn(fmaxf(amax, __uint_as_float(0x2edbe6ffu)), 127.0f);
     } else {
         float s = __fdiv_rn(fmaxf(amax, __uint_as_float(0x2edbe6ffu)), 448.0f);
         return fmaxf(s, __uint_as_float(0x36924925u));                      // 1/(448*512)
+    }
+}
+
+// Eight quotients -> eight output bytes: e4m3 (round to nearest even, saturating), or int8 (round to
+// nearest even, clamped to [-128, 127]).
+template <int MODE>
+__device__ __forceinline__ uint2 pack_out8(const float (&q)[8]) {
+    if constexpr (MODE == QM_INT8_TOKEN) {
+        uint32_t w[2] = {0u, 0u};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int v = max(-128, min(127, __float2int_rn(q[i])));
+            w[i >> 2] |= (uint32_t)(v & 0xff) << (8 * (i & 3));
+        }
+        return make_uint2(w[0], w[1]);
+    } else {
+        return fg_pack_e4m3x8(q);
     }
 }
 
@@ -459,7 +479,7 @@ __global__ void __launch_bounds__(256) row_quant_kernel(QuantArgs a) {
                 float o[8];
 #pragma unroll
                 for (int i = 0; i < 8; i += 2) apply_divider2<DMODE>(v[j][i], v[j][i + 1], d, o[i], o[i + 1]);
-                *reinterpret_cast<uint2*>(q + (int64_t)iv * 8) = fg_pack_e4m3x8(o);
+                *reinterpret_cast<uint2*>(q + (int64_t)iv * 8) = pack_out8<MODE>(o);
             }
         }
     } else {
@@ -468,7 +488,7 @@ __global__ void __launch_bounds__(256) row_quant_kernel(QuantArgs a) {
             fg_load8(x + (int64_t)iv * 8, t);
 #pragma unroll
             for (int i = 0; i < 8; ++i) o[i] = apply_divider<DMODE>(t[i], d);
-            *reinterpret_cast<uint2*>(q + (int64_t)iv * 8) = fg_pack_e4m3x8(o);
+            *reinterpret_cast<uint2*>(q + (int64_t)iv * 8) = pack_out8<MODE>(o);
         }
     }
 }
@@ -711,6 +731,31 @@ int fg_per_tensor_quant_fp8(const void* x, int x_dtype, void* q, const float* sc
         default: fg_set_error("unsupported input dtype code %d", x_dtype); return FG_ERR_INVALID_ARGUMENT;
     }
 #undef FG_ROW_LAUNCH
+    fg_count_launch(1);
+    FG_LAUNCH_CHECK();
+    return FG_OK;
+}
+
+int fg_per_token_quant_int8(const void* x, int x_dtype, void* q, float* s, int64_t M, int64_t K, int64_t ld_x,
+                            int64_t ld_q, const int32_t* row_index, int32_t index_div, int32_t index_limit,
+                            const int32_t* n_rows_dev, void* stream) {
+    QuantArgs a{};
+    a.x = x; a.q = (uint8_t*)q; a.s = s; a.rows = M; a.K = K; a.group = (int)K;
+    a.ld_x = ld_x; a.ld_q = ld_q; a.s_row_stride = 1; a.s_col_stride = 1;
+    a.eps = 1e-10f; a.pow2 = 0;
+    a.row_index = row_index; a.index_div = index_div; a.index_limit = index_limit; a.n_rows_dev = n_rows_dev;
+    FG_REQUIRE(K < (1ll << 31) && M < (1ll << 31), FG_ERR_UNSUPPORTED, "size too large");
+    FG_REQUIRE(row_index == nullptr || index_div > 0, FG_ERR_INVALID_ARGUMENT, "index_div must be positive");
+    if (K == 0 || M == 0) return FG_OK;
+    int rc = check_common(a, x_dtype);
+    if (rc != FG_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (x_dtype) {
+        case FG_DTYPE_BF16: row_quant_kernel<__nv_bfloat16, QM_INT8_TOKEN><<<(unsigned)M, 256, 0, st>>>(a); break;
+        case FG_DTYPE_F16: row_quant_kernel<__half, QM_INT8_TOKEN><<<(unsigned)M, 256, 0, st>>>(a); break;
+        case FG_DTYPE_F32: row_quant_kernel<float, QM_INT8_TOKEN><<<(unsigned)M, 256, 0, st>>>(a); break;
+        default: fg_set_error("unsupported input dtype code %d", x_dtype); return FG_ERR_INVALID_ARGUMENT;
+    }
     fg_count_launch(1);
     FG_LAUNCH_CHECK();
     return FG_OK;

@@ -8,8 +8,9 @@ Mirrors the FP8 path of src/flag_gems/fused/fused_moe.py of the reference:
 (tcgen05); rows are first gathered into expert-sorted padded order while they are
 quantised, so the GEMMs read their A operand with plain TMA boxes.
 
-Only the FP8 w8a8 modes are implemented (block 128x128, per-token x per-channel);
-the int8 / int4 / MX / bias / non-SiLU options of the reference signature raise
+Implemented: the FP8 w8a8 modes (block 128x128, per-token x per-channel, per-tensor) and int8
+w8a8 with per-token x per-channel scales (tcgen05 kind::i8, int32 accumulation); the weight-only
+(w8a16 / w4a16), MX, bias and non-SiLU options of the reference signature raise
 NotImplementedError.
 """
 import logging
@@ -75,6 +76,35 @@ def _per_token_quant(x, row_index=None, index_div=1, index_limit=0, n_rows_dev=N
             )
         )
     return q, s
+
+
+def _per_token_quant_int8(x, row_index=None, index_div=1, index_limit=0, n_rows_dev=None, out_rows=None):
+    """Dynamic per-row INT8 quantisation (reference: fused_moe.py:732-739), optionally gathering rows
+    through ``row_index``."""
+    k = x.shape[-1]
+    x2 = x.reshape(-1, k)
+    rows = x2.shape[0] if out_rows is None else out_rows
+    q = torch.empty((rows, k), dtype=torch.int8, device=x.device)
+    s = torch.empty((rows, 1), dtype=torch.float32, device=x.device)
+    if rows and k:
+        _cabi.check(
+            _cabi.lib().fg_per_token_quant_int8(
+                _cabi.ptr(x2), _cabi.DTYPE_CODE[x.dtype], _cabi.ptr(q), _cabi.ptr(s), rows, k,
+                x2.stride(0), k, _cabi.ptr(row_index), index_div, index_limit, _cabi.ptr(n_rows_dev),
+                _cabi.stream_ptr(x.device),
+            )
+        )
+    return q, s
+
+
+def _int8_quantize(A, A_scale, per_act_token, block_shape=None):
+    """INT8 quantisation of MoE activations (reference: fused_moe.py:700-747); the per-token form only."""
+    _cabi.require_cuda(A)
+    if block_shape is not None or not per_act_token:
+        raise NotImplementedError("int8 activations: only per-token quantisation is implemented")
+    with _cabi.device_guard(A):
+        q, s = _per_token_quant_int8(A)
+    return q.reshape(A.shape), s.reshape(A.shape[:-1] + (1,))
 
 
 def _group_quant(x, group, row_index=None, index_div=1, index_limit=0, n_rows_dev=None, out_rows=None):
@@ -156,8 +186,9 @@ def _grouped_gemm(c, a, w, a_scale, w_scale, topk_weights, sorted_ids, expert_id
                   scale_mode, fuse_silu, scatter, mul_weight, block_rows=_TILE_ROWS, a_scale_per_row=None):
     e, n, k = w.shape
     c = c.view(-1, c.shape[-1])
+    entry = _cabi.lib().fg_moe_grouped_gemm_int8 if w.dtype == torch.int8 else _cabi.lib().fg_moe_grouped_gemm_fp8
     _cabi.check(
-        _cabi.lib().fg_moe_grouped_gemm_fp8(
+        entry(
             _cabi.ptr(c), _cabi.ptr(a), _cabi.ptr(w), _cabi.ptr(a_scale), _cabi.ptr(w_scale),
             _cabi.ptr(topk_weights), _cabi.DTYPE_CODE.get(topk_weights.dtype, -1) if topk_weights is not None else 0,
             1,
@@ -200,10 +231,14 @@ def fused_experts_impl(
     logger.debug("GEMS FUSED MOE")
     assert activation == "silu", f"Only 'silu' activation is supported, got {activation}"
     MoEActivation.from_str(activation)
-    if use_int8_w8a8 or use_int8_w8a16 or use_int4_w4a16 or ocp_mx_scheme is not None:
-        raise NotImplementedError("only the FP8 w8a8 modes of fused_experts_impl are implemented")
-    if not use_fp8_w8a8:
-        raise NotImplementedError("unquantised (bf16/fp16) expert weights are not implemented; pass use_fp8_w8a8=True")
+    if use_int8_w8a16 or use_int4_w4a16 or ocp_mx_scheme is not None:
+        raise NotImplementedError("weight-only (w8a16 / w4a16) and OCP MX expert formats are not implemented")
+    if use_int8_w8a8 and (use_fp8_w8a8 or not per_channel_quant or block_shape is not None):
+        raise NotImplementedError("int8 w8a8 is implemented for per-token x per-channel scales "
+                                  "(use_int8_w8a8=True, per_channel_quant=True)")
+    if not use_fp8_w8a8 and not use_int8_w8a8:
+        raise NotImplementedError("unquantised (bf16/fp16) expert weights are not implemented; pass use_fp8_w8a8=True "
+                                  "or use_int8_w8a8=True")
     if w1_zp is not None or w2_zp is not None or w1_bias is not None or w2_bias is not None:
         raise NotImplementedError("zero points and expert biases are not implemented")
     if apply_router_weight_on_input:
@@ -221,8 +256,9 @@ def fused_experts_impl(
     assert w1.is_contiguous() and w2.is_contiguous(), "expert weights must be contiguous"
     assert topk_weights.stride(1) == 1
     _cabi.require_cuda(hidden_states, w1, w2, topk_weights, topk_ids, w1_scale, w2_scale, expert_map)
-    if w1.dtype != torch.float8_e4m3fn or w2.dtype != torch.float8_e4m3fn:
-        raise NotImplementedError("expert weights must be float8_e4m3fn")
+    w_dtype = torch.int8 if use_int8_w8a8 else torch.float8_e4m3fn
+    if w1.dtype != w_dtype or w2.dtype != w_dtype:
+        raise NotImplementedError(f"expert weights must be {w_dtype}")
 
     num_tokens, hidden = hidden_states.shape
     e, n, _ = w1.shape
@@ -276,7 +312,8 @@ def fused_experts_impl(
             if scale_mode == _cabi.SCALE_BLOCK:
                 a1, a1s = _group_quant(h, 128, sorted_ids, top_k, numel, post_pad, rows)
             elif scale_mode == _cabi.SCALE_VECTOR:
-                a1, a1s = _per_token_quant(h, sorted_ids, top_k, numel, post_pad, rows)
+                quant_rows = _per_token_quant_int8 if use_int8_w8a8 else _per_token_quant
+                a1, a1s = quant_rows(h, sorted_ids, top_k, numel, post_pad, rows)
             else:
                 a1, a1s = _per_tensor_quant(h, a1_scale, sorted_ids, top_k, numel, post_pad, rows)
             act = torch.empty((rows, inter), dtype=dtype, device=h.device)
@@ -285,7 +322,7 @@ def fused_experts_impl(
             if scale_mode == _cabi.SCALE_BLOCK:
                 a2, a2s = _group_quant(act, 128, None, 1, 0, post_pad, rows)
             elif scale_mode == _cabi.SCALE_VECTOR:
-                a2, a2s = _per_token_quant(act, None, 1, 0, post_pad, rows)
+                a2, a2s = quant_rows(act, None, 1, 0, post_pad, rows)
             else:
                 a2, a2s = _per_tensor_quant(act, a2_scale, None, 1, 0, post_pad, rows, amax_rows_dev=post_pad)
             routed = torch.empty((t, top_k, k_out), dtype=dtype, device=h.device)

@@ -84,6 +84,13 @@ int fg_per_token_quant_fp8(const void* x, int x_dtype, void* q, float* s, int64_
                            int64_t ld_x, int64_t ld_q, const int32_t* row_index, int32_t index_div,
                            int32_t index_limit, const int32_t* n_rows_dev, void* stream);
 
+/* Per-token branch of _int8_quantize: src/flag_gems/fused/fused_moe.py:732-739.
+ * s[m] = max(rowamax, 1e-10) / 127, q = clamp(round_half_even(x / s), -128, 127) as int8 bytes.
+ * Row gather options as above. */
+int fg_per_token_quant_int8(const void* x, int x_dtype, void* q, float* s, int64_t M, int64_t K,
+                            int64_t ld_x, int64_t ld_q, const int32_t* row_index, int32_t index_div,
+                            int32_t index_limit, const int32_t* n_rows_dev, void* stream);
+
 /* Per-tensor branches of _fp8_quantize: src/flag_gems/fused/fused_moe.py:686-698.
  * dynamic == 0 (static scale given): q = x / scale_or_amax[0].
  * dynamic != 0: scale_or_amax[0] holds max|x| over the tensor (fg_abs_max); s = max(amax,1e-10)/448,
@@ -362,6 +369,17 @@ int fg_moe_grouped_gemm_fp8(void* c, const void* a, const void* w, const float* 
                             int num_experts, int64_t N, int64_t K, int64_t ld_a, int64_t ld_c,
                             int block_rows, int scale_mode, int a_scale_per_row, int fuse_silu,
                             int scatter, int mul_weight, int out_dtype, void* stream);
+
+/* The same grouped GEMM on signed 8-bit operands with 32-bit integer accumulation (tcgen05 kind::i8):
+ * the int8 w8a8 branches of fused_moe_kernel, src/flag_gems/fused/fused_moe.py:1198-1347, :1466-1479.
+ * a, w: int8; scale_mode FG_SCALE_SCALAR or FG_SCALE_VECTOR; everything else as above. */
+int fg_moe_grouped_gemm_int8(void* c, const void* a, const void* w, const float* a_scale,
+                             const float* w_scale, const void* topk_weights, int topk_w_dtype,
+                             int64_t topk_w_stride, const int32_t* sorted_ids, const int32_t* expert_ids,
+                             const int32_t* num_post_pad, int64_t max_rows, int64_t numel,
+                             int num_experts, int64_t N, int64_t K, int64_t ld_a, int64_t ld_c,
+                             int block_rows, int scale_mode, int a_scale_per_row, int fuse_silu,
+                             int scatter, int mul_weight, int out_dtype, void* stream);
 
 /* ---- aten _scaled_grouped_mm ------------------------------------------------ */
 

@@ -24,6 +24,7 @@ from .quant import (  # noqa: F401
     per_token_group_quant_fp8,
     per_token_quant_fp8,
     per_tensor_quant_fp8,
+    per_token_quant_int8,
     quantize_weight_per_channel,
     quantize_weight_block,
 )
@@ -37,6 +38,7 @@ from .moe import (  # noqa: F401
     expert_rows_per_channel_fp8,
     fused_moe_block_fp8,
     fused_moe_per_channel_fp8,
+    fused_moe_per_channel_int8,
     fused_moe_per_tensor_fp8,
     dense_block_fp8_mlp,
 )

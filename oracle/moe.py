@@ -4,7 +4,7 @@ from typing import Optional, Tuple
 import torch
 
 from .gemm import block_scaled_mm
-from .quant import per_tensor_quant_fp8, per_token_group_quant_fp8, per_token_quant_fp8
+from .quant import per_tensor_quant_fp8, per_token_group_quant_fp8, per_token_quant_fp8, per_token_quant_int8
 
 
 def moe_align_block_size(
@@ -208,6 +208,44 @@ def fused_moe_per_channel_fp8(
         act = _silu_mul_f32(z, fuse_silu, hidden.dtype)
         aq, asc = per_token_quant_fp8(act)
         r = torch.mm(aq.float(), w2[e].float().t()) * asc * s2
+        r = (r * topk_weights[tok, slot].float().unsqueeze(1)).to(hidden.dtype)
+        out[tok, slot] = r.float()
+    return moe_sum(out).to(hidden.dtype)
+
+
+def fused_moe_per_channel_int8(
+    hidden: torch.Tensor,
+    w1: torch.Tensor,
+    w2: torch.Tensor,
+    w1_scale: torch.Tensor,
+    w2_scale: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+) -> torch.Tensor:
+    """INT8 w8a8 MoE layer with per-token activation and per-output-channel weight scales.
+
+    Restated from the kernel path of src/flag_gems/fused/fused_moe.py: per-token int8 quantisation of
+    the rows (:732-739), exact integer accumulation (``tl.dot`` of int8 operands into int32, :1318-1331),
+    ``acc.to(float32) * a_scale * b_scale`` (:1337-1341, :1478-1479), fused SiLU in fp32 (:1344),
+    per-token re-quantisation, router weight in fp32 then cast (:1485-1493), fp32 top-k sum.  The
+    reference's test of this mode, tests/test_fused_experts_impl.py:765-835, compares with a per-row
+    fake-quantised golden; tests/test_oracle_golden.py holds that golden's output as a fixture.
+    The integer products are accumulated in float64 here, which is exact for these sizes.
+    w1_scale: [E, 2I] (or [E, 2I, 1]), w2_scale: [E, H] (or [E, H, 1])."""
+    t, h = hidden.shape
+    topk = topk_ids.shape[1]
+    hq, hs = per_token_quant_int8(hidden)
+    out = torch.zeros(t, topk, w2.shape[1], dtype=torch.float32)
+    for e in range(w1.shape[0]):
+        tok, slot = torch.nonzero(topk_ids == e, as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        s1 = w1_scale[e].float().reshape(1, -1)
+        s2 = w2_scale[e].float().reshape(1, -1)
+        z = torch.mm(hq[tok].double(), w1[e].double().t()).float() * hs[tok] * s1
+        act = _silu_mul_f32(z, True, hidden.dtype)
+        aq, asc = per_token_quant_int8(act)
+        r = torch.mm(aq.double(), w2[e].double().t()).float() * asc * s2
         r = (r * topk_weights[tok, slot].float().unsqueeze(1)).to(hidden.dtype)
         out[tok, slot] = r.float()
     return moe_sum(out).to(hidden.dtype)

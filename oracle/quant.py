@@ -144,3 +144,15 @@ def quantize_weight_block(w: torch.Tensor, block: int = 128) -> Tuple[torch.Tens
     s = amax / FP8_MAX
     q = (tiles / s[:, None, :, None]).clamp(FP8_MIN, FP8_MAX).reshape(nb * block, kb * block)
     return q[:n, :k].contiguous().to(FP8), s
+
+
+def per_token_quant_int8(x: torch.Tensor):
+    """Per-row INT8 quantisation: s = max(rowamax, 1e-10) / 127, q = clamp(round(x / s), -128, 127).
+
+    Follows the per-token branch of ``_int8_quantize``, src/flag_gems/fused/fused_moe.py:732-739
+    (``torch.round`` rounds halves to even)."""
+    flat = x.reshape(-1, x.shape[-1])
+    amax = flat.abs().amax(dim=-1, keepdim=True).clamp(min=1e-10).to(torch.float32)
+    scale = amax / 127.0
+    q = (flat.float() / scale).round().clamp(-128, 127).to(torch.int8)
+    return q.reshape(x.shape), scale.reshape(x.shape[:-1] + (1,))

@@ -231,6 +231,26 @@ def main():
                               topk_weights=tw, topk_ids=ti, out=out))
     save("fused_moe_fake_quant_fp8", cases)
 
+    # ---- the same golden in its int8 mode, on the input recipe of test_fused_moe_int8 (:765-835):
+    # weights quantised per output channel to int8 (scale amax / 127), dequantised to bf16 for the golden.
+    g3 = torch.Generator().manual_seed(0)
+    cases = []
+    for (t, e, h, i, topk) in [(4, 8, 128, 256, 2), (32, 4, 128, 128, 4)]:
+        hidden = torch.randn(t, h, generator=g3).bfloat16()
+        quant = []
+        for w in (torch.randn(e, 2 * i, h, generator=g3) * (1.0 / h ** 0.5),
+                  torch.randn(e, h, i, generator=g3) * (1.0 / i ** 0.5)):
+            sc = w.abs().amax(dim=-1, keepdim=True).clamp(min=1e-10) / 127.0
+            q = (w / sc).round().clamp(-128, 127).to(torch.int8)
+            quant.append((q, sc.squeeze(-1), (q.float() * sc).bfloat16()))
+        gating = torch.randn(t, e, generator=g3)
+        tw, ti = torch.topk(torch.softmax(gating, -1), topk)
+        tw = (tw / tw.sum(-1, keepdim=True)).bfloat16()
+        out = fm["torch_fused_moe_quantized_reference"](hidden, quant[0][2], quant[1][2], tw, ti, quant_mode="int8")
+        cases.append(dict(hidden=hidden, w1=quant[0][0], w2=quant[1][0], w1_scale=quant[0][1], w2_scale=quant[1][1],
+                          topk_weights=tw, topk_ids=ti, out=out))
+    save("fused_moe_fake_quant_int8", cases)
+
 
 if __name__ == "__main__":
     if not os.path.isdir(REF):

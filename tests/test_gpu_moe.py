@@ -172,3 +172,56 @@ def test_fused_moe_expert_map_and_inplace():
 
 def test_no_device_errors_recorded():
     assert _cabi.device_status() == 0
+
+
+# ---- int8 w8a8 ------------------------------------------------------------------------------
+def _int8_channel_weights(e, n, k, g, scale):
+    w = torch.randn(e, n, k, generator=g) * scale
+    s = w.abs().amax(dim=-1, keepdim=True).clamp(min=1e-10) / 127.0
+    return (w / s).round().clamp(-128, 127).to(torch.int8), s.squeeze(-1)
+
+
+def test_per_token_quant_int8_bit_exact():
+    from flaggems_b200.fused.fused_moe import _int8_quantize
+
+    g = torch.Generator().manual_seed(40)
+    for (m, k, dt) in [(1, 128, torch.bfloat16), (77, 4096, torch.bfloat16), (33, 1000, torch.float16),
+                       (5, 7168, torch.float32)]:
+        x = (torch.randn(m, k, generator=g) * 3).to(dt)
+        x[0, :8] = torch.tensor([0.5, 1.5, 2.5, -0.5, -1.5, 3.5, 1e-3, 0.0]).to(dt)  # halves round to even
+        q, s = _int8_quantize(x.cuda(), None, True)
+        qr, sr = oracle.per_token_quant_int8(x)
+        assert q.dtype == torch.int8 and s.shape == (m, 1)
+        assert torch.equal(s.cpu(), sr) and torch.equal(q.cpu(), qr)
+    q, s = _int8_quantize(torch.zeros(3, 256, dtype=torch.bfloat16, device="cuda"), None, True)
+    assert int(q.abs().max()) == 0 and float(s.max()) == pytest.approx(1e-10 / 127.0)
+
+
+@pytest.mark.parametrize("t,h,i,e,topk", [(1, 128, 256, 8, 2), (16, 256, 512, 8, 2), (32, 128, 256, 8, 4),
+                                          (333, 1024, 512, 8, 2), (512, 4096, 1024, 8, 2)])
+def test_fused_moe_int8_per_channel(t, h, i, e, topk):
+    """Shapes of FUSED_MOE_QUANT_CONFIGS (tests/test_fused_experts_impl.py:64-80) and two larger ones."""
+    g = torch.Generator().manual_seed(41)
+    hidden = torch.randn(t, h, generator=g).bfloat16()
+    w1, s1 = _int8_channel_weights(e, 2 * i, h, g, 1.0 / h ** 0.5)
+    w2, s2 = _int8_channel_weights(e, h, i, g, 1.0 / i ** 0.5)
+    tw, ti = _router(t, e, topk, g)
+    out = flag_gems.fused_experts_impl(hidden.cuda(), w1.cuda(), w2.cuda(), tw.cuda(), ti.cuda(), use_int8_w8a8=True,
+                                       per_channel_quant=True, w1_scale=s1.cuda(), w2_scale=s2.cuda())
+    ref = oracle.fused_moe_per_channel_int8(hidden, w1, w2, s1, s2, tw, ti)
+    assert out.shape == hidden.shape and out.dtype == hidden.dtype
+    _close(out, ref)
+
+
+def test_fused_moe_int8_golden(golden_dir):
+    """The reference's int8 golden at its own tolerance (tests/test_fused_experts_impl.py:831-835)."""
+    for c in torch.load(os.path.join(golden_dir, "fused_moe_fake_quant_int8.pt")):
+        out = flag_gems.fused_experts_impl(c["hidden"].cuda(), c["w1"].cuda(), c["w2"].cuda(), c["topk_weights"].cuda(),
+                                           c["topk_ids"].cuda(), use_int8_w8a8=True, per_channel_quant=True,
+                                           w1_scale=c["w1_scale"].cuda(), w2_scale=c["w2_scale"].cuda())
+        ref = c["out"].float()
+        torch.testing.assert_close(out.cpu().float(), ref, rtol=2e-1, atol=max(5e-2, float(ref.abs().max()) * 2e-2))
+    with pytest.raises(NotImplementedError):
+        flag_gems.fused_experts_impl(c["hidden"].cuda(), c["w1"].cuda(), c["w2"].cuda(), c["topk_weights"].cuda(),
+                                     c["topk_ids"].cuda(), use_int8_w8a8=True, w1_scale=c["w1_scale"].cuda(),
+                                     w2_scale=c["w2_scale"].cuda())

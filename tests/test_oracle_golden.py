@@ -180,3 +180,28 @@ def test_fused_moe_per_tensor_and_per_channel_against_fake_quant_golden(golden_d
         # tensor where the golden uses one per row: ~6 %
         bound = 0.025 if c["granularity"] == "per_channel" else 0.10
         assert err.mean().item() <= bound * ref.abs().mean().item(), (c["granularity"], err.mean().item())
+
+
+def test_fused_moe_int8_against_fake_quant_golden(golden_dir):
+    """The reference's int8 golden (tests/test_fused_experts_impl.py:478-528 with quant_mode="int8") on the
+    recipe of test_fused_moe_int8 pins the int8 w8a8 oracle at that test's tolerance (:831-835: rtol 0.2,
+    atol max(0.05, 0.02 * max|ref|)) and, in aggregate, to 2 %: both quantise every row on its own (the golden
+    multiplies by bf16-rounded dequantised weights, the oracle by int8 weights and fp32 scales)."""
+    for c in load(golden_dir, "fused_moe_fake_quant_int8"):
+        out = oracle.fused_moe_per_channel_int8(c["hidden"], c["w1"], c["w2"], c["w1_scale"], c["w2_scale"],
+                                                c["topk_weights"], c["topk_ids"])
+        ref = c["out"].float()
+        torch.testing.assert_close(out.float(), ref, rtol=2e-1, atol=max(5e-2, ref.abs().max().item() * 2e-2))
+        err = (out.float() - ref).abs()
+        assert err.mean().item() <= 0.02 * ref.abs().mean().item(), err.mean().item() / ref.abs().mean().item()
+
+
+def test_per_token_quant_int8_oracle():
+    x = torch.tensor([[0.0, 1.0, -2.0, 127.0], [0.5, 1.5, 2.5, -3.5]]).bfloat16()
+    q, s = oracle.per_token_quant_int8(x)
+    assert torch.equal(s, torch.tensor([[1.0], [3.5 / 127.0]]))
+    assert q[0].tolist() == [0, 1, -2, 127]
+    assert q[1].tolist() == [18, 54, 91, -127]  # 0.5 * 127 / 3.5 = 18.14..., 2.5 -> 90.71 -> 91
+    z = torch.zeros(1, 8).bfloat16()
+    q, s = oracle.per_token_quant_int8(z)
+    assert float(s) == pytest.approx(1e-10 / 127.0) and int(q.abs().max()) == 0
