@@ -811,9 +811,13 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     if constexpr (FUSE_SILU) return (uint32_t)((c < 2 ? 0 : BN / 2) + 64 * half + 32 * (c & 1));
                     else return (uint32_t)(128 * half + 32 * c);
                 };
-                // Scales of four K blocks at a time, fetched one group ahead (a group lasts ~3000
-                // cycles, so the loads are long complete when their turn comes): 16-byte loads where
-                // the K-block scales of a row are contiguous and aligned, four scalar loads otherwise.
+                // Wide tiles issued by two warps (DUAL): scales of four K blocks at a time, fetched one
+                // group ahead (a group lasts ~3000 cycles, so the loads are long complete when their
+                // turn comes): 16-byte loads where the K-block scales of a row are contiguous and
+                // aligned, four scalar loads otherwise.  Everywhere else (narrow tiles, split-K
+                // slices of a handful of K blocks) one K block ahead: measured 3-4 us faster there
+                // at decode sizes than the groups.
+                constexpr bool SCALE_GROUPS = DUAL;
                 const bool as_vec = p.as_stride_k == 1 && ((reinterpret_cast<uintptr_t>(as_row) & 15) == 0);
                 const bool bs_vec = p.bs_stride_k == 1 && ((reinterpret_cast<uintptr_t>(bs0) & 15) == 0) &&
                                     ((reinterpret_cast<uintptr_t>(bs1) & 15) == 0);
@@ -830,26 +834,45 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     }
                     return make_float4(v[0], v[1], v[2], v[3]);
                 };
-                float4 a_nx = load4(as_row, p.as_stride_k, as_vec, kb_begin, false);
-                float4 b0_nx = load4(bs0, p.bs_stride_k, bs_vec, kb_begin, true);
-                float4 b1_nx = FUSE_SILU ? load4(bs1, p.bs_stride_k, bs_vec, kb_begin, true) : b0_nx;
+                float4 a_nx = make_float4(0.f, 0.f, 0.f, 0.f), b0_nx = a_nx, b1_nx = a_nx;
+                float as_next = 0.f, b0_next = 0.f, b1_next = 0.f;
+                if constexpr (SCALE_GROUPS) {
+                    a_nx = load4(as_row, p.as_stride_k, as_vec, kb_begin, false);
+                    b0_nx = load4(bs0, p.bs_stride_k, bs_vec, kb_begin, true);
+                    b1_nx = FUSE_SILU ? load4(bs1, p.bs_stride_k, bs_vec, kb_begin, true) : b0_nx;
+                } else {
+                    as_next = as_row[(int64_t)kb_begin * p.as_stride_k];
+                    b0_next = __ldg(bs0 + (int64_t)kb_begin * p.bs_stride_k);
+                    if constexpr (FUSE_SILU) b1_next = __ldg(bs1 + (int64_t)kb_begin * p.bs_stride_k);
+                }
                 float g0[4] = {0.f, 0.f, 0.f, 0.f}, g1[4] = {0.f, 0.f, 0.f, 0.f};  // products of the current group
                 for (int kb = kb_begin; kb < kb_end; ++kb) {
                     const int in_group = (kb - kb_begin) & 3;
-                    if (in_group == 0) {
-                        g0[0] = a_nx.x * b0_nx.x; g0[1] = a_nx.y * b0_nx.y; g0[2] = a_nx.z * b0_nx.z; g0[3] = a_nx.w * b0_nx.w;
-                        if constexpr (FUSE_SILU) {
-                            g1[0] = a_nx.x * b1_nx.x; g1[1] = a_nx.y * b1_nx.y; g1[2] = a_nx.z * b1_nx.z; g1[3] = a_nx.w * b1_nx.w;
+                    float sc0f, sc1f;
+                    if constexpr (!SCALE_GROUPS) {
+                        sc0f = as_next * b0_next;
+                        sc1f = FUSE_SILU ? as_next * b1_next : sc0f;
+                        if (kb + 1 < kb_end) {  // next block's scales travel while this block is folded in
+                            as_next = as_row[(int64_t)(kb + 1) * p.as_stride_k];
+                            b0_next = __ldg(bs0 + (int64_t)(kb + 1) * p.bs_stride_k);
+                            if constexpr (FUSE_SILU) b1_next = __ldg(bs1 + (int64_t)(kb + 1) * p.bs_stride_k);
                         }
-                        if (kb + 4 < kb_end) {
-                            a_nx = load4(as_row, p.as_stride_k, as_vec, kb + 4, false);
-                            b0_nx = load4(bs0, p.bs_stride_k, bs_vec, kb + 4, true);
-                            if constexpr (FUSE_SILU) b1_nx = load4(bs1, p.bs_stride_k, bs_vec, kb + 4, true);
+                    } else {
+                        if (in_group == 0) {
+                            g0[0] = a_nx.x * b0_nx.x; g0[1] = a_nx.y * b0_nx.y; g0[2] = a_nx.z * b0_nx.z; g0[3] = a_nx.w * b0_nx.w;
+                            if constexpr (FUSE_SILU) {
+                                g1[0] = a_nx.x * b1_nx.x; g1[1] = a_nx.y * b1_nx.y; g1[2] = a_nx.z * b1_nx.z; g1[3] = a_nx.w * b1_nx.w;
+                            }
+                            if (kb + 4 < kb_end) {
+                                a_nx = load4(as_row, p.as_stride_k, as_vec, kb + 4, false);
+                                b0_nx = load4(bs0, p.bs_stride_k, bs_vec, kb + 4, true);
+                                if constexpr (FUSE_SILU) b1_nx = load4(bs1, p.bs_stride_k, bs_vec, kb + 4, true);
+                            }
                         }
+                        sc0f = in_group == 0 ? g0[0] : in_group == 1 ? g0[1] : in_group == 2 ? g0[2] : g0[3];
+                        sc1f = !FUSE_SILU ? sc0f
+                               : in_group == 0 ? g1[0] : in_group == 1 ? g1[1] : in_group == 2 ? g1[2] : g1[3];
                     }
-                    const float sc0f = in_group == 0 ? g0[0] : in_group == 1 ? g0[1] : in_group == 2 ? g0[2] : g0[3];
-                    const float sc1f = !FUSE_SILU ? sc0f
-                                       : in_group == 0 ? g1[0] : in_group == 1 ? g1[1] : in_group == 2 ? g1[2] : g1[3];
                     const uint64_t sc0 = pack_f32x2(sc0f, sc0f), sc1 = pack_f32x2(sc1f, sc1f);
                     const uint32_t buf = acc_iter & 1u;
                     FG_PROF_T0(tw);
@@ -1325,8 +1348,10 @@ int launch_gemm(GemmParams& p, const void* a, int64_t a_rows, int64_t ld_a, cons
                             : launch_splitk<128, false>(ta, tb, p, t, k_slices, st);
     }
     if (bn == 256) {
-        // 16-bit outputs with 16-byte aligned rows: the tile is parked and written out by the store warp
-        const bool park = block_scaled && esz == 2 && p.c_vec_ok && p.n_out % 8 == 0;
+        // 16-bit outputs with 16-byte aligned rows: the tile is parked and written out by the store warp.
+        // Not for a single row of tiles (M <= 128), where the job is to stream the weights and the
+        // fourth ring stage is worth more than the store warp (measured 36 vs 42 us at N = 24576).
+        const bool park = m_tiles > 1 && block_scaled && esz == 2 && p.c_vec_ok && p.n_out % 8 == 0;
         if (park) return fuse_silu ? launch_inst<256, true, true, false, true>(ta, tb, p, t, st)
                                    : launch_inst<256, true, false, false, true>(ta, tb, p, t, st);
         if (block_scaled) return fuse_silu ? launch_inst<256, true, true>(ta, tb, p, t, st)
