@@ -257,6 +257,7 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(const T* __restrict__ in, 
 }
 
 // Copies rows of FP8 bytes and their fp32 scale rows through an index (pure data movement).
+// One warp per destination row, four 16-byte loads per lane in flight before the first store.
 __global__ void __launch_bounds__(256) gather_rows_kernel(const uint8_t* __restrict__ src_q,
                                                           const float* __restrict__ src_s, uint8_t* __restrict__ dst_q,
                                                           float* __restrict__ dst_s, int64_t rows, int64_t K,
@@ -270,6 +271,7 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint8_t* __restr
     }
     const int warps_per_block = blockDim.x / 32;
     const int lane = threadIdx.x & 31;
+    const int nvec = (int)(K / 16);
     for (int64_t r = (int64_t)blockIdx.x * warps_per_block + (threadIdx.x >> 5); r < rows;
          r += (int64_t)gridDim.x * warps_per_block) {
         const int32_t idx = row_index[r];
@@ -277,8 +279,22 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint8_t* __restr
         const int64_t src = real ? idx / index_div : 0;
         const uint4* sq = reinterpret_cast<const uint4*>(src_q + src * src_q_stride);
         uint4* dq = reinterpret_cast<uint4*>(dst_q + r * K);
-        for (int64_t v = lane; v < K / 16; v += 32) dq[v] = real ? sq[v] : make_uint4(0u, 0u, 0u, 0u);
-        for (int64_t v = lane; v < s_cols; v += 32) dst_s[r * s_cols + v] = real ? src_s[src * src_s_stride + v] : 1.0f;
+        const float sv = (real && lane < s_cols) ? src_s[src * src_s_stride + lane] : 1.0f;
+        for (int v0 = lane; v0 < nvec; v0 += 128) {
+            uint4 t[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int v = v0 + 32 * u;
+                t[u] = (real && v < nvec) ? __ldg(sq + v) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int v = v0 + 32 * u;
+                if (v < nvec) __stcs(dq + v, t[u]);
+            }
+        }
+        if (lane < s_cols) dst_s[r * s_cols + lane] = sv;
+        for (int64_t v = lane + 32; v < s_cols; v += 32) dst_s[r * s_cols + v] = real ? src_s[src * src_s_stride + v] : 1.0f;
     }
 }
 

@@ -192,8 +192,24 @@ int fg_moe_routed_block_fp8_local(void* y, const void* hidden, int hidden_dtype,
     rc = fg_moe_align_block_size(topk_ids, ids_are_i64, n_in, num_experts, TILE_ROWS, nullptr, 0, ws.sorted_ids,
                                  ws.max_pad, ws.expert_ids, ws.n_blocks, ws.post_pad, stream);
     if (rc != FG_OK) return rc;
-    rc = fg_per_token_group_quant_fp8_gather(hidden, hidden_dtype, ws.a1, ws.a1s, ws.rows, H, 128, H, H, ws.sorted_ids,
-                                             topk, (int32_t)n_in, ws.post_pad, stream);
+    // Every token is quantised once (as the reference does before its gathering GEMM) and its FP8 row
+    // and scales are then copied to each of its top-k places in expert order: quantising while gathering
+    // would read and quantise every token top-k times.  The token buffer borrows the room of GEMM1's
+    // output, which is first written after the copy has finished.  Bits are the same either way.
+    const int64_t s_cols = H / 128;
+    const int64_t tok_q_bytes = align_up(T * H, 256);
+    if (topk > 1 && tok_q_bytes + 4 * T * s_cols <= ws.rows * I * 2) {
+        uint8_t* tok_q = ws.act;
+        float* tok_s = reinterpret_cast<float*>(ws.act + tok_q_bytes);
+        rc = fg_per_token_group_quant_fp8(hidden, hidden_dtype, tok_q, tok_s, T, H, 128, H, H, s_cols, 1, 1e-10f, 0,
+                                          stream);
+        if (rc != FG_OK) return rc;
+        rc = fg_gather_rows_fp8(tok_q, tok_s, ws.a1, ws.a1s, ws.rows, H, s_cols, H, s_cols, ws.sorted_ids, topk,
+                                (int32_t)n_in, ws.post_pad, stream);
+    } else {
+        rc = fg_per_token_group_quant_fp8_gather(hidden, hidden_dtype, ws.a1, ws.a1s, ws.rows, H, 128, H, H,
+                                                 ws.sorted_ids, topk, (int32_t)n_in, ws.post_pad, stream);
+    }
     if (rc != FG_OK) return rc;
     return run_gemms(y, ws, n_in, w1, w2, s1, s2, num_experts, H, I, topk_w, topk_w_dtype, 1, hidden_dtype, nullptr, 0,
                      nullptr, 0, 0, stream);
