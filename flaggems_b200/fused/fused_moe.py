@@ -126,6 +126,21 @@ def _group_quant(x, group, row_index=None, index_div=1, index_limit=0, n_rows_de
     return q, s
 
 
+def _group_quant_once_then_gather(x, group, row_index, top_k, numel, n_rows_dev, out_rows):
+    """The reference's order (fused_moe.py:2016-2023 quantises A once, the kernel gathers rows by
+    ``sorted_token_ids // top_k``): every token is quantised once and its FP8 row and scales are
+    copied to each of its places in expert order.  Same bits as quantising while gathering."""
+    k = x.shape[-1]
+    tq, ts = _group_quant(x, group)
+    q = torch.empty((out_rows, k), dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty((out_rows, k // group), dtype=torch.float32, device=x.device)
+    if out_rows and k:
+        _cabi.check(_cabi.lib().fg_gather_rows_fp8(
+            _cabi.ptr(tq), _cabi.ptr(ts), _cabi.ptr(q), _cabi.ptr(s), out_rows, k, k // group, k, k // group,
+            _cabi.ptr(row_index), top_k, numel, _cabi.ptr(n_rows_dev), _cabi.stream_ptr(x.device)))
+    return q, s
+
+
 def _per_tensor_quant(x, scale=None, row_index=None, index_div=1, index_limit=0, n_rows_dev=None, out_rows=None,
                       amax_rows_dev=None):
     """Per-tensor FP8 quantisation (reference: fused_moe.py:686-698): with a given ``scale``
@@ -310,7 +325,10 @@ def fused_experts_impl(
             rows = sorted_ids.numel() // _TILE_ROWS * _TILE_ROWS
 
             if scale_mode == _cabi.SCALE_BLOCK:
-                a1, a1s = _group_quant(h, 128, sorted_ids, top_k, numel, post_pad, rows)
+                if top_k > 1:
+                    a1, a1s = _group_quant_once_then_gather(h, 128, sorted_ids, top_k, numel, post_pad, rows)
+                else:
+                    a1, a1s = _group_quant(h, 128, sorted_ids, top_k, numel, post_pad, rows)
             elif scale_mode == _cabi.SCALE_VECTOR:
                 quant_rows = _per_token_quant_int8 if use_int8_w8a8 else _per_token_quant
                 a1, a1s = quant_rows(h, sorted_ids, top_k, numel, post_pad, rows)
