@@ -81,6 +81,15 @@ __device__ __forceinline__ void fg_load8(const T* p, float (&f)[8]) {
     }
 }
 
+// Eight 16-bit elements already in registers (one 16-byte load) as floats.
+template <typename T>
+__device__ __forceinline__ void fg_unpack8(const uint4& raw, float (&f)[8]) {
+    static_assert(sizeof(T) == 2, "16-bit element types only");
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = fg_to_float(e[i]);
+}
+
 template <typename T>
 __device__ __forceinline__ void fg_store8(T* p, const float (&f)[8]) {
     if constexpr (sizeof(T) == 2) {

@@ -229,7 +229,11 @@ __global__ void __launch_bounds__(256) silu_and_mul_kernel(const T* __restrict__
     }
 }
 
-template <typename T>
+// Sum over the top-k slots of every token in slot order, in fp32 (the order and precision of the
+// reference's moe_sum_kernel), plus an optional addend row, rounded once.  TOPK > 0: all the
+// slots' 16-byte loads are issued before the first add (HBM-bound: 1 GB per step of the
+// DeepSeek-V3 layer); TOPK == 0: any top-k, one load at a time.
+template <typename T, int TOPK>
 __global__ void __launch_bounds__(256) moe_sum_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t M,
                                                       int topk, int64_t K, const int32_t* __restrict__ row_index,
                                                       const T* __restrict__ addend) {
@@ -238,19 +242,52 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(const T* __restrict__ in, 
     for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = v / vec_per_row, c = (v % vec_per_row) * 8;
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int k = 0; k < topk; ++k) {
-            float t[8];
-            const int64_t src = row_index ? (int64_t)row_index[r * topk + k] : r * topk + k;
-            if (src < 0) continue;
-            fg_load8(in + src * K + c, t);
+        if constexpr (TOPK > 0) {
+            uint4 raw[TOPK];
+            bool have[TOPK];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] += t[i];
-        }
-        if (addend) {
-            float t[8];
-            fg_load8(addend + r * K + c, t);
+            for (int k = 0; k < TOPK; ++k) {
+                const int64_t src = row_index ? (int64_t)row_index[r * TOPK + k] : r * TOPK + k;
+                have[k] = src >= 0;
+                if constexpr (sizeof(T) == 2) {
+                    raw[k] = have[k] ? __ldcs(reinterpret_cast<const uint4*>(in + src * K + c)) : make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+            uint4 add_raw = make_uint4(0u, 0u, 0u, 0u);
+            if constexpr (sizeof(T) == 2) {
+                if (addend) add_raw = *reinterpret_cast<const uint4*>(addend + r * K + c);
+            }
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] += t[i];
+            for (int k = 0; k < TOPK; ++k) {
+                if (!have[k]) continue;
+                float t[8];
+                if constexpr (sizeof(T) == 2) fg_unpack8<T>(raw[k], t);
+                else fg_load8(in + (row_index ? (int64_t)row_index[r * TOPK + k] : r * TOPK + k) * K + c, t);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] += t[i];
+            }
+            if (addend) {
+                float t[8];
+                if constexpr (sizeof(T) == 2) fg_unpack8<T>(add_raw, t);
+                else fg_load8(addend + r * K + c, t);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] += t[i];
+            }
+        } else {
+            for (int k = 0; k < topk; ++k) {
+                float t[8];
+                const int64_t src = row_index ? (int64_t)row_index[r * topk + k] : r * topk + k;
+                if (src < 0) continue;
+                fg_load8(in + src * K + c, t);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] += t[i];
+            }
+            if (addend) {
+                float t[8];
+                fg_load8(addend + r * K + c, t);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] += t[i];
+            }
         }
         fg_store8(out + r * K + c, acc);
     }
@@ -457,19 +494,23 @@ int fg_moe_sum_indexed(const void* in, void* out, int64_t M, int topk, int64_t K
                FG_ERR_UNSUPPORTED, "moe_sum needs K %% 8 == 0 and 16-byte aligned buffers");
     cudaStream_t st = (cudaStream_t)stream;
     const unsigned grid = grid_for(M * (K / 8), 256);
+    auto launch = [&](auto tag) {
+        using T = decltype(tag);
+        const T* i = (const T*)in;
+        T* o = (T*)out;
+        const T* a = (const T*)addend;
+        switch (topk) {
+            case 2: moe_sum_kernel<T, 2><<<grid, 256, 0, st>>>(i, o, M, topk, K, row_index, a); break;
+            case 4: moe_sum_kernel<T, 4><<<grid, 256, 0, st>>>(i, o, M, topk, K, row_index, a); break;
+            case 6: moe_sum_kernel<T, 6><<<grid, 256, 0, st>>>(i, o, M, topk, K, row_index, a); break;
+            case 8: moe_sum_kernel<T, 8><<<grid, 256, 0, st>>>(i, o, M, topk, K, row_index, a); break;
+            default: moe_sum_kernel<T, 0><<<grid, 256, 0, st>>>(i, o, M, topk, K, row_index, a); break;
+        }
+    };
     switch (dtype) {
-        case FG_DTYPE_BF16:
-            moe_sum_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, M, topk, K, row_index,
-                                                 (const __nv_bfloat16*)addend);
-            break;
-        case FG_DTYPE_F16:
-            moe_sum_kernel<<<grid, 256, 0, st>>>((const __half*)in, (__half*)out, M, topk, K, row_index,
-                                                 (const __half*)addend);
-            break;
-        case FG_DTYPE_F32:
-            moe_sum_kernel<<<grid, 256, 0, st>>>((const float*)in, (float*)out, M, topk, K, row_index,
-                                                 (const float*)addend);
-            break;
+        case FG_DTYPE_BF16: launch(__nv_bfloat16()); break;
+        case FG_DTYPE_F16: launch(__half()); break;
+        case FG_DTYPE_F32: launch(float()); break;
         default: fg_set_error("unsupported dtype code %d", dtype); return FG_ERR_INVALID_ARGUMENT;
     }
     fg_count_launch(1);
