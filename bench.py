@@ -305,7 +305,32 @@ def dense_extras(peaks):
                                "tflops": round(2.0 * t4 * 2 * 3 * h4 * i4 / ms / 1e9, 1),
                                "config": "T=4096, hidden 4096, intermediate 14336, 8 experts, top-2, "
                                          "per-token x per-channel FP8 (BASELINE configs[3]), fused_experts_impl"}
+    # the same layer with int8 w8a8 experts (per-token x per-channel), tcgen05 kind::i8
+    s1i, s2i = s1 * (448.0 / 127.0), s2 * (448.0 / 127.0)
+    w1i = (w1.float() * (127.0 / 448.0)).round().clamp(-127, 127).to(torch.int8)
+    w2i = (w2.float() * (127.0 / 448.0)).round().clamp(-127, 127).to(torch.int8)
     del w1, w2
+    fn = lambda: flag_gems.fused_experts_impl(hid, w1i, w2i, tw4, ti4, use_int8_w8a8=True, per_channel_quant=True,
+                                              w1_scale=s1i, w2_scale=s2i)
+    for _ in range(3):
+        fn()
+    ms = time_events(fn, 10)
+    out["moe_mixtral_8x7b_int8"] = {"tokens_per_s": round(t4 / ms * 1e3, 1), "ms": round(ms, 3),
+                                    "tops": round(2.0 * t4 * 2 * 3 * h4 * i4 / ms / 1e9, 1)}
+    del w1i, w2i
+
+    # aten _scaled_grouped_mm (rows of A grouped by device-side offsets, one B per group), expert-GEMM shaped
+    gg, mg, ng, kg = 32, 8192, 4096, 7168
+    ag = torch.randn(mg, kg, device="cuda", generator=g).to(FP8)
+    bg = torch.randn(gg, ng, kg, device="cuda", generator=g).to(FP8)
+    sag = torch.rand(mg, device="cuda") + 0.5
+    sbg = torch.rand(gg, ng, device="cuda") + 0.5
+    offs = (torch.arange(1, gg + 1, device="cuda", dtype=torch.int32) * (mg // gg))
+    fn = lambda: flag_gems.scaled_grouped_mm(ag, bg.transpose(-1, -2), sag, sbg, offs)
+    ms = time_graph(fn, iters=10)
+    out["scaled_grouped_mm_tflops"] = {f"G{gg}_M{mg}_N{ng}_K{kg}": {"tflops": round(2.0 * mg * ng * kg / ms / 1e9, 1),
+                                                                    "us": round(ms * 1e3, 1)}}
+    del ag, bg
 
     # The vendor library's FP8 GEMM under the same conditions, for scale (cuBLASLt via torch._scaled_mm).
     try:

@@ -407,6 +407,41 @@ __global__ void __launch_bounds__(256, 5) group_quant16_kernel(QuantArgs a) {
     }
 }
 
+// Expert-parallel dispatch, second step: every token was quantised once into a staging row (FP8
+// payload, then its scales); this kernel copies the staged row of route slot order[r] to output row
+// r (a local packed buffer, or this rank's region of the destination rank's receive buffer) and
+// writes the row's trailer.  One warp per row, four 16-byte loads in flight per lane.
+__global__ void __launch_bounds__(256) pack_copy_kernel(QuantArgs a, const uint8_t* __restrict__ staged) {
+    const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int nvec = (int)(a.K / 16);
+    const int s_cols = (int)(a.K / a.group);
+    for (int64_t r = (int64_t)blockIdx.x * warps + (threadIdx.x >> 5); r < a.rows; r += (int64_t)gridDim.x * warps) {
+        const int64_t src = source_row(a, r);
+        uint8_t* dst = packed_row_ptr(a, r);
+        if (src < 0 || !dst) continue;
+        const uint8_t* srow = staged + src * a.ld_q;
+        const uint4* sq = reinterpret_cast<const uint4*>(srow);
+        uint4* dq = reinterpret_cast<uint4*>(dst);
+        for (int v0 = lane; v0 < nvec; v0 += 128) {
+            uint4 t[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int v = v0 + 32 * u;
+                t[u] = v < nvec ? sq[v] : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int v = v0 + 32 * u;
+                if (v < nvec) dq[v] = t[u];
+            }
+        }
+        const float* ss = reinterpret_cast<const float*>(srow + a.K);
+        float* ds = reinterpret_cast<float*>(dst + a.K);
+        for (int v = lane; v < s_cols; v += 32) ds[v] = ss[v];
+        if (lane == 0) write_row_meta(a, r);
+    }
+}
+
 // ---- any group size (multiple of 8), one CTA per group: per-token rows, block_size = K ...
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256) row_quant_kernel(QuantArgs a) {
@@ -679,6 +714,26 @@ int fg_ep_pack_rows_fp8_peer(const void* x, int x_dtype, int64_t T, int64_t K, i
     }
     int rc = check_common(a, x_dtype);
     if (rc != FG_OK) return rc;
+    if (send_counts && packed && topk > 1) {
+        // `packed` as a staging area of T rows: every token is quantised once (not once per route slot)
+        // and its staged row is copied to each of its destinations.
+        FG_REQUIRE((uintptr_t)packed % 16 == 0, FG_ERR_UNSUPPORTED, "the staging rows must be 16-byte aligned");
+        QuantArgs b{};
+        b.x = x; b.q = (uint8_t*)packed; b.s = reinterpret_cast<float*>((uint8_t*)packed + K);
+        b.rows = T; b.K = K; b.group = 128; b.ld_x = ld_x; b.ld_q = row_bytes;
+        b.s_row_stride = row_bytes / 4; b.s_col_stride = 1; b.eps = 1e-10f; b.pow2 = 0;
+        rc = check_common(b, x_dtype);
+        if (rc != FG_OK) return rc;
+        rc = launch_quant<QM_GROUP>(x_dtype, b, (cudaStream_t)stream);
+        if (rc != FG_OK) return rc;
+        int64_t blocks = fg_cdiv(a.rows, 8);
+        const int64_t cap = (int64_t)fg_num_sms() * 8;
+        if (blocks > cap) blocks = cap;
+        pack_copy_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(a, (const uint8_t*)packed);
+        fg_count_launch(1);
+        FG_LAUNCH_CHECK();
+        return FG_OK;
+    }
     return launch_quant<QM_GROUP>(x_dtype, a, (cudaStream_t)stream);
 }
 

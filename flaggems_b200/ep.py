@@ -181,10 +181,15 @@ class CudaMoEOps:
         device; rows beyond a region are dropped by the kernel and reported in the status word)."""
         t, topk = topk_ids.shape
         dev = hidden.device
+        # staging rows: every token is quantised once there, then copied to its top-k destinations
+        stage = getattr(self, "_stage", None)
+        if stage is None or stage.shape[0] < t or stage.device != dev:
+            stage = torch.empty((max(t, 1), self.row_bytes), dtype=torch.uint8, device=dev)
+            self._stage = stage
         _cabi.check(_cabi.lib().fg_ep_pack_rows_fp8_peer(
             _cabi.ptr(hidden), _cabi.DTYPE_CODE[hidden.dtype], t, self.hidden, hidden.stride(0),
             _cabi.ptr(topk_ids), 1 if topk_ids.dtype == torch.int64 else 0, _cabi.ptr(topk_w),
-            _cabi.DTYPE_CODE[topk_w.dtype], topk, self.num_local_experts, rank, _cabi.ptr(order), None,
+            _cabi.DTYPE_CODE[topk_w.dtype], topk, self.num_local_experts, rank, _cabi.ptr(order), _cabi.ptr(stage),
             self.row_bytes, None, _cabi.ptr(send_counts), peer_rows, world, region_rows, _cabi.stream_ptr(dev)))
 
     def experts_from_buffer(self, rows_ptr, world, region_rows, counts_matrix, rank, out_dtype, device, peer_out,

@@ -231,7 +231,10 @@ int fg_ep_pack_rows_fp8(const void* x, int x_dtype, int64_t T, int64_t K, int64_
  * [home_rank * region_rows, (home_rank + 1) * region_rows): the k-th row for rank d lands at row
  * home_rank * region_rows + k there, so a rank needs nobody else's counts to send.  A row that
  * would fall outside its region is not stored and the device status word is set (code 2).
- * send_counts == NULL: as above (rows go to `packed`). */
+ * send_counts == NULL: as above (rows go to `packed`).  With send_counts, a non-NULL `packed`
+ * (at least T rows of row_bytes, 16-byte aligned) is a staging area: every token is quantised
+ * once into it and its staged row is copied to each of its top-k destinations, instead of being
+ * quantised once per route slot; same bytes either way. */
 int fg_ep_pack_rows_fp8_peer(const void* x, int x_dtype, int64_t T, int64_t K, int64_t ld_x,
                              const void* topk_ids, int ids_are_i64, const void* topk_w,
                              int topk_w_dtype, int topk, int experts_per_rank, int home_rank,
