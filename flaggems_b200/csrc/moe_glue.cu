@@ -71,6 +71,7 @@ __global__ void __launch_bounds__(ALIGN_THREADS, 1) moe_align_kernel(AlignArgs a
     int32_t* base = cta_total + E;                // [E] first output slot for this CTA's first row of e
     int32_t* pad_lo = base + E;                   // [E] first padding slot of e
     int32_t* pad_hi = pad_lo + E;                 // [E] one past the last slot of e
+    int32_t* blk_lo = pad_hi + E;                 // [E] first slot of e
     __shared__ int32_t scan_tmp[ALIGN_WARPS];
     __shared__ int32_t total_padded_s;
 
@@ -161,20 +162,24 @@ __global__ void __launch_bounds__(ALIGN_THREADS, 1) moe_align_kernel(AlignArgs a
         base[e0] = offset + before;
         pad_lo[e0] = offset + total;
         pad_hi[e0] = offset + padded;
+        blk_lo[e0] = offset;
         if (a.expert_counts && rank == 0) a.expert_counts[e0] = total;
     }
     __syncthreads();
     const int32_t total_padded = total_padded_s;
 
-    // Phase 2d: expert id of every block, padding slots, tail.  Work is spread over the ranks.
-    if (e0 < E && (e0 % n_ranks) == rank) {
-        int32_t id = e0;
-        if (a.expert_map) id = a.expert_map[e0 < a.expert_map_len ? e0 : a.expert_map_len - 1];
-        for (int32_t b = offset / bs; b < (offset + padded) / bs; ++b) a.expert_ids[b] = id;
-    }
+    // Phase 2d: expert id of every block, padding slots, tail.  Work is spread over the ranks; one warp
+    // per expert, so that few experts with many blocks each (the expert-parallel routing pass: one
+    // bucket per rank, block size 1) do not serialise on one thread.  expert_ids may be absent.
     const int32_t numel32 = (int32_t)a.numel;
-    for (int e = warp + rank * ALIGN_WARPS; e < E; e += ALIGN_WARPS * n_ranks)
+    for (int e = warp + rank * ALIGN_WARPS; e < E; e += ALIGN_WARPS * n_ranks) {
         for (int32_t p = pad_lo[e] + lane; p < pad_hi[e]; p += 32) a.sorted_ids[p] = numel32;
+        if (a.expert_ids) {
+            int32_t id = e;
+            if (a.expert_map) id = a.expert_map[e < a.expert_map_len ? e : a.expert_map_len - 1];
+            for (int32_t b = blk_lo[e] / bs + lane; b < pad_hi[e] / bs; b += 32) a.expert_ids[b] = id;
+        }
+    }
     {
         const int64_t gtid = (int64_t)rank * ALIGN_THREADS + threadIdx.x;
         const int64_t gthreads = (int64_t)n_ranks * ALIGN_THREADS;
@@ -183,7 +188,8 @@ __global__ void __launch_bounds__(ALIGN_THREADS, 1) moe_align_kernel(AlignArgs a
         // i.e. its last entry, as Python indexing of the reference does.
         int32_t tail_id = -1;
         if (a.expert_map && a.expert_map_len > 0) tail_id = a.expert_map[a.expert_map_len - 1];
-        for (int64_t b = total_padded / bs + gtid; b < a.n_blocks; b += gthreads) a.expert_ids[b] = tail_id;
+        if (a.expert_ids)
+            for (int64_t b = total_padded / bs + gtid; b < a.n_blocks; b += gthreads) a.expert_ids[b] = tail_id;
         if (gtid == 0) a.num_post_pad[0] = total_padded;
     }
 
@@ -399,10 +405,9 @@ int fg_moe_align_block_size_regions(const void* topk_ids, int ids_are_i64, int64
     FG_REQUIRE(max_pad >= need_pad, FG_ERR_INVALID_ARGUMENT,
                "sorted_ids holds %lld entries, needs at least min(numel*block_size, numel + E*(block_size-1)) = %lld",
                (long long)max_pad, (long long)need_pad);
-    FG_REQUIRE(n_blocks >= need_pad / block_size, FG_ERR_INVALID_ARGUMENT,
+    FG_REQUIRE(expert_ids == nullptr || n_blocks >= need_pad / block_size, FG_ERR_INVALID_ARGUMENT,
                "expert_ids holds %lld entries, needs %lld", (long long)n_blocks, (long long)(need_pad / block_size));
-    FG_REQUIRE(sorted_ids && expert_ids && num_post_pad && (topk_ids || numel == 0), FG_ERR_INVALID_ARGUMENT,
-               "null pointer");
+    FG_REQUIRE(sorted_ids && num_post_pad && (topk_ids || numel == 0), FG_ERR_INVALID_ARGUMENT, "null pointer");
     FG_REQUIRE(expert_map == nullptr || expert_map_len >= num_experts, FG_ERR_INVALID_ARGUMENT,
                "expert_map has %d entries for %d experts", expert_map_len, num_experts);
 
@@ -412,7 +417,7 @@ int fg_moe_align_block_size_regions(const void* topk_ids, int ids_are_i64, int64
     // One CTA handles 32 warps x 128 slots comfortably; grow the cluster with numel up to 8.
     int ranks = 1;
     while (ranks < 8 && (int64_t)ranks * ALIGN_THREADS * 4 < numel) ranks *= 2;
-    const size_t smem = (size_t)(ALIGN_WARPS + 4) * num_experts * sizeof(int32_t);
+    const size_t smem = (size_t)(ALIGN_WARPS + 5) * num_experts * sizeof(int32_t);
 
     auto kernel = ids_are_i64 ? moe_align_kernel<int64_t> : moe_align_kernel<int32_t>;
     // Opt in to large dynamic shared memory once per device, kernel and size (a per-device

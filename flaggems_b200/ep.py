@@ -167,11 +167,10 @@ class CudaMoEOps:
         numel = topk_ids.numel()
         dev = topk_ids.device
         order = torch.empty(numel, dtype=torch.int32, device=dev)
-        blocks = torch.empty(numel + 1, dtype=torch.int32, device=dev)
         meta = torch.empty(world + 1, dtype=torch.int32, device=dev)
         _cabi.check(_cabi.lib().fg_moe_align_block_size_ex(
             _cabi.ptr(topk_ids), 1 if topk_ids.dtype == torch.int64 else 0, numel, world, 1, None, 0,
-            _cabi.ptr(order), numel, _cabi.ptr(blocks), numel + 1, _cabi.ptr(meta), 1, self.num_local_experts,
+            _cabi.ptr(order), numel, None, 0, _cabi.ptr(meta), 1, self.num_local_experts,
             meta.data_ptr() + 4, None, _cabi.stream_ptr(dev)))
         return order, meta[1:]
 

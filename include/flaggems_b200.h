@@ -134,7 +134,8 @@ int fg_moe_align_block_size(const void* topk_ids, int ids_are_i64, int64_t numel
  * the bucket of a slot is id / id_div (id_div = experts per rank turns expert ids into
  * destination ranks), expert_counts (nullable) receives the unpadded rows per bucket, and
  * numel_dev (nullable) is a device-side slot count: numel is then only the capacity (and the
- * padding value), so a step needs no host round trip to learn how many rows arrived. */
+ * padding value), so a step needs no host round trip to learn how many rows arrived.
+ * expert_ids may be NULL here when the caller only needs the order and the counts. */
 int fg_moe_align_block_size_ex(const void* topk_ids, int ids_are_i64, int64_t numel, int num_experts,
                                int block_size, const int32_t* expert_map, int expert_map_len,
                                int32_t* sorted_ids, int64_t max_pad, int32_t* expert_ids,
