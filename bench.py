@@ -2,14 +2,14 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
 
-Prints ONE JSON line.  The default workload is the DeepSeek-V3-shaped fused MoE layer of
-BASELINE.json configs[4] (hidden 7168, expert intermediate 2048, 256 routed experts, top-8,
+Prints ONE JSON line.  The default workload is the DeepSeek-V3-shaped fused MoE layer, the fifth
+configuration of the benchmark definition (hidden 7168, expert intermediate 2048, 256 routed experts, top-8,
 one shared expert, T=8192 tokens in total, FP8 weights with 128x128 block scales): the one
 configuration of the metric that is defined at 1, 2, 4 and 8 GPUs, so every N reports the same
 quantity (tokens/s of the whole layer, strong scaling: the 8192 tokens and 256 experts are
-split over the ranks, dispatch/combine by all-to-all).  At N=1 the same line also carries the
+split over the ranks, dispatch/combine over peer memory).  At N=1 the same line also carries the
 other half of the metric under "extra": FP8 scaled-mm TFLOP/s on the Llama-3-8B shapes
-(configs[1]) and block-scaled shapes (configs[2]), and act_quant GB/s.
+(second configuration) and block-scaled shapes (third), and act_quant GB/s.
 
 A step = one forward pass of the layer over the step's tokens.  "value" is measured with the
 inputs resident in HBM; "e2e" goes through the public layer call with pinned HOST buffers,
@@ -281,7 +281,7 @@ def dense_extras(peaks):
     out["router_us"]["grouped_topk_T8192_E256_g8_tg4_top8_sigmoid"] = round(ms * 1e3, 1)
     out["router_us"]["grouped_topk_gbs"] = round((router_bytes - TOKENS * TOPK * 4) / ms / 1e6, 1)
 
-    # BASELINE configs[3]: Mixtral-8x7B-shaped layer, per-token x per-channel FP8, through fused_experts_impl
+    # fourth benchmark configuration: Mixtral-8x7B-shaped layer, per-token x per-channel FP8, through fused_experts_impl
     t4, h4, i4, e4 = 4096, 4096, 14336, 8
     w1 = torch.empty(e4, 2 * i4, h4, dtype=FP8, device="cuda")
     w2 = torch.empty(e4, h4, i4, dtype=FP8, device="cuda")
@@ -304,7 +304,7 @@ def dense_extras(peaks):
     out["moe_mixtral_8x7b"] = {"tokens_per_s": round(t4 / ms * 1e3, 1), "ms": round(ms, 3),
                                "tflops": round(2.0 * t4 * 2 * 3 * h4 * i4 / ms / 1e9, 1),
                                "config": "T=4096, hidden 4096, intermediate 14336, 8 experts, top-2, "
-                                         "per-token x per-channel FP8 (BASELINE configs[3]), fused_experts_impl"}
+                                         "per-token x per-channel FP8 (configs[3]), fused_experts_impl"}
     # the same layer with int8 w8a8 experts (per-token x per-channel), tcgen05 kind::i8
     s1i, s2i = s1 * (448.0 / 127.0), s2 * (448.0 / 127.0)
     w1i = (w1.float() * (127.0 / 448.0)).round().clamp(-127, 127).to(torch.int8)
@@ -453,7 +453,7 @@ def run_reference(args):
 
 
 def workload_config(n):
-    return {"workload": "deepseek_v3_moe_layer (BASELINE configs[4])", "hidden": HIDDEN, "intermediate": INTER,
+    return {"workload": "deepseek_v3_moe_layer (configs[4])", "hidden": HIDDEN, "intermediate": INTER,
             "experts": EXPERTS, "top_k": TOPK, "shared_experts": 1, "tokens_global": TOKENS,
             "weight_format": "fp8_e4m3 128x128 block scales", "activation_format": "fp8_e4m3 1x128 group scales",
             "router": "zipf(1.1) gumbel top-8, seed 0", "parallelism": f"ep{n}",

@@ -40,7 +40,7 @@ def test_act_quant_reference_shapes(m, n, block, fmt):
 
 
 def test_act_quant_baseline_config_and_per_token_block():
-    """BASELINE configs[0]: A bf16 [256, 4096], group 128; and block_size = K (per-token scales)."""
+    """First benchmark configuration: A bf16 [256, 4096], group 128; and block_size = K (per-token scales)."""
     torch.manual_seed(0)
     x = torch.randn(256, 4096).bfloat16()
     for block in (128, 4096, 512, 1024):
@@ -137,7 +137,7 @@ def test_group_quant_golden_and_tiny(golden_dir):
 
 
 def test_group_quant_full_size_scale_roundtrip():
-    """BASELINE configs[2] size (M=16384, K=7168): properties that need no CPU oracle pass:
+    """Third benchmark configuration's size (M=16384, K=7168): properties that need no CPU oracle pass:
     every scale equals amax/448 of its group computed independently on the device, and
     dequantised values stay within half an FP8 step of the input."""
     torch.manual_seed(3)
