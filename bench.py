@@ -317,7 +317,16 @@ def dense_extras(peaks):
     ms = time_events(fn, 10)
     out["moe_mixtral_8x7b_int8"] = {"tokens_per_s": round(t4 / ms * 1e3, 1), "ms": round(ms, 3),
                                     "tops": round(2.0 * t4 * 2 * 3 * h4 * i4 / ms / 1e9, 1)}
+    # and unquantised bf16 experts (the default path of fused_experts_impl), tcgen05 kind::f16
+    w1b, w2b = w1i.bfloat16() * 0.01, w2i.bfloat16() * 0.01
     del w1i, w2i
+    fn = lambda: flag_gems.fused_experts_impl(hid, w1b, w2b, tw4, ti4)
+    for _ in range(3):
+        fn()
+    ms = time_events(fn, 10)
+    out["moe_mixtral_8x7b_bf16"] = {"tokens_per_s": round(t4 / ms * 1e3, 1), "ms": round(ms, 3),
+                                    "tflops": round(2.0 * t4 * 2 * 3 * h4 * i4 / ms / 1e9, 1)}
+    del w1b, w2b
 
     # aten _scaled_grouped_mm (rows of A grouped by device-side offsets, one B per group), expert-GEMM shaped
     gg, mg, ng, kg = 32, 8192, 4096, 7168

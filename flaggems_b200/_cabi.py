@@ -91,6 +91,9 @@ _SIGS = {
     "fg_grouped_topk": (
         c_int, [_P, _P, _P, _P, c_int, c_int64, c_int, c_int64, c_int, c_int, c_int, c_int, ctypes.c_float, c_int,
                 _P, _P]),
+    "fg_moe_grouped_gemm_16bit": (
+        c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int64, _P, _P, _P, c_int64, c_int64, c_int, c_int64, c_int64,
+                c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P]),
     "fg_moe_grouped_gemm_int8": (
         c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int64, _P, _P, _P, c_int64, c_int64, c_int, c_int64, c_int64,
                 c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P]),

@@ -78,7 +78,7 @@ struct GemmParams {
     int64_t bs_stride_n, bs_stride_k, bs_stride_e;  // block mode: strides of Bs
     int64_t sb_stride_e;                            // vector mode: per-expert stride of sb
     int grouped;
-    int int8;  // operands are signed 8-bit integers (accumulators int32)
+    int int8;  // operand kind: 0 e4m3, 1 signed 8-bit integers (accumulators int32), 2 bf16, 3 f16 (K then counts bytes)
     const int32_t* sorted_ids;
     const int32_t* expert_ids;
     const int32_t* num_post_pad;
@@ -286,16 +286,20 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int num_m, int num_n) {
 // leaves its fp32 partial tile in its own shared memory and the cluster adds them up through
 // distributed shared memory (no global scratch, no atomics).  For decode-sized M, where there are
 // fewer tiles than SMs and the job is to pull the weights from HBM with every SM.
-// INT8: signed 8-bit operands with 32-bit integer accumulators (tcgen05 kind::i8) for the int8 w8a8 expert
-// GEMMs; the epilogue converts the accumulators to fp32 and applies the per-row x per-column scales.
+// OPK (operand kind): 0 = e4m3 (kind::f8f6f4); 1 = signed 8-bit integers with 32-bit integer accumulators
+// (kind::i8) for the int8 w8a8 expert GEMMs (the epilogue converts the accumulators to fp32 and applies
+// the per-row x per-column scales); 2 / 3 = bf16 / f16 (kind::f16) for the unquantised and
+// weight-only-quantised expert GEMMs.  The main loop is written in bytes (a K block is 128 bytes of a
+// K-major row, an MMA consumes 32 of them), so a 16-bit product of K elements runs as 2K bytes.
 template <int BN, bool BLOCK_SCALED, bool FUSE_SILU, bool SMALL_A, bool SPLITK, bool PAIR = false, bool ASTORE = false,
-          bool INT8 = false>
+          int OPK = 0>
 __global__ void __launch_bounds__(Cfg<BN, SMALL_A, PAIR, ASTORE>::THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                 const GemmParams p) {
     using C = Cfg<BN, SMALL_A, PAIR, ASTORE>;
     static_assert(!ASTORE || (BLOCK_SCALED && !SPLITK), "the store warp serves the block-scaled tiles");
-    static_assert(!INT8 || (!BLOCK_SCALED && !SPLITK && !PAIR && !SMALL_A), "int8 serves the plain and grouped tiles");
+    constexpr bool INT8 = OPK == 1;
+    static_assert(OPK == 0 || (!BLOCK_SCALED && !SPLITK && !PAIR && !SMALL_A), "int8 and 16-bit operands serve the plain and grouped tiles");
     // accumulator word -> fp32
     auto acc_f = [](uint32_t raw) -> float {
         if constexpr (INT8) return __int2float_rn((int)raw);
@@ -558,8 +562,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         // path: the state of the next K block's barriers is therefore probed (non-blocking)
         // before the current block's MMAs are issued, and the blocking wait is only the fallback.
         if (cta_rank == 0) {
-            constexpr uint32_t idesc = INT8 ? umma_idesc_s8_s32(BLOCK_M, BN)
-                                            : umma_idesc_e4m3_f32(PAIR ? 2 * BLOCK_M : BLOCK_M, BN);
+            constexpr uint32_t idesc = OPK == 1 ? umma_idesc_s8_s32(BLOCK_M, BN)
+                                       : OPK >= 2 ? umma_idesc_16bit_f32(BLOCK_M, BN, OPK == 2)
+                                                  : umma_idesc_e4m3_f32(PAIR ? 2 * BLOCK_M : BLOCK_M, BN);
             int stage = 0;
             uint32_t phase = 0;
             uint32_t acc_iter = 0;
@@ -580,6 +585,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                         umma_f8f6f4_2cta(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, accumulate);
                     else if constexpr (INT8)
                         umma_i8(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, accumulate);
+                    else if constexpr (OPK >= 2)
+                        umma_f16(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, accumulate);
                     else
                         umma_f8f6f4(d_tmem, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, accumulate);
                 }
@@ -1237,10 +1244,10 @@ bool pair_enabled() {
     return v != 0;
 }
 
-template <int BN, bool BS, bool SILU, bool SMALL_A = false, bool ASTORE = false, bool INT8 = false>
+template <int BN, bool BS, bool SILU, bool SMALL_A = false, bool ASTORE = false, int OPK = 0>
 int launch_inst(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int max_tiles, cudaStream_t st) {
     using C = Cfg<BN, SMALL_A, false, ASTORE>;
-    auto kernel = gemm_fp8_kernel<BN, BS, SILU, SMALL_A, false, false, ASTORE, INT8>;
+    auto kernel = gemm_fp8_kernel<BN, BS, SILU, SMALL_A, false, false, ASTORE, OPK>;
     static bool attr_done[64];
     static std::mutex mu;
     {
@@ -1335,11 +1342,20 @@ int launch_gemm(GemmParams& p, const void* a, int64_t a_rows, int64_t ld_a, cons
     const int t = (int)tiles;
     if (p.int8) {
         FG_REQUIRE(!block_scaled && (bn == 256 || bn == 128) && k_slices == 1 && !pair, FG_ERR_UNSUPPORTED,
-                   "int8 operands are built for the grouped expert GEMMs");
-        if (bn == 256) return fuse_silu ? launch_inst<256, false, true, false, false, true>(ta, tb, p, t, st)
-                                        : launch_inst<256, false, false, false, false, true>(ta, tb, p, t, st);
-        return fuse_silu ? launch_inst<128, false, true, false, false, true>(ta, tb, p, t, st)
-                         : launch_inst<128, false, false, false, false, true>(ta, tb, p, t, st);
+                   "int8 and 16-bit operands are built for the grouped expert GEMMs");
+        auto by_kind = [&](auto bn_tag, auto silu_tag) -> int {
+            constexpr int B = decltype(bn_tag)::value;
+            constexpr bool S = decltype(silu_tag)::value;
+            switch (p.int8) {
+                case 1: return launch_inst<B, false, S, false, false, 1>(ta, tb, p, t, st);
+                case 2: return launch_inst<B, false, S, false, false, 2>(ta, tb, p, t, st);
+                default: return launch_inst<B, false, S, false, false, 3>(ta, tb, p, t, st);
+            }
+        };
+        using I256 = std::integral_constant<int, 256>;
+        using I128 = std::integral_constant<int, 128>;
+        if (bn == 256) return fuse_silu ? by_kind(I256(), std::true_type()) : by_kind(I256(), std::false_type());
+        return fuse_silu ? by_kind(I128(), std::true_type()) : by_kind(I128(), std::false_type());
     }
     if (k_slices > 1) {
         if (bn == 256) return block_scaled ? launch_splitk<256, true>(ta, tb, p, t, k_slices, st)
@@ -1513,6 +1529,12 @@ static int grouped_gemm_common(int int8, void* c, const void* a, const void* w, 
                "fused SiLU with block scales needs the intermediate size %lld to be a multiple of 128",
                (long long)(N / 2));
     if (max_rows == 0) return FG_OK;
+    if (int8 >= 2) {  // 16-bit operands: the kernel counts K and the operand row strides in bytes
+        FG_REQUIRE(!block && K % 8 == 0 && 2 * K < (1ll << 31), FG_ERR_UNSUPPORTED,
+                   "16-bit operands take per-tensor or per-row x per-column scales and K a multiple of 8");
+        K *= 2;
+        ld_a *= 2;
+    }
     GemmParams p{};
     p.M = max_rows / block_rows * block_rows; p.N = (int)N; p.K = (int)K; p.n_out = fuse_silu ? (int)(N / 2) : (int)N;
     p.c = c; p.ld_c = ld_c; p.out_dtype = out_dtype;
@@ -1545,6 +1567,22 @@ int fg_moe_grouped_gemm_fp8_peer(void* c, const void* a, const void* w, const fl
                                expert_ids, num_post_pad, max_rows, numel, num_experts, N, K, ld_a, ld_c, block_rows,
                                scale_mode, a_scale_per_row, fuse_silu, scatter, mul_weight, out_dtype, dest, dest_stride,
                                peer_out, n_peers, peer_rows, stream);
+}
+
+int fg_moe_grouped_gemm_16bit(void* c, const void* a, const void* w, const float* a_scale, const float* w_scale,
+                              const void* topk_weights, int topk_w_dtype, int64_t topk_w_stride,
+                              const int32_t* sorted_ids, const int32_t* expert_ids, const int32_t* num_post_pad,
+                              int64_t max_rows, int64_t numel, int num_experts, int64_t N, int64_t K, int64_t ld_a,
+                              int64_t ld_c, int block_rows, int scale_mode, int a_scale_per_row, int fuse_silu,
+                              int scatter, int mul_weight, int operand_dtype, int out_dtype, void* stream) {
+    FG_REQUIRE(operand_dtype == FG_DTYPE_BF16 || operand_dtype == FG_DTYPE_F16, FG_ERR_INVALID_ARGUMENT,
+               "operand_dtype must be bf16 or fp16");
+    FG_REQUIRE(scale_mode == FG_SCALE_SCALAR || scale_mode == FG_SCALE_VECTOR, FG_ERR_UNSUPPORTED,
+               "16-bit expert GEMMs take per-tensor or per-row x per-column scales");
+    return grouped_gemm_common(operand_dtype == FG_DTYPE_BF16 ? 2 : 3, c, a, w, a_scale, w_scale, topk_weights,
+                               topk_w_dtype, topk_w_stride, sorted_ids, expert_ids, num_post_pad, max_rows, numel,
+                               num_experts, N, K, ld_a, ld_c, block_rows, scale_mode, a_scale_per_row, fuse_silu, scatter,
+                               mul_weight, out_dtype, nullptr, 0, nullptr, 0, 0, stream);
 }
 
 int fg_moe_grouped_gemm_int8(void* c, const void* a, const void* w, const float* a_scale, const float* w_scale,

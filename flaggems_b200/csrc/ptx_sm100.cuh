@@ -171,6 +171,24 @@ __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// 16-bit floating-point operands (kind::f16: bf16 x bf16 or f16 x f16), fp32 accumulators, K = 16
+// elements (the same 32 bytes of a K-major row as the 8-bit kinds).
+__host__ __device__ constexpr uint32_t umma_idesc_16bit_f32(int m, int n, bool bf16) {
+    return (1u << 4)                                              // D format fp32
+           | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10)   // A, B format: f16 = 0, bf16 = 1
+           | (0u << 15) | (0u << 16)                              // A, B K-major
+           | ((uint32_t)(n >> 3) << 17)                           // N / 8
+           | ((uint32_t)(m >> 4) << 24);                          // M / 16
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // Arrives on the mbarrier once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))

@@ -201,19 +201,94 @@ def _grouped_gemm(c, a, w, a_scale, w_scale, topk_weights, sorted_ids, expert_id
                   scale_mode, fuse_silu, scatter, mul_weight, block_rows=_TILE_ROWS, a_scale_per_row=None):
     e, n, k = w.shape
     c = c.view(-1, c.shape[-1])
-    entry = _cabi.lib().fg_moe_grouped_gemm_int8 if w.dtype == torch.int8 else _cabi.lib().fg_moe_grouped_gemm_fp8
-    _cabi.check(
-        entry(
-            _cabi.ptr(c), _cabi.ptr(a), _cabi.ptr(w), _cabi.ptr(a_scale), _cabi.ptr(w_scale),
-            _cabi.ptr(topk_weights), _cabi.DTYPE_CODE.get(topk_weights.dtype, -1) if topk_weights is not None else 0,
-            1,
-            _cabi.ptr(sorted_ids), _cabi.ptr(expert_ids), _cabi.ptr(num_post_pad),
-            a.shape[0], numel, e, n, k, a.stride(0), c.stride(0), block_rows, scale_mode,
-            (0 if scale_mode == _cabi.SCALE_SCALAR else 1) if a_scale_per_row is None else int(a_scale_per_row),
-            1 if fuse_silu else 0, 1 if scatter else 0, 1 if mul_weight else 0,
-            _cabi.DTYPE_CODE[c.dtype], _cabi.stream_ptr(a.device),
-        )
+    head = (
+        _cabi.ptr(c), _cabi.ptr(a), _cabi.ptr(w), _cabi.ptr(a_scale), _cabi.ptr(w_scale),
+        _cabi.ptr(topk_weights), _cabi.DTYPE_CODE.get(topk_weights.dtype, -1) if topk_weights is not None else 0,
+        1,
+        _cabi.ptr(sorted_ids), _cabi.ptr(expert_ids), _cabi.ptr(num_post_pad),
+        a.shape[0], numel, e, n, k, a.stride(0), c.stride(0), block_rows, scale_mode,
+        (0 if scale_mode == _cabi.SCALE_SCALAR else 1) if a_scale_per_row is None else int(a_scale_per_row),
+        1 if fuse_silu else 0, 1 if scatter else 0, 1 if mul_weight else 0,
     )
+    tail = (_cabi.DTYPE_CODE[c.dtype], _cabi.stream_ptr(a.device))
+    if w.dtype in (torch.bfloat16, torch.float16):
+        assert a.dtype == w.dtype, "16-bit expert GEMMs take both operands in one type"
+        _cabi.check(_cabi.lib().fg_moe_grouped_gemm_16bit(*head, _cabi.DTYPE_CODE[w.dtype], *tail))
+        return
+    entry = _cabi.lib().fg_moe_grouped_gemm_int8 if w.dtype == torch.int8 else _cabi.lib().fg_moe_grouped_gemm_fp8
+    _cabi.check(entry(*head, *tail))
+
+
+def _fused_experts_16bit(hidden_states, w1, w2, topk_weights, topk_ids, inplace, weight_only, w1_scale, w2_scale,
+                         global_num_experts, expert_map):
+    """Unquantised bf16 / fp16 experts and the weight-only int8 / int4 forms (int4 values in int8
+    containers) on the 16-bit tcgen05 grouped GEMM.  The reference converts integer weights to the
+    activation type and multiplies them by their per-channel scale before its GEMM
+    (fused_moe.py:1976-1983); here the integers are converted exactly and the fp32 scale is applied to
+    the fp32 accumulators, one rounding fewer per weight."""
+    assert hidden_states.size(1) == w1.size(2), f"Hidden size mismatch {hidden_states.size(1)} != {w1.size(2)}"
+    assert topk_weights.size() == topk_ids.size(), "topk shape mismatch"
+    assert hidden_states.is_contiguous(), "Hidden_states must be contiguous"
+    assert w1.is_contiguous() and w2.is_contiguous(), "expert weights must be contiguous"
+    assert topk_weights.stride(1) == 1
+    _cabi.require_cuda(hidden_states, w1, w2, topk_weights, topk_ids, w1_scale, w2_scale, expert_map)
+    dtype = hidden_states.dtype
+    if dtype not in (torch.bfloat16, torch.float16):
+        raise NotImplementedError(f"16-bit expert GEMMs take bf16 or fp16 activations, got {dtype}")
+    num_tokens, hidden = hidden_states.shape
+    e, n, _ = w1.shape
+    k_out = w2.size(1)
+    inter = n // 2
+    assert w2.size(2) == inter, "w2 inner size must be half of w1's output size"
+    if hidden % 8 or inter % 8:
+        raise NotImplementedError("hidden and intermediate sizes must be multiples of 8")
+    dev = hidden_states.device
+    if weight_only:
+        if w1.dtype != torch.int8 or w2.dtype != torch.int8:
+            raise NotImplementedError("weight-only experts are int8 tensors (int4 values in int8 containers)")
+        assert w1_scale is not None and w2_scale is not None, "weight-only experts need w1_scale and w2_scale"
+        w1s = w1_scale.float().reshape(e, -1).contiguous()
+        w2s = w2_scale.float().reshape(e, -1).contiguous()
+        assert w1s.shape == (e, n) and w2s.shape == (e, k_out), "per-channel scales must be [E, N]"
+        w1, w2 = w1.to(dtype), w2.to(dtype)  # exact: |v| <= 128
+        scale_mode = _cabi.SCALE_VECTOR
+    else:
+        if w1.dtype != dtype or w2.dtype != dtype:
+            raise NotImplementedError(f"unquantised expert weights must have the activation type {dtype}")
+        w1s = w2s = torch.ones(e, dtype=torch.float32, device=dev)
+        scale_mode = _cabi.SCALE_SCALAR
+    if global_num_experts == -1:
+        global_num_experts = e
+    top_k = topk_ids.size(1)
+    out = hidden_states if inplace else torch.empty_like(hidden_states)
+    if num_tokens == 0:
+        return out
+    tw = topk_weights if topk_weights.dtype in _cabi.DTYPE_CODE else topk_weights.float()
+    tw = tw.contiguous()
+    with _cabi.device_guard(hidden_states):
+        for begin in range(0, num_tokens, _CHUNK_SIZE):
+            end = min(begin + _CHUNK_SIZE, num_tokens)
+            h = hidden_states[begin:end]
+            ids = topk_ids[begin:end]
+            w = tw[begin:end].reshape(-1)
+            t = end - begin
+            numel = t * top_k
+            sorted_ids, expert_ids, post_pad = moe_align_block_size(ids, _TILE_ROWS, global_num_experts, expert_map)
+            rows = sorted_ids.numel() // _TILE_ROWS * _TILE_ROWS
+            # rows into expert order: a byte copy of the 16-bit rows (zeros for padding rows)
+            a1 = torch.empty((rows, hidden), dtype=dtype, device=dev)
+            _cabi.check(_cabi.lib().fg_gather_rows_fp8(
+                _cabi.ptr(h), None, _cabi.ptr(a1), None, rows, 2 * hidden, 0, 2 * h.stride(0), 1,
+                _cabi.ptr(sorted_ids), top_k, numel, _cabi.ptr(post_pad), _cabi.stream_ptr(dev)))
+            ones = torch.ones(rows if scale_mode == _cabi.SCALE_VECTOR else 1, dtype=torch.float32, device=dev)
+            act = torch.empty((rows, inter), dtype=dtype, device=dev)
+            _grouped_gemm(act, a1, w1, ones, w1s, None, sorted_ids, expert_ids, post_pad, numel, scale_mode,
+                          fuse_silu=True, scatter=False, mul_weight=False)
+            routed = torch.empty((t, top_k, k_out), dtype=dtype, device=dev)
+            _grouped_gemm(routed, act, w2, ones, w2s, w, sorted_ids, expert_ids, post_pad, numel, scale_mode,
+                          fuse_silu=False, scatter=True, mul_weight=True)
+            moe_sum(routed, out[begin:end])
+    return out
 
 
 def fused_experts_impl(
@@ -246,18 +321,21 @@ def fused_experts_impl(
     logger.debug("GEMS FUSED MOE")
     assert activation == "silu", f"Only 'silu' activation is supported, got {activation}"
     MoEActivation.from_str(activation)
-    if use_int8_w8a16 or use_int4_w4a16 or ocp_mx_scheme is not None:
-        raise NotImplementedError("weight-only (w8a16 / w4a16) and OCP MX expert formats are not implemented")
+    if ocp_mx_scheme is not None:
+        raise NotImplementedError("OCP MX expert formats are not implemented")
     if use_int8_w8a8 and (use_fp8_w8a8 or not per_channel_quant or block_shape is not None):
         raise NotImplementedError("int8 w8a8 is implemented for per-token x per-channel scales "
                                   "(use_int8_w8a8=True, per_channel_quant=True)")
-    if not use_fp8_w8a8 and not use_int8_w8a8:
-        raise NotImplementedError("unquantised (bf16/fp16) expert weights are not implemented; pass use_fp8_w8a8=True "
-                                  "or use_int8_w8a8=True")
     if w1_zp is not None or w2_zp is not None or w1_bias is not None or w2_bias is not None:
         raise NotImplementedError("zero points and expert biases are not implemented")
     if apply_router_weight_on_input:
         raise NotImplementedError("apply_router_weight_on_input is not implemented")
+    weight_only = use_int8_w8a16 or use_int4_w4a16
+    if weight_only or (not use_fp8_w8a8 and not use_int8_w8a8):
+        if weight_only and (use_fp8_w8a8 or use_int8_w8a8):
+            raise NotImplementedError("weight-only formats cannot be combined with w8a8")
+        return _fused_experts_16bit(hidden_states, w1, w2, topk_weights, topk_ids, inplace, weight_only, w1_scale,
+                                    w2_scale, global_num_experts, expert_map)
     if (a1_scale is not None or a2_scale is not None) and (block_shape is not None or per_channel_quant):
         raise NotImplementedError("static activation scales are implemented for the per-tensor mode only")
 

@@ -385,6 +385,20 @@ int fg_moe_grouped_gemm_int8(void* c, const void* a, const void* w, const float*
                              int block_rows, int scale_mode, int a_scale_per_row, int fuse_silu,
                              int scatter, int mul_weight, int out_dtype, void* stream);
 
+/* The same grouped GEMM on bf16 or fp16 operands with fp32 accumulation (tcgen05 kind::f16): the
+ * unquantised path of fused_moe_kernel (src/flag_gems/fused/fused_moe.py:1016, accumulate at :1468) and, with the
+ * integer weights converted to the activation type and their per-channel scales passed as w_scale,
+ * the weight-only int8 / int4 forms (:1976-1983).  a: [max_rows, K], w: [E, N, K], both of
+ * operand_dtype, K a multiple of 8; scale_mode FG_SCALE_SCALAR (a_scale[0] or per row, w_scale[e]) or
+ * FG_SCALE_VECTOR (a_scale[row], w_scale[e, n]); pass ones for an unscaled product. */
+int fg_moe_grouped_gemm_16bit(void* c, const void* a, const void* w, const float* a_scale,
+                              const float* w_scale, const void* topk_weights, int topk_w_dtype,
+                              int64_t topk_w_stride, const int32_t* sorted_ids, const int32_t* expert_ids,
+                              const int32_t* num_post_pad, int64_t max_rows, int64_t numel,
+                              int num_experts, int64_t N, int64_t K, int64_t ld_a, int64_t ld_c,
+                              int block_rows, int scale_mode, int a_scale_per_row, int fuse_silu,
+                              int scatter, int mul_weight, int operand_dtype, int out_dtype, void* stream);
+
 /* ---- aten _scaled_grouped_mm ------------------------------------------------ */
 
 /* scaled_grouped_mm, the "A 2-D, B 3-D" form: src/flag_gems/ops/scaled_grouped_mm.py:470-583 (kernel

@@ -39,6 +39,7 @@ from .moe import (  # noqa: F401
     fused_moe_block_fp8,
     fused_moe_per_channel_fp8,
     fused_moe_per_channel_int8,
+    fused_moe_16bit,
     fused_moe_per_tensor_fp8,
     dense_block_fp8_mlp,
 )

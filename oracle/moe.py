@@ -251,6 +251,46 @@ def fused_moe_per_channel_int8(
     return moe_sum(out).to(hidden.dtype)
 
 
+def fused_moe_16bit(
+    hidden: torch.Tensor,
+    w1: torch.Tensor,
+    w2: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    w1_scale: Optional[torch.Tensor] = None,
+    w2_scale: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Unquantised (bf16 / fp16) MoE layer and the weight-only int8 / int4 forms.
+
+    Restated from src/flag_gems/fused/fused_moe.py: integer weights (int4 values live in int8
+    containers) are converted to the activation type (:1976-1983); products of 16-bit operands
+    accumulate in fp32 (``tl.dot``, :1468); fused SiLU in fp32 (:1344) rounded to the activation
+    type; router weight in fp32 then cast (:1485-1493); fp32 top-k sum.  One deliberate difference:
+    the reference multiplies the converted weights by their per-channel scale in the activation
+    type before the product (one more rounding of every weight); here, as in the device path, the
+    exactly converted integers are multiplied and the fp32 scale is applied to the fp32 sums, which
+    is what the reference's own golden for these modes computes
+    (tests/test_fused_experts_impl.py:837-872, fp32 ``w_int * scale``).
+    w1: [E, 2I, H], w2: [E, H, I]; w*_scale: None or [E, N] per output channel."""
+    t, h = hidden.shape
+    topk = topk_ids.shape[1]
+    out = torch.zeros(t, topk, w2.shape[1], dtype=torch.float32)
+    for e in range(w1.shape[0]):
+        tok, slot = torch.nonzero(topk_ids == e, as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        z = torch.mm(hidden[tok].float(), w1[e].to(hidden.dtype).float().t())
+        if w1_scale is not None:
+            z = z * w1_scale[e].float().reshape(1, -1)
+        act = _silu_mul_f32(z, True, hidden.dtype)
+        r = torch.mm(act.float(), w2[e].to(hidden.dtype).float().t())
+        if w2_scale is not None:
+            r = r * w2_scale[e].float().reshape(1, -1)
+        r = (r * topk_weights[tok, slot].float().unsqueeze(1)).to(hidden.dtype)
+        out[tok, slot] = r.float()
+    return moe_sum(out).to(hidden.dtype)
+
+
 def fused_moe_per_tensor_fp8(
     hidden: torch.Tensor,
     w1: torch.Tensor,

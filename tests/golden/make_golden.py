@@ -251,6 +251,29 @@ def main():
                           topk_weights=tw, topk_ids=ti, out=out))
     save("fused_moe_fake_quant_int8", cases)
 
+    # ---- weight-only golden (torch_fused_moe_weight_only_reference, :837-872) on the recipes of
+    # test_fused_moe_int8_w8a16 (:880-950) and test_fused_moe_int4_w4a16 (:958-1030, int4 values in int8
+    # containers): per-channel symmetric weights, bf16 activations, everything in fp32.
+    wo = lift("tests/test_fused_experts_impl.py", ["torch_fused_moe_weight_only_reference"])
+    g4 = torch.Generator().manual_seed(0)
+    cases = []
+    for bits, (t, e, h, i, topk) in ((8, (4, 8, 128, 256, 2)), (8, (32, 4, 128, 128, 4)), (4, (16, 4, 128, 128, 2))):
+        qmax, qmin = (127, -128) if bits == 8 else (7, -8)
+        hidden = torch.randn(t, h, generator=g4).bfloat16()
+        quant = []
+        for w in (torch.randn(e, 2 * i, h, generator=g4) * (1.0 / h ** 0.5),
+                  torch.randn(e, h, i, generator=g4) * (1.0 / i ** 0.5)):
+            sc = w.abs().amax(dim=-1, keepdim=True).clamp(min=1e-10) / qmax
+            quant.append(((w / sc).round().clamp(qmin, qmax).to(torch.int8), sc.squeeze(-1)))
+        gating = torch.randn(t, e, generator=g4)
+        tw, ti = torch.topk(torch.softmax(gating, -1), topk)
+        tw = (tw / tw.sum(-1, keepdim=True)).bfloat16()
+        out = wo["torch_fused_moe_weight_only_reference"](hidden, quant[0][0], quant[1][0], quant[0][1], quant[1][1],
+                                                          tw, ti)
+        cases.append(dict(bits=bits, hidden=hidden, w1=quant[0][0], w2=quant[1][0], w1_scale=quant[0][1],
+                          w2_scale=quant[1][1], topk_weights=tw, topk_ids=ti, out=out))
+    save("fused_moe_weight_only", cases)
+
 
 if __name__ == "__main__":
     if not os.path.isdir(REF):

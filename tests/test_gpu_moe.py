@@ -225,3 +225,68 @@ def test_fused_moe_int8_golden(golden_dir):
         flag_gems.fused_experts_impl(c["hidden"].cuda(), c["w1"].cuda(), c["w2"].cuda(), c["topk_weights"].cuda(),
                                      c["topk_ids"].cuda(), use_int8_w8a8=True, w1_scale=c["w1_scale"].cuda(),
                                      w2_scale=c["w2_scale"].cuda())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("t,h,i,e,topk", [(33, 256, 128, 8, 2), (200, 1024, 512, 16, 4), (512, 4096, 1024, 8, 2),
+                                          (1, 512, 256, 4, 1)])
+def test_fused_moe_unquantised_16bit(t, h, i, e, topk, dtype):
+    """The default path of fused_experts_impl (no quantisation flags): 16-bit tcgen05 grouped GEMMs."""
+    g = torch.Generator().manual_seed(21)
+    hidden = torch.randn(t, h, generator=g).to(dtype)
+    w1 = (torch.randn(e, 2 * i, h, generator=g) * h ** -0.5).to(dtype)
+    w2 = (torch.randn(e, h, i, generator=g) * i ** -0.5).to(dtype)
+    tw, ti = _router(t, e, topk, g)
+    tw = tw.to(dtype)
+    out = flag_gems.fused_experts_impl(hidden.cuda(), w1.cuda(), w2.cuda(), tw.cuda(), ti.cuda())
+    ref = oracle.fused_moe_16bit(hidden, w1, w2, tw, ti)
+    assert out.shape == hidden.shape and out.dtype == dtype
+    _close(out, ref)
+    assert _cabi.device_status() == 0
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("t,e,h,i,topk", [(1, 8, 128, 256, 2), (4, 8, 128, 256, 2), (16, 8, 256, 512, 2),
+                                          (32, 8, 128, 256, 2), (64, 8, 512, 1024, 2)])
+def test_fused_moe_weight_only(t, e, h, i, topk, bits):
+    """Recipe of tests/test_fused_experts_impl.py:880-1030 (int8 w8a16, and int4 values in int8 containers):
+    per-channel symmetric weights, bf16 activations.  Against the oracle at the path's own tolerance and
+    against the reference test's fp32 golden at the reference test's tolerance."""
+    g = torch.Generator().manual_seed(0)
+    dtype = torch.bfloat16
+    hidden = torch.randn(t, h, generator=g).to(dtype)
+    qmax, qmin = (127, -128) if bits == 8 else (7, -8)
+    def quant(w):
+        sc = w.abs().amax(-1, keepdim=True).clamp(min=1e-10) / qmax
+        return (w / sc).round().clamp(qmin, qmax).to(torch.int8), sc.squeeze(-1)
+    w1, s1 = quant(torch.randn(e, 2 * i, h, generator=g) * h ** -0.5)
+    w2, s2 = quant(torch.randn(e, h, i, generator=g) * i ** -0.5)
+    tw, ti = _router(t, e, topk, g)
+    kw = dict(use_int8_w8a16=True) if bits == 8 else dict(use_int4_w4a16=True)
+    out = flag_gems.fused_experts_impl(hidden.cuda(), w1.cuda(), w2.cuda(), tw.cuda(), ti.cuda(),
+                                       per_channel_quant=True, w1_scale=s1.cuda(), w2_scale=s2.cuda(), **kw)
+    _close(out, oracle.fused_moe_16bit(hidden, w1, w2, tw, ti, s1, s2))
+    # the reference test's golden: everything in fp32, rows weighted and rounded, summed in the output type
+    gold = torch.zeros(t, h, dtype=dtype)
+    for m in range(t):
+        for j in range(topk):
+            ex = int(ti[m, j])
+            z = hidden[m].float() @ (w1[ex].float() * s1[ex].unsqueeze(-1)).t()
+            gate, up = z[:i], z[i:]
+            r = ((gate * torch.sigmoid(gate)) * up) @ (w2[ex].float() * s2[ex].unsqueeze(-1)).t()
+            gold[m] += (tw[m, j].float() * r).to(dtype)
+    rtol, atol_rel = (2e-1, 2e-2) if bits == 8 else (3e-1, 5e-2)
+    torch.testing.assert_close(out.cpu(), gold, rtol=rtol, atol=max(5e-2, float(gold.abs().max()) * atol_rel))
+    assert _cabi.device_status() == 0
+
+
+def test_fused_moe_weight_only_golden(golden_dir):
+    """The committed outputs of the reference's weight-only golden, at the reference tests' tolerances."""
+    for c in torch.load(os.path.join(golden_dir, "fused_moe_weight_only.pt")):
+        kw = dict(use_int8_w8a16=True) if c["bits"] == 8 else dict(use_int4_w4a16=True)
+        out = flag_gems.fused_experts_impl(c["hidden"].cuda(), c["w1"].cuda(), c["w2"].cuda(), c["topk_weights"].cuda(),
+                                           c["topk_ids"].cuda(), per_channel_quant=True, w1_scale=c["w1_scale"].cuda(),
+                                           w2_scale=c["w2_scale"].cuda(), **kw)
+        ref = c["out"].float()
+        rtol, rel = (2e-1, 2e-2) if c["bits"] == 8 else (3e-1, 5e-2)
+        torch.testing.assert_close(out.cpu().float(), ref, rtol=rtol, atol=max(5e-2, ref.abs().max().item() * rel))

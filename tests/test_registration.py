@@ -95,7 +95,13 @@ def test_unsupported_modes_raise_cleanly():
     with pytest.raises(NotImplementedError):
         flag_gems.fused_experts_impl(h, w1, w2, tw, ti, use_int8_w8a8=True)
     with pytest.raises(NotImplementedError):
-        flag_gems.fused_experts_impl(h, w1, w2, tw, ti)
+        flag_gems.fused_experts_impl(h, w1, w2, tw, ti, ocp_mx_scheme="w_mxfp4_a_bf16")
+    with pytest.raises(NotImplementedError):
+        flag_gems.fused_experts_impl(h, w1, w2, tw, ti, use_int8_w8a16=True, use_fp8_w8a8=True)
+    # the unquantised path exists, and like every path it has no CPU fallback
+    from flaggems_b200._cabi import FlagGemsB200Error
+    with pytest.raises(FlagGemsB200Error):
+        flag_gems.fused_experts_impl(h, w1.bfloat16(), w2.bfloat16(), tw, ti)
     with pytest.raises(AssertionError):
         flag_gems.fused_experts_impl(h, w1, w2, tw, ti, activation="gelu", use_fp8_w8a8=True)
 
