@@ -454,10 +454,37 @@ def invoke_fused_moe_triton_kernel(A, B, C, A_scale, B_scale, topk_weights, sort
     assert topk_weights is not None or not mul_routed_weight
     assert topk_weights is None or topk_weights.stride(1) == 1
     assert sorted_token_ids is None or sorted_token_ids.stride(0) == 1
-    if not use_fp8_w8a8 or use_int8_w8a8 or use_int8_w8a16 or use_int4_w4a16:
-        raise NotImplementedError("only use_fp8_w8a8 is implemented")
+    if use_int8_w8a8 or use_int8_w8a16 or use_int4_w4a16:
+        raise NotImplementedError("use_fp8_w8a8 and unquantised 16-bit operands are implemented here")
     if B_bias is not None or direct_sum:
         raise NotImplementedError("expert bias and direct_sum are not implemented")
+    if not use_fp8_w8a8:
+        # unquantised operands (the reference's plain tl.dot branch, fused_moe.py:1468): bf16 or fp16 A and B
+        assert A.dtype == B.dtype and A.dtype in (torch.bfloat16, torch.float16), "16-bit operands of one type"
+        _cabi.require_cuda(A, B, C, sorted_token_ids, expert_ids, num_tokens_post_padded)
+        block_rows = int(config["BLOCK_SIZE_M"])
+        e, n, k = B.shape
+        m = A.shape[0]
+        numel = m * top_k
+        assert C.dtype == _dtype_of(compute_type), "C must have the compute dtype"
+        c2 = C.view(-1, n // 2 if FUSE_SILU else n)
+        rows = sorted_token_ids.numel() // block_rows * block_rows
+        with _cabi.device_guard(A):
+            a_sorted = torch.empty((rows, k), dtype=A.dtype, device=A.device)
+            _cabi.check(_cabi.lib().fg_gather_rows_fp8(
+                _cabi.ptr(A), None, _cabi.ptr(a_sorted), None, rows, 2 * k, 0, 2 * A.stride(0), 1,
+                _cabi.ptr(sorted_token_ids), top_k, numel, _cabi.ptr(num_tokens_post_padded),
+                _cabi.stream_ptr(A.device)))
+            tw = None
+            if mul_routed_weight:
+                tw = topk_weights if topk_weights.dtype in _cabi.DTYPE_CODE else topk_weights.float()
+                tw = tw.contiguous().reshape(-1)
+            one_a = torch.ones(1, dtype=torch.float32, device=A.device)
+            one_b = torch.ones(e, dtype=torch.float32, device=A.device)
+            _grouped_gemm(c2, a_sorted, B, one_a, one_b, tw, sorted_token_ids, expert_ids, num_tokens_post_padded,
+                          numel, _cabi.SCALE_SCALAR, fuse_silu=FUSE_SILU, scatter=True, mul_weight=mul_routed_weight,
+                          block_rows=block_rows, a_scale_per_row=0)
+        return
     assert B_scale is not None and A_scale is not None
     _cabi.require_cuda(A, B, C, A_scale, B_scale, sorted_token_ids, expert_ids, num_tokens_post_padded)
     block_rows = int(config["BLOCK_SIZE_M"])
@@ -505,7 +532,7 @@ def dispatch_fused_moe_kernel(A, B, C, A_scale, B_scale, B_zp, topk_weights, sor
                               num_tokens_post_padded, mul_routed_weight, top_k, config, compute_type, use_fp8_w8a8,
                               use_int8_w8a8, use_int8_w8a16, use_int4_w4a16, per_channel_quant, block_shape=None,
                               B_bias=None, FUSE_SILU=False, direct_sum=False, out_top_k=1) -> None:
-    """Reference: fused_moe.py:1730-1818.  The weight-only (wna16) branch is not implemented."""
+    """Reference: fused_moe.py:1730-1818.  The zero-point (wna16 / GPTQ-AWQ) branch is not implemented."""
     if B_zp is not None:
         raise NotImplementedError("zero points (weight-only quantisation) are not implemented")
     invoke_fused_moe_triton_kernel(A, B, C, A_scale, B_scale, topk_weights, sorted_token_ids, expert_ids,

@@ -290,3 +290,27 @@ def test_fused_moe_weight_only_golden(golden_dir):
         ref = c["out"].float()
         rtol, rel = (2e-1, 2e-2) if c["bits"] == 8 else (3e-1, 5e-2)
         torch.testing.assert_close(out.cpu().float(), ref, rtol=rtol, atol=max(5e-2, ref.abs().max().item() * rel))
+
+
+@pytest.mark.parametrize("block_m", [16, 128])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_dispatch_fused_moe_kernel_unquantised(block_m, dtype):
+    """The launch-level API with 16-bit operands and no quantisation flags (the reference's plain branch)."""
+    g = torch.Generator().manual_seed(5)
+    t, k, n, e, topk = 77, 520, 384, 8, 2
+    a = torch.randn(t, k, generator=g).to(dtype)
+    w = (torch.randn(e, n, k, generator=g) * 0.05).to(dtype)
+    tw, ti = _router(t, e, topk, g)
+    sorted_ids, expert_ids, post_pad = flag_gems.moe_align_block_size(ti.cuda(), block_m, e)
+    c = torch.full((t, topk, n), float("nan"), dtype=dtype, device="cuda")
+    flag_gems.dispatch_fused_moe_kernel(
+        a.cuda(), w.cuda(), c, None, None, None, tw.cuda(), sorted_ids, expert_ids, post_pad,
+        True, topk, {"BLOCK_SIZE_M": block_m}, dtype, False, False, False, False, False)
+    ref = torch.zeros(t, topk, n)
+    for x in range(e):
+        tok, slot = torch.nonzero(ti == x, as_tuple=True)
+        if tok.numel():
+            r = torch.mm(a[tok].float(), w[x].float().t())
+            ref[tok, slot] = (r * tw[tok, slot].float().unsqueeze(1)).to(dtype).float()
+    assert not torch.isnan(c.float()).any()
+    _close(c, ref)
