@@ -827,7 +827,8 @@ def run_capture_case(args):
       moe_gemm2    the matching GEMM2 (router weight, rows scattered back)
       block_mm     w8a8 block-scaled GEMM, M = N = 8192, K = 7168
       scaled_mm    per-token x per-channel GEMM, same shape
-      group_quant  per_token_group_quant_fp8 and act_quant on [16384, 7168] bf16"""
+      group_quant  per_token_group_quant_fp8 and act_quant on [16384, 7168] bf16
+      moe_glue     the FP8 row gather into expert order and the top-k sum, on 2048 tokens of the layer"""
     import flag_gems
     from flaggems_b200 import _cabi
     from flaggems_b200.fused.fused_moe import _TILE_ROWS, _group_quant, _grouped_gemm
@@ -893,6 +894,27 @@ def run_capture_case(args):
             flag_gems.act_quant_triton(x, 128)
 
         flops, info = 0.0, {"M": 16384, "K": 7168, "bytes_per_kernel": 16384 * 7168 * (2 + 1 + 4 / 128)}
+    elif name == "moe_glue":
+        # the two data-movement kernels of the layer at a quarter of the step: 2048 tokens, top-8
+        from flaggems_b200.fused.fused_moe import _group_quant_once_then_gather
+        from flaggems_b200.fused.moe_sum import moe_sum
+
+        t = 2048
+        hid = torch.randn(t, HIDDEN, device=dev, generator=g).bfloat16()
+        _, ti = make_router(t, EXPERTS, TOPK)
+        ids = ti.to(torch.int32).to(dev)
+        sorted_ids, expert_ids, post_pad = moe_align_block_size(ids, _TILE_ROWS, EXPERTS)
+        rows = sorted_ids.numel() // _TILE_ROWS * _TILE_ROWS
+        routed = torch.randn(t, TOPK, HIDDEN, device=dev, generator=g).bfloat16()
+        out = torch.empty(t, HIDDEN, dtype=torch.bfloat16, device=dev)
+
+        def fn():
+            _group_quant_once_then_gather(hid, 128, sorted_ids, TOPK, t * TOPK, post_pad, rows)
+            moe_sum(routed, out)
+
+        flops, info = 0.0, {"tokens": t, "rows_padded": int(post_pad),
+                            "gather_bytes": 2 * int(post_pad) * (HIDDEN + 4 * HIDDEN // 128),
+                            "moe_sum_bytes": t * HIDDEN * 2 * (TOPK + 1)}
     else:
         raise SystemExit(f"unknown --workload {name!r}")
     for _ in range(2):
@@ -925,7 +947,7 @@ def main():
                     help="return expert outputs by NCCL all-to-all instead of the fused peer-memory combine")
     ap.add_argument("--workload", default="moe_layer",
                     help="moe_layer (the benchmark) or a single-kernel capture case: moe_gemm1, moe_gemm2, block_mm, "
-                         "scaled_mm, group_quant")
+                         "scaled_mm, group_quant, moe_glue")
     args = ap.parse_args()
     if args.workload != "moe_layer":
         run_capture_case(args)
