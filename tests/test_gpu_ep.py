@@ -265,3 +265,44 @@ def test_bounded_wait_runs_out_and_reports():
 
     q, s = flag_gems.per_token_group_quant_fp8(x, 128)
     assert q.shape == x.shape and s.shape == (4, 2)
+
+
+def test_dispatch_staged_equals_per_slot_quantisation():
+    """The two forms of the dispatch kernel entry put the same bytes into the receive buffers: quantising
+    every token once into staging rows and copying them out, or quantising per route slot while sending."""
+    import ctypes
+
+    from flaggems_b200 import _cabi
+    from flaggems_b200.ep import CudaMoEOps
+
+    dev = torch.device("cuda", 0)
+    hidden, w1, w2, s1, s2, tw, ti, shared = make_case(seed=9, t=96, h=512, i=256, e=16, topk=4)
+    world, rank = 4, 1
+    ops = CudaMoEOps(w1[:4].to(dev), w2[:4].to(dev), s1[:4].to(dev), s2[:4].to(dev), None)
+    h, w, i = hidden.to(dev), tw.to(dev).contiguous(), ti.to(dev).contiguous()
+    t, topk = i.shape
+    region = t * topk
+    order, counts = ops.route(i, world)
+    counts = counts.contiguous()
+    bufs = []
+    for staged in (True, False):
+        recv = [torch.full((world * region, ops.row_bytes), 0xAB, dtype=torch.uint8, device=dev) for _ in range(world)]
+        ptrs = (ctypes.c_void_p * world)(*[b.data_ptr() for b in recv])
+        if staged:
+            ops.pack_to_peers(h, i, w, order, counts, world, rank, ptrs, region)
+        else:
+            _cabi.check(_cabi.lib().fg_ep_pack_rows_fp8_peer(
+                _cabi.ptr(h), _cabi.DTYPE_CODE[h.dtype], t, ops.hidden, h.stride(0), _cabi.ptr(i),
+                1 if i.dtype == torch.int64 else 0, _cabi.ptr(w), _cabi.DTYPE_CODE[w.dtype], topk, ops.num_local_experts,
+                rank, _cabi.ptr(order), None, ops.row_bytes, None, _cabi.ptr(counts), ptrs, world, region,
+                _cabi.stream_ptr(dev)))
+        torch.cuda.synchronize()
+        bufs.append([b.cpu() for b in recv])
+    assert _cabi.device_status() == 0
+    c = counts.cpu().tolist()
+    assert sum(c) == region
+    for d in range(world):
+        lo = rank * region
+        assert torch.equal(bufs[0][d][lo:lo + c[d]], bufs[1][d][lo:lo + c[d]])
+        # nothing outside this rank's region, or beyond its count, was touched
+        assert bool((bufs[0][d][:lo] == 0xAB).all()) and bool((bufs[0][d][lo + c[d]:] == 0xAB).all())
