@@ -314,3 +314,37 @@ def test_dispatch_fused_moe_kernel_unquantised(block_m, dtype):
             ref[tok, slot] = (r * tw[tok, slot].float().unsqueeze(1)).to(dtype).float()
     assert not torch.isnan(c.float()).any()
     _close(c, ref)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("mode", ["block", "channel"])
+def test_fused_moe_fp8_other_activation_types(mode, dtype):
+    """The reference accepts fp16 and fp32 hidden states as well (fused_moe.py:1879); intermediates and the
+    output then have that type."""
+    g = torch.Generator().manual_seed(17)
+    t, h, i, e, topk = 96, 512, 256, 8, 2
+    hidden = torch.randn(t, h, generator=g).to(dtype)
+    tw, ti = _router(t, e, topk, g)
+    tw = tw.to(dtype)
+    if mode == "block":
+        w1 = torch.empty(e, 2 * i, h, dtype=FP8)
+        w2 = torch.empty(e, h, i, dtype=FP8)
+        s1 = torch.empty(e, 2 * i // 128, h // 128)
+        s2 = torch.empty(e, h // 128, i // 128)
+        for x in range(e):
+            w1[x], s1[x] = oracle.quantize_weight_block(torch.randn(2 * i, h, generator=g) * 0.02)
+            w2[x], s2[x] = oracle.quantize_weight_block(torch.randn(h, i, generator=g) * 0.02)
+        out = flag_gems.fused_experts_impl(hidden.cuda(), w1.cuda(), w2.cuda(), tw.cuda(), ti.cuda(),
+                                           use_fp8_w8a8=True, w1_scale=s1.cuda(), w2_scale=s2.cuda(),
+                                           block_shape=[128, 128])
+        ref = oracle.fused_moe_block_fp8(hidden, w1, w2, s1, s2, tw, ti)
+    else:
+        w1, s1 = oracle.quantize_weight_per_channel(torch.randn(e, 2 * i, h, generator=g) * 0.02)
+        w2, s2 = oracle.quantize_weight_per_channel(torch.randn(e, h, i, generator=g) * 0.02)
+        out = flag_gems.fused_experts_impl(hidden.cuda(), w1.cuda(), w2.cuda(), tw.cuda(), ti.cuda(),
+                                           use_fp8_w8a8=True, per_channel_quant=True,
+                                           w1_scale=s1.cuda(), w2_scale=s2.cuda())
+        ref = oracle.fused_moe_per_channel_fp8(hidden, w1, w2, s1, s2, tw, ti)
+    assert out.dtype == dtype
+    _close(out, ref)
+    assert _cabi.device_status() == 0
