@@ -348,3 +348,29 @@ def test_fused_moe_fp8_other_activation_types(mode, dtype):
     assert out.dtype == dtype
     _close(out, ref)
     assert _cabi.device_status() == 0
+
+
+def test_fused_moe_16bit_expert_map_inplace_and_empty():
+    """The unquantised path under the reference's expert-parallel convention (non-local experts map to -1 and
+    contribute zeros; the halves add up), in place, through outplace_fused_experts, and with no tokens."""
+    g = torch.Generator().manual_seed(23)
+    t, h, i, e, topk = 96, 512, 256, 8, 2
+    hidden = torch.randn(t, h, generator=g).bfloat16()
+    w1 = (torch.randn(e, 2 * i, h, generator=g) * h ** -0.5).bfloat16()
+    w2 = (torch.randn(e, h, i, generator=g) * i ** -0.5).bfloat16()
+    tw, ti = _router(t, e, topk, g)
+    full = flag_gems.fused_experts_impl(hidden.cuda(), w1.cuda(), w2.cuda(), tw.cuda(), ti.cuda())
+    parts = []
+    for lo in (0, 4):
+        emap = torch.full((e,), -1, dtype=torch.int32)
+        emap[lo:lo + 4] = torch.arange(4, dtype=torch.int32)
+        parts.append(flag_gems.fused_experts_impl(hidden.cuda(), w1[lo:lo + 4].cuda(), w2[lo:lo + 4].cuda(), tw.cuda(),
+                                                  ti.cuda(), global_num_experts=e, expert_map=emap.cuda()))
+    torch.testing.assert_close((parts[0].float() + parts[1].float()).cpu(), full.float().cpu(), rtol=2e-2, atol=2e-2)
+    hc = hidden.cuda().clone()
+    flag_gems.inplace_fused_experts(hc, w1.cuda(), w2.cuda(), tw.cuda(), ti.cuda())
+    assert torch.equal(hc, full)
+    assert torch.equal(flag_gems.outplace_fused_experts(hidden.cuda(), w1.cuda(), w2.cuda(), tw.cuda(), ti.cuda()), full)
+    empty = flag_gems.fused_experts_impl(hidden[:0].cuda(), w1.cuda(), w2.cuda(), tw[:0].cuda(), ti[:0].cuda())
+    assert empty.shape == (0, h)
+    assert _cabi.device_status() == 0
