@@ -825,6 +825,7 @@ def run_capture_case(args):
       moe_gemm1    grouped block-scaled GEMM1 with fused SiLU, 32 experts / the rows the T=8192 router sends
                    them (one rank's share at 8 ranks; an eighth of the single-GPU launch)
       moe_gemm2    the matching GEMM2 (router weight, rows scattered back)
+      moe_gemm1_bf16  GEMM1 of the same shape on unquantised bf16 operands
       block_mm     w8a8 block-scaled GEMM, M = N = 8192, K = 7168
       scaled_mm    per-token x per-channel GEMM, same shape
       group_quant  per_token_group_quant_fp8 and act_quant on [16384, 7168] bf16
@@ -869,6 +870,29 @@ def run_capture_case(args):
 
         fn = gemm1 if name == "moe_gemm1" else gemm2
         flops = 2.0 * n_rows * (2 * INTER if name == "moe_gemm1" else HIDDEN) * (HIDDEN if name == "moe_gemm1" else INTER)
+        info = {"experts": e, "rows": n_rows, "rows_padded": int(post_pad)}
+    elif name == "moe_gemm1_bf16":
+        # the same grouped GEMM1 on unquantised bf16 operands (tcgen05 kind::f16)
+        from flaggems_b200.ep import balanced_expert_placement
+
+        e = 32
+        _, ti = make_router(TOKENS, EXPERTS, TOPK)
+        ti = balanced_expert_placement(torch.bincount(ti.reshape(-1), minlength=EXPERTS), EXPERTS // e)[ti]
+        ids = ti[ti < e].to(torch.int32).to(dev)
+        n_rows = ids.numel()
+        sorted_ids, expert_ids, post_pad = moe_align_block_size(ids, _TILE_ROWS, e)
+        rows = sorted_ids.numel() // _TILE_ROWS * _TILE_ROWS
+        a1 = torch.randn(rows, HIDDEN, device=dev, generator=g).bfloat16()
+        w1 = (torch.randn(e, 2 * INTER, HIDDEN, device=dev, generator=g) * 0.02).bfloat16()
+        act = torch.empty((rows, INTER), dtype=torch.bfloat16, device=dev)
+        one_a = torch.ones(1, device=dev)
+        one_b = torch.ones(e, device=dev)
+
+        def fn():
+            _grouped_gemm(act, a1, w1, one_a, one_b, None, sorted_ids, expert_ids, post_pad, n_rows,
+                          _cabi.SCALE_SCALAR, fuse_silu=True, scatter=False, mul_weight=False)
+
+        flops = 2.0 * n_rows * 2 * INTER * HIDDEN
         info = {"experts": e, "rows": n_rows, "rows_padded": int(post_pad)}
     elif name in ("block_mm", "scaled_mm"):
         m = n = 8192
@@ -947,7 +971,7 @@ def main():
                     help="return expert outputs by NCCL all-to-all instead of the fused peer-memory combine")
     ap.add_argument("--workload", default="moe_layer",
                     help="moe_layer (the benchmark) or a single-kernel capture case: moe_gemm1, moe_gemm2, block_mm, "
-                         "scaled_mm, group_quant, moe_glue")
+                         "scaled_mm, group_quant, moe_glue, moe_gemm1_bf16")
     args = ap.parse_args()
     if args.workload != "moe_layer":
         run_capture_case(args)
