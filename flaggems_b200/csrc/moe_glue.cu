@@ -300,7 +300,9 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(const T* __restrict__ in, 
 }
 
 // Copies rows of FP8 bytes and their fp32 scale rows through an index (pure data movement).
-// One warp per destination row, four 16-byte loads per lane in flight before the first store.
+// One warp per destination row, eight 16-byte loads per lane in flight before the first store
+// (measured 142 us against 148 with four, and 158 with plain instead of streaming stores, for the
+// 82688 rows of the DeepSeek-V3-shaped step: the destination is a 611 MB write stream).
 __global__ void __launch_bounds__(256) gather_rows_kernel(const uint8_t* __restrict__ src_q,
                                                           const float* __restrict__ src_s, uint8_t* __restrict__ dst_q,
                                                           float* __restrict__ dst_s, int64_t rows, int64_t K,
@@ -323,15 +325,15 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint8_t* __restr
         const uint4* sq = reinterpret_cast<const uint4*>(src_q + src * src_q_stride);
         uint4* dq = reinterpret_cast<uint4*>(dst_q + r * K);
         const float sv = (real && lane < s_cols) ? src_s[src * src_s_stride + lane] : 1.0f;
-        for (int v0 = lane; v0 < nvec; v0 += 128) {
-            uint4 t[4];
+        for (int v0 = lane; v0 < nvec; v0 += 256) {
+            uint4 t[8];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < 8; ++u) {
                 const int v = v0 + 32 * u;
                 t[u] = (real && v < nvec) ? __ldg(sq + v) : make_uint4(0u, 0u, 0u, 0u);
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < 8; ++u) {
                 const int v = v0 + 32 * u;
                 if (v < nvec) __stcs(dq + v, t[u]);
             }
